@@ -1,0 +1,537 @@
+// Public API: cuttPlan / cuttPlanMeasure / cuttExecute / cuttDestroy (C++ symbols of
+// include/cutt.h) and their extern "C" twins (include/cutt_c.h).
+//
+// Behaviour follows src/cutt.cpp of the original library:
+//   validation rules                         src/cutt.cpp:59-82
+//   handles 0,1,2,... consumed once the input is valid, even if planning fails later   :96-97
+//   cuttPlanMeasure rejects idata == odata, overwrites odata, synchronises the device   :193,240-250
+//   cuttExecute: unknown handle -> INVALID_PLAN, idata == odata -> INVALID_PARAMETER,
+//                other current device -> INVALID_DEVICE                                 :296-308
+// Differences (supersets): CUDA failures return CUTT_INTERNAL_ERROR instead of exiting the
+// process; the handle table and the plan cache are guarded by a mutex; plans own no device
+// memory; measured winners are remembered in an LRU plan cache that cuttPlan consults.
+#include "../../include/cutt.h"
+#include "../../include/cutt_c.h"
+
+#include <cstdio>
+#include <cstdlib>
+#include <cstring>
+#include <list>
+#include <memory>
+#include <mutex>
+#include <string>
+#include <unordered_map>
+#include <vector>
+
+#include "kernels.h"
+#include "planner.h"
+
+using namespace cuttb;
+
+namespace {
+
+struct Plan {
+  int device = 0;
+  cudaStream_t stream = 0;
+  int elt = 4;
+  size_t bytes = 0;
+  Method method = kMethodTiles;
+  Problem prob;
+  Candidate cand;          // tiled candidate in use
+  int grid = 0;
+  bool haveFallback = false;
+  Candidate fallback;      // same tile with element-sized accesses, for unaligned pointers
+  int fallbackGrid = 0;
+  NaiveDesc naive;
+  int numSM = 148;
+  std::string note;
+};
+
+struct CachedChoice {
+  Method method;
+  TileParams params;
+};
+
+// LRU map: problem key -> choice found by measurement.
+class PlanCache {
+ public:
+  explicit PlanCache(size_t cap) : cap_(cap) {}
+  bool get(const std::string& k, CachedChoice& out) {
+    auto it = map_.find(k);
+    if (it == map_.end()) return false;
+    order_.splice(order_.begin(), order_, it->second);
+    out = it->second->second;
+    return true;
+  }
+  void put(const std::string& k, const CachedChoice& c) {
+    auto it = map_.find(k);
+    if (it != map_.end()) {
+      it->second->second = c;
+      order_.splice(order_.begin(), order_, it->second);
+      return;
+    }
+    order_.emplace_front(k, c);
+    map_[k] = order_.begin();
+    while (map_.size() > cap_) {
+      map_.erase(order_.back().first);
+      order_.pop_back();
+    }
+  }
+  void clear() { map_.clear(); order_.clear(); }
+  size_t size() const { return map_.size(); }
+
+ private:
+  size_t cap_;
+  std::list<std::pair<std::string, CachedChoice>> order_;
+  std::unordered_map<std::string, std::list<std::pair<std::string, CachedChoice>>::iterator> map_;
+};
+
+std::mutex g_mutex;
+std::unordered_map<cuttHandle, std::unique_ptr<Plan>> g_plans;
+cuttHandle g_nextHandle = 0;
+std::unordered_map<int, DeviceInfo> g_devices;
+
+size_t env_size(const char* name, size_t dflt) {
+  const char* v = getenv(name);
+  if (!v || !*v) return dflt;
+  long long x = atoll(v);
+  return x > 0 ? (size_t)x : dflt;
+}
+bool env_flag(const char* name) {
+  const char* v = getenv(name);
+  return v && *v && strcmp(v, "0") != 0;
+}
+
+PlanCache& plan_cache() {
+  static PlanCache cache(env_size("CUTT_PLAN_CACHE_SIZE", 4096));
+  return cache;
+}
+
+bool device_info(int& dev, DeviceInfo& info) {
+  if (cudaGetDevice(&dev) != cudaSuccess) return false;
+  auto it = g_devices.find(dev);
+  if (it != g_devices.end()) { info = it->second; return true; }
+  int v = 0;
+  DeviceInfo d;
+  if (cudaDeviceGetAttribute(&v, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess) return false;
+  d.numSM = v;
+  if (cudaDeviceGetAttribute(&v, cudaDevAttrMaxSharedMemoryPerBlockOptin, dev) != cudaSuccess) return false;
+  d.maxSmemPerBlock = v;
+  if (cudaDeviceGetAttribute(&v, cudaDevAttrMaxSharedMemoryPerMultiprocessor, dev) != cudaSuccess) return false;
+  d.smemPerSM = v;
+  if (cudaDeviceGetAttribute(&v, cudaDevAttrMaxThreadsPerMultiProcessor, dev) != cudaSuccess) return false;
+  d.maxThreadsPerSM = v;
+  g_devices[dev] = d;
+  info = d;
+  return true;
+}
+
+// src/cutt.cpp:59-82
+cuttResult check_input(int rank, const int* dim, const int* perm, size_t elt) {
+  if (elt != 4 && elt != 8) return CUTT_INVALID_PARAMETER;
+  if (rank <= 1) return CUTT_INVALID_PARAMETER;
+  if (!dim || !perm) return CUTT_INVALID_PARAMETER;
+  for (int i = 0; i < rank; i++)
+    if (dim[i] <= 1) return CUTT_INVALID_PARAMETER;
+  std::vector<char> seen(rank, 0);
+  for (int i = 0; i < rank; i++) {
+    if (perm[i] < 0 || perm[i] >= rank || seen[perm[i]]) return CUTT_INVALID_PARAMETER;
+    seen[perm[i]] = 1;
+  }
+  return CUTT_SUCCESS;
+}
+
+std::string problem_key(int dev, int rank, const int* dim, const int* perm, size_t elt) {
+  std::string k = std::to_string(dev) + "/" + std::to_string(elt) + "/";
+  for (int i = 0; i < rank; i++) k += std::to_string(dim[i]) + ",";
+  k += "/";
+  for (int i = 0; i < rank; i++) k += std::to_string(perm[i]) + ",";
+  return k;
+}
+
+void fill_naive(Plan& p, int rank, const int* dim, const int* perm) {
+  NaiveDesc& n = p.naive;
+  memset(&n, 0, sizeof n);
+  n.rank = rank;
+  n.elt = p.elt;
+  unsigned long long is[32], acc = 1;
+  for (int i = 0; i < rank; i++) { is[i] = acc; acc *= (unsigned long long)dim[i]; }
+  n.volume = acc;
+  for (int k = 0; k < rank; k++) { n.odim[k] = dim[perm[k]]; n.istride[k] = is[perm[k]]; }
+}
+
+// Occupancy-based grid for a tiled candidate; false if the kernel cannot be configured.
+bool finalize_tiles(const DeviceInfo& dev, Candidate& c, int& grid) {
+  int nb = tiles_blocks_per_sm(c);
+  if (nb <= 0) return false;
+  c.blocksPerSM = nb;
+  long long g = (long long)dev.numSM * nb;
+  if (g > (long long)c.desc.numTiles) g = c.desc.numTiles;
+  grid = (int)g;
+  c.gridBlocks = grid;
+  return true;
+}
+
+cudaError_t run_plan(const Plan& p, const void* in, void* out, cudaStream_t stream) {
+  switch (p.method) {
+    case kMethodMemcpy:
+      return cudaMemcpyAsync(out, in, p.bytes, cudaMemcpyDeviceToDevice, stream);
+    case kMethodCopy:
+      return launch_copy(in, out, p.bytes, p.numSM, stream);
+    case kMethodNaive:
+      return launch_naive(p.naive, in, out, stream);
+    case kMethodTiles: {
+      PeerPtrs pp;
+      for (int i = 0; i < kMaxPeers; i++) pp.p[i] = (unsigned char*)out;
+      if (tiles_pointers_aligned(p.cand, in, out)) return launch_tiles(p.cand, p.grid, in, pp, stream);
+      if (p.haveFallback) return launch_tiles(p.fallback, p.fallbackGrid, in, pp, stream);
+      return launch_naive(p.naive, in, out, stream);
+    }
+  }
+  return cudaErrorInvalidValue;
+}
+
+// Completes a plan around a chosen candidate (grid sizes, unaligned-pointer fallback).
+bool adopt_candidate(Plan& p, const DeviceInfo& dev, const Candidate& c) {
+  p.method = c.method;
+  p.cand = c;
+  if (c.method != kMethodTiles) return true;
+  if (!finalize_tiles(dev, p.cand, p.grid)) return false;
+  p.haveFallback = false;
+  if (p.cand.desc.in.vec > 1 || p.cand.desc.out.vec > 1) {
+    TileParams tp = c.params;
+    tp.maxVecBytes = p.elt;
+    Candidate f;
+    if (build_tile(p.prob, tp, dev, f) && finalize_tiles(dev, f, p.fallbackGrid)) {
+      p.fallback = f;
+      p.haveFallback = true;
+    }
+  }
+  return true;
+}
+
+enum PlanMode { kByModel, kByMeasure, kByIndex, kByParams };
+
+struct PlanRequest {
+  PlanMode mode = kByModel;
+  void* idata = nullptr;
+  void* odata = nullptr;
+  int index = 0;
+  int method = kMethodTiles;
+  TileParams params;
+};
+
+cuttResult make_plan(cuttHandle* handle, int rank, const int* dim, const int* perm, size_t elt,
+                     cudaStream_t stream, const PlanRequest& req) {
+  cuttResult chk = check_input(rank, dim, perm, elt);
+  if (chk != CUTT_SUCCESS) return chk;
+  if (!handle) return CUTT_INVALID_PARAMETER;
+  if (req.mode == kByMeasure && req.idata == req.odata) return CUTT_INVALID_PARAMETER;
+
+  std::unique_lock<std::mutex> lk(g_mutex);
+  *handle = g_nextHandle++;
+  if (g_plans.count(*handle)) return CUTT_INTERNAL_ERROR;
+
+  int devId = 0;
+  DeviceInfo dev;
+  if (!device_info(devId, dev)) return CUTT_INTERNAL_ERROR;
+
+  std::unique_ptr<Plan> p(new Plan);
+  p->device = devId;
+  p->stream = stream;
+  p->elt = (int)elt;
+  p->numSM = dev.numSM;
+  size_t vol = 1;
+  for (int i = 0; i < rank; i++) vol *= (size_t)dim[i];
+  p->bytes = vol * elt;
+  if (rank <= 32) fill_naive(*p, rank, dim, perm);
+  else return CUTT_INVALID_PARAMETER;
+
+  const bool verbose = env_flag("CUTT_VERBOSE");
+  bool ok = false;
+  const bool canon = problem_from_cutt(rank, dim, perm, (int)elt, p->prob);
+  const std::string key = problem_key(devId, rank, dim, perm, elt);
+
+  if (!canon) {
+    p->method = kMethodNaive;  // fused rank beyond the tiled kernel's limit
+    ok = true;
+  } else if (req.mode == kByParams) {
+    if (req.method == kMethodNaive) { p->method = kMethodNaive; ok = true; }
+    else if (req.method == kMethodCopy || req.method == kMethodMemcpy) {
+      if (!p->prob.identity) return CUTT_INVALID_PARAMETER;
+      p->method = (Method)req.method; ok = true;
+    } else {
+      if (p->prob.identity) return CUTT_INVALID_PARAMETER;
+      Candidate c;
+      if (!build_tile(p->prob, req.params, dev, c)) return CUTT_INVALID_PARAMETER;
+      ok = adopt_candidate(*p, dev, c);
+    }
+  } else {
+    std::vector<Candidate> cands = enumerate_candidates(p->prob, dev);
+    if (cands.empty()) {
+      p->method = kMethodNaive;
+      ok = true;
+    } else if (req.mode == kByIndex) {
+      if (req.index < 0 || req.index >= (int)cands.size()) return CUTT_INVALID_PARAMETER;
+      ok = adopt_candidate(*p, dev, cands[req.index]);
+    } else {
+      CachedChoice cc;
+      bool hit = plan_cache().get(key, cc);
+      if (hit) {
+        if (cc.method == kMethodTiles) {
+          Candidate c;
+          ok = build_tile(p->prob, cc.params, dev, c) && adopt_candidate(*p, dev, c);
+        } else {
+          p->method = cc.method;
+          ok = true;
+        }
+        if (ok) p->note = "cache";
+      }
+      if (!ok && req.mode == kByModel) {
+        for (size_t i = 0; i < cands.size() && !ok; i++) ok = adopt_candidate(*p, dev, cands[i]);
+        if (ok) p->note = "model";
+      }
+      if (!ok && req.mode == kByMeasure) {
+        // Time the most promising candidates on the device (src/cutt.cpp:236-258 times every
+        // candidate once, cold, on stream 0; here: one warm-up and the best of three runs on
+        // the plan's stream, after the same memset + device synchronisation).
+        lk.unlock();
+        const size_t topk = env_size("CUTT_MEASURE_TOPK", 12);
+        cudaEvent_t e0, e1;
+        if (cudaEventCreate(&e0) != cudaSuccess || cudaEventCreate(&e1) != cudaSuccess)
+          return CUTT_INTERNAL_ERROR;
+        if (cudaMemsetAsync(req.odata, 0xFF, p->bytes, stream) != cudaSuccess ||
+            cudaDeviceSynchronize() != cudaSuccess) {
+          cudaEventDestroy(e0); cudaEventDestroy(e1);
+          return CUTT_INTERNAL_ERROR;
+        }
+        double best = 1e30;
+        int bestIdx = -1;
+        Plan trial = *p;
+        for (size_t i = 0; i < cands.size() && i < topk; i++) {
+          if (!adopt_candidate(trial, dev, cands[i])) continue;
+          bool fail = run_plan(trial, req.idata, req.odata, stream) != cudaSuccess;
+          double tmin = 1e30;
+          for (int rep = 0; rep < 3 && !fail; rep++) {
+            cudaEventRecord(e0, stream);
+            fail = run_plan(trial, req.idata, req.odata, stream) != cudaSuccess;
+            cudaEventRecord(e1, stream);
+            if (cudaEventSynchronize(e1) != cudaSuccess) fail = true;
+            float ms = 0.f;
+            if (!fail && cudaEventElapsedTime(&ms, e0, e1) == cudaSuccess && ms < tmin) tmin = ms;
+          }
+          if (fail) { cudaGetLastError(); continue; }
+          if (verbose) fprintf(stderr, "[cutt] measure %2zu %8.4f ms  %s\n", i, tmin, cands[i].label.c_str());
+          if (tmin < best) { best = tmin; bestIdx = (int)i; }
+        }
+        cudaEventDestroy(e0);
+        cudaEventDestroy(e1);
+        lk.lock();
+        if (bestIdx >= 0) {
+          ok = adopt_candidate(*p, dev, cands[bestIdx]);
+          if (ok) {
+            CachedChoice w;
+            w.method = cands[bestIdx].method;
+            w.params = cands[bestIdx].params;
+            plan_cache().put(key, w);
+            p->note = "measured";
+          }
+        }
+      }
+    }
+  }
+  if (!ok) return CUTT_INTERNAL_ERROR;
+  if (verbose) {
+    Candidate shown = p->cand;
+    shown.method = p->method;
+    if (p->method != kMethodTiles) shown.label = p->method == kMethodNaive ? "naive" : (p->method == kMethodCopy ? "copy" : "memcpy");
+    fprintf(stderr, "[cutt] plan %u (%s): %s\n", *handle, p->note.c_str(),
+            canon ? describe(p->prob, shown).c_str() : "naive (rank too high after fusion)");
+  }
+  g_plans[*handle] = std::move(p);
+  return CUTT_SUCCESS;
+}
+
+}  // namespace
+
+// ---------------------------------------------------------------------------------------
+// C++ API (include/cutt.h)
+
+cuttResult cuttPlan(cuttHandle* handle, int rank, int* dim, int* permutation, size_t sizeofType,
+                    cudaStream_t stream) {
+  PlanRequest req;
+  req.mode = kByModel;
+  return make_plan(handle, rank, dim, permutation, sizeofType, stream, req);
+}
+
+cuttResult cuttPlanMeasure(cuttHandle* handle, int rank, int* dim, int* permutation, size_t sizeofType,
+                           cudaStream_t stream, void* idata, void* odata) {
+  PlanRequest req;
+  req.mode = kByMeasure;
+  req.idata = idata;
+  req.odata = odata;
+  return make_plan(handle, rank, dim, permutation, sizeofType, stream, req);
+}
+
+cuttResult cuttDestroy(cuttHandle handle) {
+  std::lock_guard<std::mutex> lk(g_mutex);
+  auto it = g_plans.find(handle);
+  if (it == g_plans.end()) return CUTT_INVALID_PLAN;
+  g_plans.erase(it);
+  return CUTT_SUCCESS;
+}
+
+cuttResult cuttExecute(cuttHandle handle, void* idata, void* odata) {
+  const Plan* p = nullptr;
+  {
+    std::lock_guard<std::mutex> lk(g_mutex);
+    auto it = g_plans.find(handle);
+    if (it == g_plans.end()) return CUTT_INVALID_PLAN;
+    p = it->second.get();
+  }
+  if (idata == odata) return CUTT_INVALID_PARAMETER;
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess) return CUTT_INTERNAL_ERROR;
+  if (dev != p->device) return CUTT_INVALID_DEVICE;
+  return run_plan(*p, idata, odata, p->stream) == cudaSuccess ? CUTT_SUCCESS : CUTT_INTERNAL_ERROR;
+}
+
+// ---------------------------------------------------------------------------------------
+// C ABI (include/cutt_c.h)
+
+extern "C" {
+
+int cutt_c_plan(unsigned int* handle, int rank, const int* dim, const int* permutation,
+                size_t sizeofType, void* stream) {
+  PlanRequest req;
+  return (int)make_plan(handle, rank, dim, permutation, sizeofType, (cudaStream_t)stream, req);
+}
+
+int cutt_c_plan_measure(unsigned int* handle, int rank, const int* dim, const int* permutation,
+                        size_t sizeofType, void* stream, void* idata, void* odata) {
+  PlanRequest req;
+  req.mode = kByMeasure;
+  req.idata = idata;
+  req.odata = odata;
+  return (int)make_plan(handle, rank, dim, permutation, sizeofType, (cudaStream_t)stream, req);
+}
+
+int cutt_c_execute(unsigned int handle, void* idata, void* odata) {
+  return (int)cuttExecute(handle, idata, odata);
+}
+
+int cutt_c_destroy(unsigned int handle) { return (int)cuttDestroy(handle); }
+
+int cutt_c_plan_describe(unsigned int handle, char* buf, size_t len) {
+  std::lock_guard<std::mutex> lk(g_mutex);
+  auto it = g_plans.find(handle);
+  if (it == g_plans.end()) return CUTT_INVALID_PLAN;
+  if (!buf || !len) return CUTT_INVALID_PARAMETER;
+  const Plan& p = *it->second;
+  Candidate shown = p.cand;
+  shown.method = p.method;
+  if (p.method == kMethodNaive) shown.label = "naive";
+  else if (p.method == kMethodCopy) shown.label = "copy";
+  else if (p.method == kMethodMemcpy) shown.label = "memcpy";
+  snprintf(buf, len, "%s", describe(p.prob, shown).c_str());
+  return CUTT_SUCCESS;
+}
+
+int cutt_c_num_candidates(int rank, const int* dim, const int* permutation, size_t sizeofType) {
+  if (check_input(rank, dim, permutation, sizeofType) != CUTT_SUCCESS) return 0;
+  std::lock_guard<std::mutex> lk(g_mutex);
+  int devId;
+  DeviceInfo dev;
+  if (!device_info(devId, dev)) return 0;
+  Problem P;
+  if (!problem_from_cutt(rank, dim, permutation, (int)sizeofType, P)) return 0;
+  return (int)enumerate_candidates(P, dev).size();
+}
+
+int cutt_c_plan_candidate(unsigned int* handle, int rank, const int* dim, const int* permutation,
+                          size_t sizeofType, void* stream, int index) {
+  PlanRequest req;
+  req.mode = kByIndex;
+  req.index = index;
+  return (int)make_plan(handle, rank, dim, permutation, sizeofType, (cudaStream_t)stream, req);
+}
+
+int cutt_c_plan_params(unsigned int* handle, int rank, const int* dim, const int* permutation,
+                       size_t sizeofType, void* stream, int method, unsigned tinBytes,
+                       unsigned toutBytes, unsigned vtargetBytes, int extend, int loopOrder,
+                       int maxVecBytes, int nthreads, int stages) {
+  PlanRequest req;
+  req.mode = kByParams;
+  req.method = method;
+  req.params.tinBytes = tinBytes;
+  req.params.toutBytes = toutBytes;
+  req.params.vtargetBytes = vtargetBytes;
+  req.params.extend = extend;
+  req.params.loopOrder = loopOrder;
+  req.params.maxVecBytes = maxVecBytes;
+  if (nthreads != 64 && nthreads != 128 && nthreads != 256 && nthreads != 512) return CUTT_INVALID_PARAMETER;
+  if (stages != 1 && stages != 2) return CUTT_INVALID_PARAMETER;
+  req.params.nthreads = nthreads;
+  req.params.stages = stages;
+  return (int)make_plan(handle, rank, dim, permutation, sizeofType, (cudaStream_t)stream, req);
+}
+
+int cutt_c_transpose_host(int rank, const int* dim, const int* permutation, size_t sizeofType,
+                          const void* hin, void* hout) {
+  // device scratch, grown on demand and kept (one pair per process; serialised)
+  static std::mutex hostMutex;
+  static void* dIn = nullptr;
+  static void* dOut = nullptr;
+  static size_t cap = 0;
+  static int capDev = -1;
+  static std::unordered_map<std::string, cuttHandle> plans;
+  if (check_input(rank, dim, permutation, sizeofType) != CUTT_SUCCESS) return CUTT_INVALID_PARAMETER;
+  if (!hin || !hout) return CUTT_INVALID_PARAMETER;
+  std::lock_guard<std::mutex> lk(hostMutex);
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess) return CUTT_INTERNAL_ERROR;
+  size_t bytes = sizeofType;
+  for (int i = 0; i < rank; i++) bytes *= (size_t)dim[i];
+  if (bytes > cap || dev != capDev) {
+    if (dIn) cudaFree(dIn);
+    if (dOut) cudaFree(dOut);
+    dIn = dOut = nullptr;
+    cap = 0;
+    if (cudaMalloc(&dIn, bytes) != cudaSuccess || cudaMalloc(&dOut, bytes) != cudaSuccess) {
+      if (dIn) cudaFree(dIn);
+      dIn = dOut = nullptr;
+      cudaGetLastError();
+      return CUTT_INTERNAL_ERROR;
+    }
+    cap = bytes;
+    capDev = dev;
+  }
+  std::string key = problem_key(dev, rank, dim, permutation, sizeofType);
+  cuttHandle h;
+  auto it = plans.find(key);
+  if (it == plans.end()) {
+    PlanRequest req;
+    cuttResult r = make_plan(&h, rank, dim, permutation, sizeofType, 0, req);
+    if (r != CUTT_SUCCESS) return r;
+    plans[key] = h;
+  } else {
+    h = it->second;
+  }
+  if (cudaMemcpyAsync(dIn, hin, bytes, cudaMemcpyHostToDevice, 0) != cudaSuccess) return CUTT_INTERNAL_ERROR;
+  cuttResult r = cuttExecute(h, dIn, dOut);
+  if (r != CUTT_SUCCESS) return r;
+  if (cudaMemcpyAsync(hout, dOut, bytes, cudaMemcpyDeviceToHost, 0) != cudaSuccess) return CUTT_INTERNAL_ERROR;
+  if (cudaStreamSynchronize(0) != cudaSuccess) return CUTT_INTERNAL_ERROR;
+  return CUTT_SUCCESS;
+}
+
+unsigned long long cutt_c_launch_count(void) { return launch_count(); }
+
+void cutt_c_clear_plan_cache(void) {
+  std::lock_guard<std::mutex> lk(g_mutex);
+  plan_cache().clear();
+}
+
+const char* cutt_c_version(void) { return "cutt-b200 0.1 (sm_100a)"; }
+
+}  // extern "C"

@@ -1,0 +1,95 @@
+// Host-side plan interpreter.  TEST ONLY: built into its own shared library
+// (libcutt_hostcheck.so), never linked into libcutt.  It executes a tile descriptor on
+// host arrays by calling, for every block, tile and thread index in turn, the very same
+// per-thread phase functions the CUDA kernel calls, so the planner and the index
+// arithmetic are checked against the CPU oracle without a GPU.
+#include <cstdio>
+#include <cstring>
+#include <vector>
+#include "permute_tile_impl.h"
+#include "planner.h"
+
+using namespace cuttb;
+
+template <int ELT, int WIN, int WOUT>
+static void run_desc(const TileDesc& D, const unsigned char* in, unsigned char* out) {
+  std::vector<RowEnt> tabIn(D.in.nrows), tabOut(D.out.nrows);
+  for (uint32_t r = 0; r < D.in.nrows; r++) tabIn[r] = make_row(D.in, r);
+  for (uint32_t r = 0; r < D.out.nrows; r++) tabOut[r] = make_row(D.out, r);
+  std::vector<unsigned char> sbuf(D.stageBytes);
+  for (uint32_t tile = 0; tile < D.numTiles; tile++) {
+    TileCtx c;
+    decode_tile(D, tile, c);
+    memset(sbuf.data(), 0xEE, sbuf.size());
+    for (uint32_t tid = 0; tid < D.nthreads; tid++)
+      tile_load<ELT, WIN>(D, c, tabIn.data(), sbuf.data(), in, tid);
+    for (uint32_t tid = 0; tid < D.nthreads; tid++)
+      tile_store<ELT, WOUT>(D, c, tabOut.data(), sbuf.data(), out, tid);
+  }
+}
+
+static int dispatch(const TileDesc& D, const unsigned char* in, unsigned char* out) {
+#define CASE(E, A, B) if (D.elt == E && D.in.vec == A && D.out.vec == B) { run_desc<E, A, B>(D, in, out); return 0; }
+  CASE(4, 1, 1) CASE(4, 1, 2) CASE(4, 1, 4) CASE(4, 2, 1) CASE(4, 2, 2) CASE(4, 2, 4)
+  CASE(4, 4, 1) CASE(4, 4, 2) CASE(4, 4, 4)
+  CASE(8, 1, 1) CASE(8, 1, 2) CASE(8, 2, 1) CASE(8, 2, 2)
+#undef CASE
+  return 4;
+}
+
+static DeviceInfo g_dev;
+
+extern "C" {
+
+// Number of candidates the planner enumerates for a cuTT-style problem (0 on invalid input).
+int cutt_hostcheck_num_candidates(int rank, const int* dim, const int* perm, int elt) {
+  Problem P;
+  if (!problem_from_cutt(rank, dim, perm, elt, P)) return 0;
+  return (int)enumerate_candidates(P, g_dev).size();
+}
+
+// Executes candidate `index` on host memory.  Returns 0 on success; `label` receives the
+// JSON description of the candidate.  Copy candidates are executed as a memcpy.
+int cutt_hostcheck_run(int rank, const int* dim, const int* perm, int elt, int index,
+                       const void* in, void* out, char* label, int labelLen) {
+  Problem P;
+  if (!problem_from_cutt(rank, dim, perm, elt, P)) return 2;
+  std::vector<Candidate> cands = enumerate_candidates(P, g_dev);
+  if (index < 0 || index >= (int)cands.size()) return 3;
+  const Candidate& c = cands[index];
+  if (label && labelLen > 0) snprintf(label, labelLen, "%s", describe(P, c).c_str());
+  if (c.method == kMethodCopy || c.method == kMethodMemcpy) {
+    memcpy(out, in, (size_t)P.volume * elt);
+    return 0;
+  }
+  return dispatch(c.desc, (const unsigned char*)in, (unsigned char*)out);
+}
+
+// Same, for an explicit parameter choice (used to force odd tile shapes in tests).
+int cutt_hostcheck_run_params(int rank, const int* dim, const int* perm, int elt,
+                              unsigned tinBytes, unsigned toutBytes, unsigned vtargetBytes,
+                              int extend, int loopOrder, int maxVecBytes, int nthreads,
+                              const void* in, void* out, char* label, int labelLen) {
+  Problem P;
+  if (!problem_from_cutt(rank, dim, perm, elt, P)) return 2;
+  if (P.identity) { memcpy(out, in, (size_t)P.volume * elt); return 0; }
+  TileParams tp;
+  tp.tinBytes = tinBytes; tp.toutBytes = toutBytes; tp.vtargetBytes = vtargetBytes;
+  tp.extend = extend; tp.loopOrder = loopOrder; tp.maxVecBytes = maxVecBytes; tp.nthreads = nthreads;
+  Candidate c;
+  if (!build_tile(P, tp, g_dev, c)) return 5;
+  if (label && labelLen > 0) snprintf(label, labelLen, "%s", describe(P, c).c_str());
+  return dispatch(c.desc, (const unsigned char*)in, (unsigned char*)out);
+}
+
+// Exhaustive-ish self check of the division helper: returns the number of mismatches.
+long long cutt_hostcheck_fastdiv(unsigned d, unsigned long long nmax, unsigned long long step) {
+  FastDiv f = make_fastdiv(d);
+  long long bad = 0;
+  for (unsigned long long n = 0; n <= nmax; n += step) if (fdiv((uint32_t)n, f) != (uint32_t)n / d) bad++;
+  const uint32_t edge[] = {0u, 1u, d - 1, d, d + 1, 0x7fffffffu, 0x80000000u, 0xfffffffeu, 0xffffffffu};
+  for (uint32_t n : edge) if (fdiv(n, f) != n / d) bad++;
+  return bad;
+}
+
+}  // extern "C"

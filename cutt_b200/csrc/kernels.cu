@@ -1,0 +1,215 @@
+// sm_100a kernels of the permutation path.
+//
+//  permute_tiles_kernel  the general kernel: a persistent grid walks the tile space; each
+//                        tile is staged global -> shared with cp.async (4/8/16-byte, two
+//                        stages so the next tile's loads overlap this tile's stores) and
+//                        written back as contiguous runs of the output.  It covers what the
+//                        reference does with four kernels (Tiled, TiledCopy, Packed,
+//                        PackedSplit; src/cuttkernel.cu:38-426).
+//  copy_kernel           identity permutations (the reference's Trivial method,
+//                        src/cuttkernel.cu:846-851, uses cudaMemcpyAsync).
+//  naive_kernel          one thread per output element, any rank; fallback and cross-check.
+#include "kernels.h"
+#include <atomic>
+#include <mutex>
+#include <map>
+#include <tuple>
+#include "permute_tile_impl.h"
+
+namespace cuttb {
+
+static std::atomic<unsigned long long> g_launches{0};
+unsigned long long launch_count() { return g_launches.load(); }
+
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;\n" ::: "memory"); }
+template <int N>
+__device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;\n" ::"n"(N) : "memory"); }
+
+template <int ELT, int WIN, int WOUT>
+__global__ void __launch_bounds__(512)
+permute_tiles_kernel(const __grid_constant__ TileDesc D, const unsigned char* __restrict__ in,
+                     const __grid_constant__ PeerPtrs outs) {
+  extern __shared__ __align__(16) unsigned char smem[];
+  RowEnt* tabIn = reinterpret_cast<RowEnt*>(smem);
+  RowEnt* tabOut = tabIn + D.in.nrows;
+  unsigned char* stage0 = smem + D.tableBytes;
+  const uint32_t tid = threadIdx.x;
+
+  for (uint32_t r = tid; r < D.in.nrows; r += blockDim.x) tabIn[r] = make_row(D.in, r);
+  for (uint32_t r = tid; r < D.out.nrows; r += blockDim.x) tabOut[r] = make_row(D.out, r);
+  __syncthreads();
+
+  uint32_t tile = blockIdx.x;
+  if (tile >= D.numTiles) return;
+  TileCtx cur, nxt;
+  decode_tile(D, tile, cur);
+  nxt = cur;
+
+  if (D.stages >= 2) {
+    tile_load<ELT, WIN>(D, cur, tabIn, stage0, in, tid);
+    cp_async_commit();
+    uint32_t s = 0;
+    for (; tile < D.numTiles; tile += gridDim.x) {
+      const uint32_t tn = tile + gridDim.x;
+      if (tn < D.numTiles) {
+        decode_tile(D, tn, nxt);
+        tile_load<ELT, WIN>(D, nxt, tabIn, stage0 + (s ^ 1u) * D.stageBytes, in, tid);
+      }
+      cp_async_commit();
+      cp_async_wait<1>();
+      __syncthreads();
+      unsigned char* o = D.peerLoopDim >= 0 ? outs.p[cur.peer] : outs.p[0];
+      tile_store<ELT, WOUT>(D, cur, tabOut, stage0 + s * D.stageBytes, o, tid);
+      __syncthreads();
+      cur = nxt;
+      s ^= 1u;
+    }
+  } else {
+    for (; tile < D.numTiles; tile += gridDim.x) {
+      decode_tile(D, tile, cur);
+      tile_load<ELT, WIN>(D, cur, tabIn, stage0, in, tid);
+      cp_async_commit();
+      cp_async_wait<0>();
+      __syncthreads();
+      unsigned char* o = D.peerLoopDim >= 0 ? outs.p[cur.peer] : outs.p[0];
+      tile_store<ELT, WOUT>(D, cur, tabOut, stage0, o, tid);
+      __syncthreads();
+    }
+  }
+}
+
+typedef void (*TilesKernel)(const TileDesc, const unsigned char*, const PeerPtrs);
+
+static TilesKernel pick_tiles_kernel(int elt, int win, int wout) {
+#define CASE(E, A, B) if (elt == E && win == A && wout == B) return permute_tiles_kernel<E, A, B>;
+  CASE(4, 1, 1) CASE(4, 1, 2) CASE(4, 1, 4) CASE(4, 2, 1) CASE(4, 2, 2) CASE(4, 2, 4)
+  CASE(4, 4, 1) CASE(4, 4, 2) CASE(4, 4, 4)
+  CASE(8, 1, 1) CASE(8, 1, 2) CASE(8, 2, 1) CASE(8, 2, 2)
+#undef CASE
+  return nullptr;
+}
+
+// Largest dynamic shared-memory size configured so far per (device, kernel).
+static std::mutex g_attrMutex;
+static std::map<std::pair<int, const void*>, int> g_smemAttr;
+
+static cudaError_t ensure_smem(TilesKernel k, int bytes) {
+  int dev = 0;
+  cudaError_t e = cudaGetDevice(&dev);
+  if (e != cudaSuccess) return e;
+  std::lock_guard<std::mutex> lk(g_attrMutex);
+  auto key = std::make_pair(dev, (const void*)k);
+  auto it = g_smemAttr.find(key);
+  if (it != g_smemAttr.end() && it->second >= bytes) return cudaSuccess;
+  // raise to the device maximum once: later plans never need to touch the attribute again
+  int maxOptin = 0;
+  e = cudaDeviceGetAttribute(&maxOptin, cudaDevAttrMaxSharedMemoryPerBlockOptin, dev);
+  if (e != cudaSuccess) return e;
+  if (bytes > maxOptin) return cudaErrorInvalidValue;
+  e = cudaFuncSetAttribute((const void*)k, cudaFuncAttributeMaxDynamicSharedMemorySize, maxOptin);
+  if (e != cudaSuccess) return e;
+  g_smemAttr[key] = maxOptin;
+  return cudaSuccess;
+}
+
+int tiles_blocks_per_sm(const Candidate& c) {
+  const TileDesc& D = c.desc;
+  TilesKernel k = pick_tiles_kernel(D.elt, D.in.vec, D.out.vec);
+  if (!k) return -1;
+  if (ensure_smem(k, c.smemBytes) != cudaSuccess) return -1;
+  int nb = 0;
+  if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&nb, (const void*)k, (int)D.nthreads,
+                                                    (size_t)c.smemBytes) != cudaSuccess)
+    return -1;
+  return nb;
+}
+
+bool tiles_pointers_aligned(const Candidate& c, const void* in, const void* out) {
+  const TileDesc& D = c.desc;
+  return ((uintptr_t)in % (D.in.vec * D.elt) == 0) && ((uintptr_t)out % (D.out.vec * D.elt) == 0);
+}
+
+cudaError_t launch_tiles(const Candidate& c, int gridBlocks, const void* in, const PeerPtrs& outs,
+                         cudaStream_t stream) {
+  const TileDesc& D = c.desc;
+  TilesKernel k = pick_tiles_kernel(D.elt, D.in.vec, D.out.vec);
+  if (!k) return cudaErrorInvalidValue;
+  cudaError_t e = ensure_smem(k, c.smemBytes);
+  if (e != cudaSuccess) return e;
+  k<<<gridBlocks, D.nthreads, c.smemBytes, stream>>>(D, (const unsigned char*)in, outs);
+  g_launches++;
+  return cudaGetLastError();
+}
+
+// ---------------------------------------------------------------------------------------
+// contiguous copy
+template <typename V, int UNROLL>
+__global__ void __launch_bounds__(256)
+copy_kernel(const V* __restrict__ in, V* __restrict__ out, size_t n) {
+  const size_t stride = (size_t)gridDim.x * blockDim.x;
+  size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+  // full groups of UNROLL accesses per thread keep several loads in flight
+  for (; i + (UNROLL - 1) * stride < n; i += UNROLL * stride) {
+    V v[UNROLL];
+#pragma unroll
+    for (int u = 0; u < UNROLL; u++) v[u] = __ldcs(in + i + u * stride);
+#pragma unroll
+    for (int u = 0; u < UNROLL; u++) __stcs(out + i + u * stride, v[u]);
+  }
+  for (; i < n; i += stride) out[i] = in[i];
+}
+
+cudaError_t launch_copy(const void* in, void* out, size_t bytes, int numSM, cudaStream_t stream) {
+  if (bytes == 0) return cudaSuccess;
+  const int threads = 256;
+  const bool al16 = ((uintptr_t)in % 16 == 0) && ((uintptr_t)out % 16 == 0);
+  size_t body = al16 ? bytes / 16 : 0;  // 16-byte words
+  if (body) {
+    size_t want = (body + threads * 4 - 1) / (threads * 4);
+    int grid = (int)(want < (size_t)numSM * 8 ? want : (size_t)numSM * 8);
+    copy_kernel<uint4, 4><<<grid, threads, 0, stream>>>((const uint4*)in, (uint4*)out, body);
+    g_launches++;
+  }
+  size_t done = body * 16;
+  if (done < bytes) {  // tail (or everything, for pointers that are only 4-byte aligned)
+    size_t words = (bytes - done) / 4;
+    size_t want = (words + threads * 4 - 1) / (threads * 4);
+    int grid = (int)(want < (size_t)numSM * 8 ? want : (size_t)numSM * 8);
+    if (grid < 1) grid = 1;
+    copy_kernel<uint32_t, 4><<<grid, threads, 0, stream>>>(
+        (const uint32_t*)((const unsigned char*)in + done), (uint32_t*)((unsigned char*)out + done), words);
+    g_launches++;
+  }
+  return cudaGetLastError();
+}
+
+// ---------------------------------------------------------------------------------------
+// one thread per output element
+template <typename T>
+__global__ void __launch_bounds__(256)
+naive_kernel(const __grid_constant__ NaiveDesc d, const T* __restrict__ in, T* __restrict__ out) {
+  const unsigned long long stride = (unsigned long long)gridDim.x * blockDim.x;
+  for (unsigned long long o = (unsigned long long)blockIdx.x * blockDim.x + threadIdx.x; o < d.volume;
+       o += stride) {
+    unsigned long long rem = o, src = 0;
+    for (int k = 0; k < d.rank; k++) {
+      unsigned long long q = rem / d.odim[k];
+      src += (rem - q * d.odim[k]) * d.istride[k];
+      rem = q;
+    }
+    out[o] = in[src];
+  }
+}
+
+cudaError_t launch_naive(const NaiveDesc& d, const void* in, void* out, cudaStream_t stream) {
+  const int threads = 256;
+  unsigned long long want = (d.volume + threads - 1) / threads;
+  int grid = (int)(want < 148ull * 16 ? want : 148ull * 16);
+  if (grid < 1) grid = 1;
+  if (d.elt == 4) naive_kernel<uint32_t><<<grid, threads, 0, stream>>>(d, (const uint32_t*)in, (uint32_t*)out);
+  else naive_kernel<unsigned long long><<<grid, threads, 0, stream>>>(d, (const unsigned long long*)in, (unsigned long long*)out);
+  g_launches++;
+  return cudaGetLastError();
+}
+
+}  // namespace cuttb

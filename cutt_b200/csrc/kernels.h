@@ -1,0 +1,37 @@
+// Launch interface of the sm_100a permutation kernels (kernels.cu).
+#pragma once
+#include <cuda_runtime.h>
+#include <stddef.h>
+#include "planner.h"
+
+namespace cuttb {
+
+struct PeerPtrs {
+  unsigned char* p[kMaxPeers];
+};
+
+// One thread per output element; any rank up to 32.  Fallback and cross-check.
+struct NaiveDesc {
+  int rank;
+  int elt;
+  unsigned long long volume;
+  unsigned long long odim[32];     // extents in output order
+  unsigned long long istride[32];  // input stride of the k-th output dimension
+};
+
+// Resident blocks per SM of the tiled kernel for this candidate (also raises the kernel's
+// dynamic shared-memory limit).  <= 0 on error.
+int tiles_blocks_per_sm(const Candidate& c);
+
+// Effective vector widths the kernel can use with these pointers (elements).
+bool tiles_pointers_aligned(const Candidate& c, const void* in, const void* out);
+
+cudaError_t launch_tiles(const Candidate& c, int gridBlocks, const void* in, const PeerPtrs& outs,
+                         cudaStream_t stream);
+cudaError_t launch_copy(const void* in, void* out, size_t bytes, int numSM, cudaStream_t stream);
+cudaError_t launch_naive(const NaiveDesc& d, const void* in, void* out, cudaStream_t stream);
+
+// Number of kernel launches issued by this library since load (for benchmarks' accounting).
+unsigned long long launch_count();
+
+}  // namespace cuttb

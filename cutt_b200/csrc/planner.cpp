@@ -1,0 +1,438 @@
+// Plan builder (host only).  See planner.h.
+#include "planner.h"
+#include <algorithm>
+#include <cmath>
+#include <cstdio>
+#include <cstring>
+#include <set>
+
+namespace cuttb {
+
+static inline int64_t ceil_div(int64_t a, int64_t b) { return (a + b - 1) / b; }
+
+bool canonicalize(int rank, const int64_t* d, const int64_t* is, const int64_t* os, int elt,
+                  int peerDim, Problem& P) {
+  struct Dim { int64_t d, is, os; bool peer; };
+  std::vector<Dim> v;
+  int64_t vol = 1;
+  for (int i = 0; i < rank; i++) {
+    vol *= d[i];
+    if (d[i] == 1 && i != peerDim) continue;
+    v.push_back({d[i], is[i], os[i], i == peerDim});
+  }
+  std::stable_sort(v.begin(), v.end(), [](const Dim& a, const Dim& b) { return a.is < b.is; });
+  // fuse neighbours that are contiguous on both sides (the rule of reduceRanks,
+  // src/cuttplan.cpp:63-126, stated on strides)
+  std::vector<Dim> f;
+  for (const Dim& x : v) {
+    if (!f.empty()) {
+      Dim& b = f.back();
+      if (!b.peer && !x.peer && x.is == b.is * b.d && x.os == b.os * b.d) {
+        b.d *= x.d;
+        continue;
+      }
+    }
+    f.push_back(x);
+  }
+  if (f.empty()) f.push_back({1, 1, 1, false});
+  if ((int)f.size() > kMaxDims) return false;
+  P = Problem();
+  P.rank = (int)f.size();
+  P.elt = elt;
+  P.volume = vol;
+  P.peerDim = -1;
+  for (int i = 0; i < P.rank; i++) {
+    P.d[i] = f[i].d;
+    P.is[i] = f[i].is;
+    P.os[i] = f[i].os;
+    if (f[i].peer) P.peerDim = i;
+  }
+  P.identity = (P.rank == 1 && P.is[0] == 1 && P.os[0] == 1 && P.peerDim < 0);
+  return true;
+}
+
+bool problem_from_cutt(int rank, const int* dim, const int* perm, int elt, Problem& P) {
+  std::vector<int64_t> d(rank), is(rank), os(rank);
+  int64_t acc = 1;
+  for (int i = 0; i < rank; i++) { d[i] = dim[i]; is[i] = acc; acc *= dim[i]; }
+  acc = 1;
+  for (int k = 0; k < rank; k++) { os[perm[k]] = acc; acc *= dim[perm[k]]; }
+  return canonicalize(rank, d.data(), is.data(), os.data(), elt, -1, P);
+}
+
+// chunk of about `want` elements out of d, with equal-sized chunks except possibly the last
+static int64_t balanced_chunk(int64_t d, int64_t want) {
+  if (want >= d) return d;
+  if (want < 1) want = 1;
+  int64_t n = ceil_div(d, want);
+  return ceil_div(d, n);
+}
+
+static uint32_t ilog2_exact(uint32_t x) { uint32_t l = 0; while ((1u << l) < x) l++; return l; }
+
+// thread split of a side: tq threads along the run, nthreads/tq along the rows,
+// minimising the number of loop trips of the busiest thread.
+static void choose_thread_split(Side& S, uint32_t nthreads) {
+  uint32_t vpr = (uint32_t)ceil_div(S.run, S.vec);
+  uint64_t best = ~0ull;
+  uint32_t bestTq = 1;
+  for (uint32_t tq = 1; tq <= nthreads; tq *= 2) {
+    uint32_t tr = nthreads / tq;
+    uint64_t trips = (uint64_t)ceil_div(S.nrows, tr) * (uint64_t)ceil_div(vpr, tq);
+    // prefer wider tq on ties: neighbouring lanes then touch neighbouring addresses
+    if (trips < best || (trips == best && tq <= 32)) { best = trips; bestTq = tq; }
+  }
+  S.tq = bestTq;
+  S.tqShift = ilog2_exact(bestTq);
+}
+
+bool build_tile(const Problem& P, const TileParams& tp, const DeviceInfo& dev, Candidate& out) {
+  const int r = P.rank;
+  const int elt = P.elt;
+  if (r < 1 || r > kMaxDims) return false;
+  int64_t t[kMaxDims];
+  for (int j = 0; j < r; j++) t[j] = 1;
+
+  // output order
+  int oo[kMaxDims];
+  for (int j = 0; j < r; j++) oo[j] = j;
+  std::stable_sort(oo, oo + r, [&](int a, int b) { return P.os[a] < P.os[b]; });
+
+  const int64_t tin = std::max<int64_t>(1, tp.tinBytes / elt);
+  const int64_t tout = std::max<int64_t>(1, tp.toutBytes / elt);
+  const int64_t vtarget = std::max<int64_t>(1, tp.vtargetBytes / elt);
+  const int64_t kMaxChunk = 32768;
+
+  // 1. input run: leading dimensions in input order
+  {
+    int64_t cum = 1, expect = 1;
+    for (int j = 0; j < r; j++) {
+      if (P.is[j] != expect || j == P.peerDim || cum >= tin) break;
+      int64_t want = ceil_div(tin, cum);
+      if (P.d[j] <= want + want / 2 && P.d[j] <= kMaxChunk) {
+        t[j] = P.d[j]; cum *= P.d[j]; expect *= P.d[j];
+      } else {
+        t[j] = balanced_chunk(P.d[j], std::min(want, kMaxChunk));
+        break;
+      }
+    }
+  }
+  // 2. output run: leading dimensions in output order
+  {
+    int64_t cum = 1, expect = 1;
+    for (int k = 0; k < r; k++) {
+      int j = oo[k];
+      if (P.os[j] != expect || j == P.peerDim) break;
+      if (t[j] == P.d[j]) { cum *= P.d[j]; expect *= P.d[j]; continue; }
+      if (t[j] > 1) break;  // already chunked by the input run: the output run ends here
+      if (cum >= tout) break;
+      int64_t want = ceil_div(tout, cum);
+      if (P.d[j] <= want + want / 2 && P.d[j] <= kMaxChunk) {
+        t[j] = P.d[j]; cum *= P.d[j]; expect *= P.d[j];
+      } else {
+        t[j] = balanced_chunk(P.d[j], std::min(want, kMaxChunk));
+        break;
+      }
+    }
+  }
+  // 3. grow the tile towards the target volume
+  auto volume = [&]() { int64_t v = 1; for (int j = 0; j < r; j++) v *= t[j]; return v; };
+  auto num_chunked = [&]() { int n = 0; for (int j = 0; j < r; j++) if (t[j] > 1 && t[j] < P.d[j]) n++; return n; };
+  for (int guard = 0; guard < 2 * kMaxDims; guard++) {
+    int64_t V = volume();
+    if (V >= vtarget) break;
+    int pick = -1;
+    // prefer enlarging a dimension that is already chunked? No: a new row dimension keeps
+    // both runs at their target; take the first non-full dimension in the chosen order.
+    for (int k = 0; k < r && pick < 0; k++) {
+      int j = tp.extend == 0 ? oo[k] : k;
+      if (j == P.peerDim) continue;
+      if (t[j] < P.d[j]) {
+        if (t[j] == 1 && num_chunked() >= 2) continue;  // would create a third chunked dimension
+        pick = j;
+      }
+    }
+    if (pick < 0) break;
+    int64_t want = ceil_div(vtarget * t[pick], V);
+    int64_t nt = balanced_chunk(P.d[pick], std::min(want, kMaxChunk));
+    if (nt <= t[pick]) break;
+    t[pick] = nt;
+    if (nt < P.d[pick]) break;  // chunked: the target is met (or the chunk limit was hit)
+  }
+  if (num_chunked() > 2) return false;
+
+  // 4. derive descriptor
+  TileDesc& D = out.desc;
+  memset(&D, 0, sizeof(D));
+  D.elt = elt;
+  D.nthreads = tp.nthreads;
+  D.stages = tp.stages;
+  D.peerLoopDim = -1;
+  D.inBase = P.inBase;
+  D.outBase = P.outBase;
+
+  // partial slots
+  int slotOf[kMaxDims];
+  int nslots = 0;
+  for (int j = 0; j < r; j++) {
+    slotOf[j] = -1;
+    if (t[j] > 1 && t[j] < P.d[j] && P.d[j] % t[j] != 0) {
+      if (nslots == 2) return false;
+      slotOf[j] = nslots++;
+    }
+  }
+
+  // run membership
+  bool inRun[kMaxDims] = {false}, outRun[kMaxDims] = {false};
+  int inRunLast = -1, outRunLast = -1;
+  {
+    int64_t expect = 1;
+    for (int j = 0; j < r; j++) {
+      if (P.is[j] != expect || t[j] == 1 || j == P.peerDim) break;
+      inRun[j] = true; inRunLast = j;
+      if (t[j] < P.d[j]) break;
+      expect *= P.d[j];
+    }
+  }
+  int outRunOrder[kMaxDims], nOutRun = 0;
+  {
+    int64_t expect = 1;
+    for (int k = 0; k < r; k++) {
+      int j = oo[k];
+      if (P.os[j] != expect || t[j] == 1 || j == P.peerDim) break;
+      outRun[j] = true; outRunLast = j; outRunOrder[nOutRun++] = j;
+      if (t[j] < P.d[j]) break;
+      expect *= P.d[j];
+    }
+  }
+
+  // vector widths (elements per access)
+  auto side_vec = [&](bool input) -> uint32_t {
+    const bool* inrun = input ? inRun : outRun;
+    int last = input ? inRunLast : outRunLast;
+    for (int W = std::min(16, tp.maxVecBytes) / elt; W > 1; W /= 2) {
+      bool ok = true;
+      if (last < 0) { ok = false; }
+      else {
+        int64_t prefix = 1;
+        for (int j = 0; j < r; j++) if (inrun[j] && j != last) prefix *= t[j];
+        // every valid run length must be a multiple of W
+        if (prefix % W != 0) {
+          if (t[last] % W != 0) ok = false;
+          if (t[last] < P.d[last] && P.d[last] % W != 0) ok = false;
+        }
+      }
+      for (int j = 0; j < r && ok; j++) {
+        int64_t gs = input ? P.is[j] : P.os[j];
+        if (inrun[j]) {
+          // chunk steps along the run's last dimension
+          if (j == last && t[j] < P.d[j] && (gs * t[j]) % W != 0) ok = false;
+          continue;
+        }
+        if (P.d[j] > 1 && gs % W != 0 && !(j == P.peerDim && !input)) ok = false;
+      }
+      if ((input ? P.inBase : P.outBase) % W != 0) ok = false;
+      if (ok) return (uint32_t)W;
+    }
+    return 1;
+  };
+  const uint32_t win = side_vec(true);
+  const uint32_t wout = side_vec(false);
+
+  // shared-memory strides: input order, padded where the output run starts
+  int64_t ss[kMaxDims];
+  {
+    int p0 = nOutRun > 0 ? outRunOrder[0] : -1;
+    int64_t s = 1;
+    for (int j = 0; j < r; j++) {
+      if (t[j] == 1) { ss[j] = 0; continue; }
+      if (!inRun[j]) {
+        // rows start on a multiple of the input vector width
+        s = ceil_div(s, (int64_t)win) * win;
+        if (j == p0) { while (((s / win) & 1) == 0) s += win; }
+      }
+      ss[j] = s;
+      s *= t[j];
+    }
+    int64_t elems = 1;
+    for (int j = 0; j < r; j++) if (t[j] > 1) elems += (t[j] - 1) * ss[j];
+    if (elems > (int64_t)dev.maxSmemPerBlock / elt) return false;
+    D.tileElems = (uint32_t)elems;
+    D.stageBytes = (uint32_t)((elems * elt + 15) / 16 * 16);
+  }
+
+  // sides
+  auto fill_side = [&](Side& S, bool input) -> bool {
+    const bool* inrun = input ? inRun : outRun;
+    int last = input ? inRunLast : outRunLast;
+    int64_t run = 1, prefix = 1;
+    for (int j = 0; j < r; j++) if (inrun[j]) { run *= t[j]; if (j != last) prefix *= t[j]; }
+    S.run = (uint32_t)run;
+    S.runPrefix = (uint32_t)prefix;
+    S.runSlot = last >= 0 ? slotOf[last] : -1;
+    S.vec = input ? win : wout;
+    S.nRowDims = 0;
+    int64_t nrows = 1;
+    for (int j = 0; j < r; j++) {
+      if (t[j] == 1 || inrun[j]) continue;
+      RowDim& R = S.rowDim[S.nRowDims++];
+      R.ext = (uint32_t)t[j];
+      R.sstride = (uint32_t)ss[j];
+      R.gstride = input ? P.is[j] : P.os[j];
+      R.slot = slotOf[j];
+      nrows *= t[j];
+    }
+    if (nrows > 8192) return false;
+    S.nrows = (uint32_t)nrows;
+    choose_thread_split(S, tp.nthreads);
+    return true;
+  };
+  if (!fill_side(D.in, true)) return false;
+  if (!fill_side(D.out, false)) return false;
+  D.tableBytes = (D.in.nrows + D.out.nrows) * (uint32_t)sizeof(RowEnt);
+  if (D.tableBytes > 48 * 1024) return false;
+
+  // gather description of the output run
+  D.nOutRunDims = 0;
+  for (int k = 0; k < nOutRun; k++) {
+    int j = outRunOrder[k];
+    RunDim& R = D.outRunDim[D.nOutRunDims++];
+    R.div = make_fastdiv((uint32_t)t[j]);
+    R.sstride = (uint32_t)ss[j];
+  }
+  if (D.nOutRunDims == 0) {
+    D.outRunDim[0].div = make_fastdiv(1);
+    D.outRunDim[0].sstride = 0;
+    D.nOutRunDims = 1;
+  }
+  D.smemGatherContig = 0;
+  if (wout > 1 && nOutRun > 0) {
+    int j0 = outRunOrder[0];
+    bool ok = ss[j0] == 1 && t[j0] % wout == 0;
+    for (int j = 0; j < r && ok; j++)
+      if (j != j0 && t[j] > 1 && ss[j] % wout != 0) ok = false;
+    D.smemGatherContig = ok ? 1 : 0;
+  }
+
+  // loop dimensions
+  {
+    int order[kMaxDims];
+    for (int k = 0; k < r; k++) order[k] = tp.loopOrder == 0 ? k : oo[k];
+    int64_t ntiles = 1;
+    D.nLoopDims = 0;
+    for (int k = 0; k < r; k++) {
+      int j = order[k];
+      int64_t n = ceil_div(P.d[j], t[j]);
+      if (n <= 1) continue;
+      LoopDim& L = D.loop[D.nLoopDims];
+      L.n = (uint32_t)n;
+      L.div = make_fastdiv((uint32_t)n);
+      L.t = (uint32_t)t[j];
+      L.d = (uint32_t)P.d[j];
+      L.slot = slotOf[j];
+      L.istep = P.is[j] * t[j];
+      L.ostep = P.os[j] * t[j];
+      if (j == P.peerDim) D.peerLoopDim = (int32_t)D.nLoopDims;
+      D.nLoopDims++;
+      ntiles *= n;
+      if (ntiles >= (1ll << 31)) return false;
+    }
+    D.numTiles = (uint32_t)ntiles;
+  }
+  for (int j = 0; j < r; j++) if (P.d[j] >= (1ll << 32)) return false;
+
+  out.method = kMethodTiles;
+  out.params = tp;
+  out.smemBytes = (int)(D.tableBytes + D.stages * D.stageBytes);
+  if (out.smemBytes > dev.maxSmemPerBlock) return false;
+  int bps = std::min(dev.smemPerSM / (out.smemBytes + 1024), dev.maxThreadsPerSM / tp.nthreads);
+  bps = std::max(1, std::min(bps, 32));
+  out.blocksPerSM = bps;
+  out.gridBlocks = (int)std::min<int64_t>(D.numTiles, (int64_t)dev.numSM * bps);
+
+  char buf[512];
+  std::string ts;
+  for (int j = 0; j < r; j++) { snprintf(buf, sizeof buf, "%s%lld", j ? "," : "", (long long)t[j]); ts += buf; }
+  snprintf(buf, sizeof buf, "tiles t=[%s] in=%ux%u/v%u out=%ux%u/v%u smem=%d st=%d lo=%d nt=%d",
+           ts.c_str(), D.in.nrows, D.in.run, D.in.vec, D.out.nrows, D.out.run, D.out.vec,
+           out.smemBytes, D.stages, tp.loopOrder, tp.nthreads);
+  out.label = buf;
+  out.cost = model_cost(P, out, dev);
+  return true;
+}
+
+double model_cost(const Problem& P, const Candidate& c, const DeviceInfo& dev) {
+  const TileDesc& D = c.desc;
+  const double bytes = 2.0 * (double)P.volume * P.elt;
+  const double rin = (double)D.in.run * P.elt, rout = (double)D.out.run * P.elt;
+  // DRAM/L2 sector over-fetch at both ends of every run
+  double fin = rin / (rin + 32.0), fout = rout / (rout + 32.0);
+  // instruction pressure: work items per element on both sides
+  double ipe = 1.0 / D.in.vec + 1.0 / D.out.vec + (D.smemGatherContig ? 0.0 : 1.0);
+  double finstr = 1.0 / (1.0 + 0.04 * ipe);
+  // fixed per-tile overhead
+  double vol = (double)D.in.run * D.in.nrows;
+  double ftile = vol / (vol + 384.0);
+  // bytes in flight per SM
+  double inflight = (double)c.blocksPerSM * D.stageBytes;
+  double focc = std::min(1.0, inflight / 49152.0);
+  // tail quantisation
+  double waves = std::ceil((double)D.numTiles / c.gridBlocks);
+  double fwave = (double)D.numTiles / (waves * c.gridBlocks);
+  fwave = 0.5 + 0.5 * fwave;
+  double eff = fin * fout * finstr * ftile * (0.5 + 0.5 * focc) * fwave;
+  return bytes / (dev.hbmGBs * 1e9 * eff) + 4e-6;
+}
+
+std::vector<Candidate> enumerate_candidates(const Problem& P, const DeviceInfo& dev) {
+  std::vector<Candidate> res;
+  if (P.identity) {
+    Candidate c;
+    c.method = kMethodCopy;
+    c.label = "copy";
+    c.cost = 2.0 * P.volume * P.elt / (dev.hbmGBs * 1e9);
+    res.push_back(c);
+    Candidate m = c;
+    m.method = kMethodMemcpy;
+    m.label = "memcpy";
+    m.cost = c.cost * 1.01;
+    res.push_back(m);
+    return res;
+  }
+  std::set<std::string> seen;
+  const uint32_t runs[] = {128, 256, 512, 1024};
+  const uint32_t vols[] = {8192, 16384, 32768};
+  for (uint32_t tinB : runs)
+    for (uint32_t toutB : runs)
+      for (uint32_t vB : vols)
+        for (int ext = 0; ext < 2; ext++)
+          for (int lo = 0; lo < 2; lo++) {
+            TileParams tp;
+            tp.tinBytes = tinB; tp.toutBytes = toutB; tp.vtargetBytes = vB;
+            tp.extend = ext; tp.loopOrder = lo;
+            Candidate c;
+            if (!build_tile(P, tp, dev, c)) continue;
+            if (!seen.insert(c.label).second) continue;
+            res.push_back(c);
+          }
+  std::stable_sort(res.begin(), res.end(), [](const Candidate& a, const Candidate& b) { return a.cost < b.cost; });
+  return res;
+}
+
+std::string describe(const Problem& P, const Candidate& c) {
+  char buf[1024];
+  std::string dims, iss, oss;
+  for (int j = 0; j < P.rank; j++) {
+    snprintf(buf, sizeof buf, "%s%lld", j ? "," : "", (long long)P.d[j]); dims += buf;
+    snprintf(buf, sizeof buf, "%s%lld", j ? "," : "", (long long)P.is[j]); iss += buf;
+    snprintf(buf, sizeof buf, "%s%lld", j ? "," : "", (long long)P.os[j]); oss += buf;
+  }
+  snprintf(buf, sizeof buf,
+           "{\"method\": %d, \"label\": \"%s\", \"fused_dims\": [%s], \"istride\": [%s], \"ostride\": [%s], "
+           "\"elt\": %d, \"num_tiles\": %u, \"grid\": %d, \"smem\": %d, \"model_us\": %.2f}",
+           (int)c.method, c.label.c_str(), dims.c_str(), iss.c_str(), oss.c_str(), P.elt,
+           c.method == kMethodTiles ? c.desc.numTiles : 0u, c.gridBlocks, c.smemBytes, c.cost * 1e6);
+  return buf;
+}
+
+}  // namespace cuttb

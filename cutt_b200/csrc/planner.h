@@ -1,0 +1,87 @@
+// Plan builder: canonical form of a permutation, candidate tile enumeration, cost model.
+// Pure host C++ (no CUDA calls) so that it is unit-tested without a GPU.
+//
+// Replaces reduceRanks (src/cuttplan.cpp:63-126), TensorSplit and the five
+// create*Plans enumerators (src/cuttplan.cpp:172-698) and the MWP-CWP cycle model
+// (src/cuttGpuModel.cpp) of the reference.
+#pragma once
+#include <stdint.h>
+#include <string>
+#include <vector>
+#include "permute_desc.h"
+
+namespace cuttb {
+
+struct DeviceInfo {
+  int numSM = 148;
+  int maxSmemPerBlock = 227 * 1024;  // opt-in dynamic shared memory per block
+  int smemPerSM = 228 * 1024;
+  int maxThreadsPerSM = 2048;
+  double hbmGBs = 6500.0;            // attainable copy bandwidth used by the cost model
+};
+
+// A permutation as a strided copy, dimensions sorted by input stride, fused.
+struct Problem {
+  int rank = 0;
+  int elt = 4;
+  int64_t d[kMaxDims];
+  int64_t is[kMaxDims];
+  int64_t os[kMaxDims];
+  int64_t inBase = 0, outBase = 0;
+  int peerDim = -1;   // canonical dimension whose coordinate selects the destination GPU
+  int64_t volume = 0;
+  bool identity = false;  // one contiguous run on both sides: a plain copy
+};
+
+// rank, dims, strides (elements). Drops unit dims, sorts by input stride, fuses runs that
+// are contiguous on both sides.  peerDim (index into the given dims, or -1) is never fused.
+// Returns false if the fused rank exceeds kMaxDims.
+bool canonicalize(int rank, const int64_t* d, const int64_t* is, const int64_t* os, int elt,
+                  int peerDim, Problem& P);
+
+// cuTT convention (dim[0] fastest, outDim[i] = dim[perm[i]]) -> Problem.
+bool problem_from_cutt(int rank, const int* dim, const int* perm, int elt, Problem& P);
+
+enum Method : int {
+  kMethodCopy = 0,     // identity after fusion: contiguous copy kernel
+  kMethodMemcpy = 1,   // identity: cudaMemcpyAsync device-to-device
+  kMethodTiles = 2,    // tiled permutation kernel (cp.async staged)
+  kMethodNaive = 3,    // one thread per output element (fallback for rank > kMaxDims, debug)
+};
+
+struct TileParams {
+  uint32_t tinBytes = 256;     // target bytes per input run
+  uint32_t toutBytes = 256;    // target bytes per output run
+  uint32_t vtargetBytes = 16384;  // target tile volume
+  int extend = 0;              // which dimension grows when the tile is below target: 0 next in output order, 1 next in input order
+  int nthreads = 256;
+  int stages = 2;
+  int maxVecBytes = 16;
+  int loopOrder = 0;           // tile index runs fastest along 0: input order, 1: output order
+};
+
+struct Candidate {
+  Method method = kMethodTiles;
+  TileParams params;
+  TileDesc desc;
+  int smemBytes = 0;
+  int blocksPerSM = 1;
+  int gridBlocks = 0;
+  double cost = 0.0;           // model estimate, seconds
+  std::string label;           // short human-readable description
+};
+
+// Builds the descriptor for one parameter choice; false if it is illegal
+// (too much shared memory, more than two partial dimensions, ...).
+bool build_tile(const Problem& P, const TileParams& tp, const DeviceInfo& dev, Candidate& out);
+
+// All distinct candidates for a problem, cheapest model cost first.
+std::vector<Candidate> enumerate_candidates(const Problem& P, const DeviceInfo& dev);
+
+// Model estimate (seconds) for a tiles candidate.
+double model_cost(const Problem& P, const Candidate& c, const DeviceInfo& dev);
+
+// One-line JSON description (used by tests and by CUTT_VERBOSE).
+std::string describe(const Problem& P, const Candidate& c);
+
+}  // namespace cuttb

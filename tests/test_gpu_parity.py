@@ -1,0 +1,169 @@
+"""GPU parity tests: the CUDA path, called through the C ABI, against the CPU oracle.
+Bit-exact equality is required everywhere (the path only moves bytes)."""
+import itertools
+import random
+
+import numpy as np
+import pytest
+
+from helpers import (README_CASE, TEST3_CASES, TEST4_CASE, assert_bit_exact, gpu_transpose,
+                     random_case, raw_bits, dims_of_test1, volume)
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.mark.parametrize("elt", [4, 8])
+@pytest.mark.parametrize("planner", ["plan", "measure"])
+def test_readme_example(native, oracle_mod, elt, planner):
+    dims, perm = README_CASE
+    a = raw_bits(volume(dims), elt, 1)
+    out, desc = gpu_transpose(native, dims, perm, elt, a, planner=planner)
+    assert_bit_exact(out, oracle_mod.transpose_formula(dims, perm, a), desc)
+
+
+@pytest.mark.parametrize("rank", [2, 3, 4, 5, 6, 7])
+def test_all_permutations(native, oracle_mod, rank):
+    """Every permutation (identity included) of the reference's test1 tensor, both sizes."""
+    dims = dims_of_test1(rank)
+    vol = volume(dims)
+    for elt in (8, 4):
+        a = raw_bits(vol, elt, 100 + rank)
+        for perm in itertools.permutations(range(rank)):
+            out, desc = gpu_transpose(native, dims, list(perm), elt, a)
+            assert_bit_exact(out, oracle_mod.transpose_blocked(dims, list(perm), a), "%s %s" % (perm, desc))
+
+
+@pytest.mark.parametrize("case", range(len(TEST3_CASES)))
+@pytest.mark.parametrize("elt", [4, 8])
+def test_hand_picked(native, oracle_mod, case, elt):
+    dims, perm = TEST3_CASES[case]
+    a = oracle_mod.index_pattern(volume(dims), elt)
+    for planner in ("plan", "measure"):
+        out, desc = gpu_transpose(native, dims, perm, elt, a, planner=planner)
+        assert_bit_exact(out, oracle_mod.transpose_blocked(dims, perm, a), desc)
+
+
+def test_random_ranks(native, oracle_mod):
+    rng = random.Random(20240607)
+    for rank in range(2, 16):
+        for rep in range(12):
+            dims, perm = random_case(rng, rank, 400_000)
+            for elt in (4, 8):
+                a = raw_bits(volume(dims), elt, rank * 100 + rep)
+                out, desc = gpu_transpose(native, dims, perm, elt, a)
+                assert_bit_exact(out, oracle_mod.transpose_blocked(dims, perm, a), "%s %s %s" % (dims, perm, desc))
+
+
+@pytest.mark.parametrize("dims,perm", [
+    ([31, 549, 2, 3], [3, 0, 2, 1]),
+    ([129, 130], [1, 0]),
+    ([4, 3, 5, 40, 7, 24], [4, 1, 5, 0, 3, 2]),
+    ([1305, 59, 8], [0, 2, 1]),
+    ([6, 500, 7], [2, 1, 0]),
+    ([1000, 3, 70], [1, 2, 0]),
+])
+def test_every_candidate(native, oracle_mod, dims, perm):
+    for elt in (4, 8):
+        n = native.num_candidates(dims, perm, elt)
+        assert n > 0
+        a = raw_bits(volume(dims), elt, 7)
+        want = oracle_mod.transpose_blocked(dims, perm, a)
+        for i in range(n):
+            out, desc = gpu_transpose(native, dims, perm, elt, a, planner="candidate", index=i)
+            assert_bit_exact(out, want, desc)
+
+
+@pytest.mark.parametrize("kw", [
+    dict(max_vec=4), dict(max_vec=8), dict(stages=1), dict(nthreads=128), dict(nthreads=512),
+    dict(nthreads=64, stages=1), dict(tin=128, tout=1024), dict(tin=1024, tout=128, vtarget=32768),
+    dict(loop_order=1, extend=1), dict(method=3),
+])
+def test_forced_parameters(native, oracle_mod, kw):
+    rng = random.Random(5)
+    cases = [([64, 48, 20], [2, 1, 0]), ([130, 257], [1, 0]), ([8, 6, 30, 50], [3, 0, 2, 1]),
+             ([256, 64, 12], [1, 0, 2]), ([96, 40, 33], [0, 2, 1])]
+    cases += [random_case(rng, r, 300_000) for r in (3, 4, 5, 6)]
+    for dims, perm in cases:
+        if perm == sorted(perm):
+            continue
+        for elt in (4, 8):
+            a = raw_bits(volume(dims), elt, 11)
+            out, desc = gpu_transpose(native, dims, perm, elt, a, planner="params", **kw)
+            assert_bit_exact(out, oracle_mod.transpose_blocked(dims, perm, a), "%s %s %s" % (dims, perm, desc))
+
+
+def test_streams(native, oracle_mod):
+    """Ten plans on ten streams, all writing the same output (src/cutt_test.cpp:371-404)."""
+    import torch
+    dims, perm = TEST4_CASE
+    a = oracle_mod.index_pattern(volume(dims), 8)
+    tin = torch.from_numpy(a.view(np.int64)).cuda()
+    tout = torch.full_like(tin, -1)
+    streams = [torch.cuda.Stream() for _ in range(10)]
+    torch.cuda.synchronize()
+    handles = []
+    for s in streams:
+        rc, h = native.cuttPlan(len(dims), dims, perm, 8, s.cuda_stream)
+        assert rc == 0
+        assert native.cuttExecute(h, tin.data_ptr(), tout.data_ptr()) == 0
+        handles.append(h)
+    torch.cuda.synchronize()
+    for h in handles:
+        assert native.cuttDestroy(h) == 0
+    assert_bit_exact(tout.cpu().numpy().view(np.uint64), oracle_mod.transpose_blocked(dims, perm, a))
+
+
+def test_unaligned_pointers(native, oracle_mod):
+    """Buffers that are only element-aligned must take the scalar-access variant."""
+    import torch
+    dims, perm = [64, 48, 20], [2, 1, 0]
+    for elt in (4, 8):
+        vol = volume(dims)
+        a = raw_bits(vol, elt, 3)
+        dt = torch.int32 if elt == 4 else torch.int64
+        big_in = torch.zeros(vol + 1, dtype=dt, device="cuda")
+        big_out = torch.full((vol + 1,), -1, dtype=dt, device="cuda")
+        big_in[1:] = torch.from_numpy(a.view(np.int32 if elt == 4 else np.int64)).cuda()
+        rc, h = native.cuttPlan(len(dims), dims, perm, elt, 0)
+        assert rc == 0
+        assert native.cuttExecute(h, big_in.data_ptr() + elt, big_out.data_ptr() + elt) == 0
+        torch.cuda.synchronize()
+        native.cuttDestroy(h)
+        out = big_out[1:].cpu().numpy().view(np.uint32 if elt == 4 else np.uint64)
+        assert_bit_exact(out, oracle_mod.transpose_blocked(dims, perm, a))
+        assert int(big_out[0].item()) == -1
+
+
+def test_error_codes_on_device(native):
+    import torch
+    dims, perm = [16, 16], [1, 0]
+    x = torch.zeros(256, dtype=torch.int32, device="cuda")
+    y = torch.zeros(256, dtype=torch.int32, device="cuda")
+    rc, h0 = native.cuttPlan(2, dims, perm, 4, 0)
+    assert rc == native.CUTT_SUCCESS
+    # handles count up by one per accepted plan call (src/cutt.cpp:96-97)
+    rc, h1 = native.cuttPlan(2, dims, perm, 4, 0)
+    assert rc == native.CUTT_SUCCESS and h1 == h0 + 1
+    # rejected input does not consume a handle
+    rc, _ = native.cuttPlan(2, [16, 1], perm, 4, 0)
+    assert rc == native.CUTT_INVALID_PARAMETER
+    rc, h2 = native.cuttPlan(2, dims, perm, 8, 0)
+    assert rc == native.CUTT_SUCCESS and h2 == h1 + 1
+    assert native.cuttExecute(h0, x.data_ptr(), x.data_ptr()) == native.CUTT_INVALID_PARAMETER
+    rc, _ = native.cuttPlanMeasure(2, dims, perm, 4, 0, x.data_ptr(), x.data_ptr())
+    assert rc == native.CUTT_INVALID_PARAMETER
+    assert native.cuttExecute(h0, x.data_ptr(), y.data_ptr()) == native.CUTT_SUCCESS
+    for h in (h0, h1, h2):
+        assert native.cuttDestroy(h) == native.CUTT_SUCCESS
+    assert native.cuttDestroy(h0) == native.CUTT_INVALID_PLAN
+    assert native.cuttExecute(h0, x.data_ptr(), y.data_ptr()) == native.CUTT_INVALID_PLAN
+    torch.cuda.synchronize()
+
+
+def test_transpose_host_entry(native, oracle_mod):
+    dims, perm = [300, 70, 9], [2, 0, 1]
+    for elt in (4, 8):
+        a = raw_bits(volume(dims), elt, 9)
+        out = np.empty_like(a)
+        assert native.transpose_host(dims, perm, elt, a.ctypes.data, out.ctypes.data) == 0
+        assert_bit_exact(out, oracle_mod.transpose_blocked(dims, perm, a))
