@@ -1,0 +1,447 @@
+#!/usr/bin/env python
+"""Benchmark of the tensor-transpose hot path (cuttPlanMeasure -> cuttExecute).
+
+  python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference] [--workload NAME]
+
+Workloads (all data synthetic, seeded):
+  c2   (default) one step = the 14142 x 14142 matrix transpose in fp32 and then in fp64
+       (two launches).  With N > 1 every rank transposes its own pair: independent
+       objects, no collective, weak scaling.
+  c4   rank-6 fp32 tensor with tiny leading dimensions.
+  c3   the 100-case random rank 2-7 suite (fp64 and fp32); value = median over cases.
+
+Metric: effective GB/s = 2 * volume * sizeofType / time  (the reference's definition,
+src/cuttTimer.cpp:92,134-138), whole job over all ranks.  One JSON line on stdout (rank 0).
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+METRIC = "effective_transpose_bandwidth"
+UNIT = "GB/s"
+
+
+def _peaks():
+    p = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(p):
+        try:
+            with open(p) as f:
+                return float(json.load(f)["hbm_gbs"]), "measured"
+        except Exception:
+            pass
+    return 6650.0, "fallback"
+
+
+def _workload_cases(name):
+    from cutt_b200 import workloads as W
+    if name == "c2":
+        return [("c2_f32", W.C2[0], W.C2[1], 4), ("c2_f64", W.C2[0], W.C2[1], 8)]
+    if name == "c4":
+        return [("c4_f32", W.C4[0], W.C4[1], 4)]
+    if name == "c1":
+        return [("c1_f64", W.C1[0], W.C1[1], 8)]
+    raise ValueError(name)
+
+
+def _vol(dims):
+    v = 1
+    for d in dims:
+        v *= int(d)
+    return v
+
+
+# ----------------------------------------------------------------------------------------
+# reference arm: the CPU restatement of the path (the original library has no CPU code and
+# no sm_100 build), all host threads, on bounded samples of the same workload.
+def run_reference(args):
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return 0
+    import numpy as np
+    import oracle
+    cases = _workload_cases(args.workload if args.workload != "c3" else "c2")
+    cores = oracle.num_threads()
+    bufs = []
+    for name, dims, perm, elt in cases:
+        vol = _vol(dims)
+        rng = np.random.default_rng(2 if elt == 4 else 3)
+        a = rng.random(vol, dtype=np.float32 if elt == 4 else np.float64)
+        bufs.append((dims, perm, elt, a))
+    nbytes = sum(2 * _vol(d) * e for d, _, e, _ in bufs)
+
+    def step():
+        for dims, perm, elt, a in bufs:
+            oracle.transpose_blocked(dims, perm, a)
+
+    for _ in range(min(args.warmup, 1)):
+        step()
+    steps = max(1, min(args.steps, 5))
+    t0 = time.perf_counter()
+    for _ in range(steps):
+        step()
+    dt = (time.perf_counter() - t0) / steps
+    val = nbytes / dt / 1e9
+    line = {
+        "impl": "reference", "metric": METRIC, "value": val, "unit": UNIT, "n_gpus": args.gpus,
+        "steps": steps, "warmup": min(args.warmup, 1), "ms_per_step": dt * 1e3,
+        "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+        "dtype": "b32+b64 (bit moves)", "data": "synthetic",
+        "config": {"workload": args.workload, "cases": [[n, d, p, e] for n, d, p, e in cases]},
+        "cpu_baseline": {"value": val, "unit": UNIT, "cores": cores, "kind": "port",
+                         "sample": "%d full steps of the workload (blocked OpenMP loop nest)" % steps},
+        "e2e": {"value": val, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "note": "the original cuTT has no CPU implementation and no sm_100 build; this arm times "
+                "the CPU restatement of its permutation (oracle/host_transpose.c) on the host cores",
+    }
+    print(json.dumps(line))
+    return 0
+
+
+# ----------------------------------------------------------------------------------------
+class ClockSampler:
+    QUERY = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"
+             "clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+             "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, device_index: int):
+        self.dev = device_index
+        self.proc = None
+        self.path = "/tmp/cutt_bench_clocks_%d.csv" % os.getpid()
+
+    def start(self):
+        try:
+            self.f = open(self.path, "w")
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", "--query-gpu=" + self.QUERY, "--format=csv,noheader,nounits", "-lms", "100"],
+                stdout=self.f, stderr=subprocess.DEVNULL)
+        except Exception:
+            self.proc = None
+
+    def stop(self):
+        out = {"sm_mhz": None, "sm_max_mhz": None, "reasons": []}
+        if self.proc is None:
+            return out
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=5)
+        except Exception:
+            self.proc.kill()
+        self.f.close()
+        sm, mx, reasons = [], [], set()
+        try:
+            with open(self.path) as f:
+                for ln in f:
+                    p = [x.strip() for x in ln.split(",")]
+                    if len(p) < 9 or not p[0].isdigit() or int(p[0]) != self.dev:
+                        continue
+                    try:
+                        sm.append(float(p[1])); mx.append(float(p[2]))
+                    except ValueError:
+                        continue
+                    for name, v in zip(("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"), p[5:9]):
+                        if v.lower().startswith("active"):
+                            reasons.add(name)
+            os.remove(self.path)
+        except Exception:
+            pass
+        if sm:
+            # samples under load: the upper half of the observed clocks
+            sm.sort()
+            out["sm_mhz"] = statistics.median(sm[len(sm) // 2:])
+            out["sm_max_mhz"] = max(mx)
+        out["reasons"] = sorted(reasons)
+        out["samples"] = len(sm)
+        return out
+
+
+def _physical_gpu_index(local_device: int) -> int:
+    vis = os.environ.get("CUDA_VISIBLE_DEVICES")
+    if vis:
+        try:
+            return int(vis.split(",")[local_device])
+        except Exception:
+            return local_device
+    return local_device
+
+
+def run_ours(args):
+    import numpy as np
+    import torch
+    import cutt_b200 as C
+    from cutt_b200 import workloads as W
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py: no CUDA device; the transpose path has no CPU fallback")
+    torch.cuda.set_device(local)
+    dist = None
+    if world > 1:
+        import torch.distributed as dist
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local))
+    C.lib()
+    peak, peak_kind = _peaks()
+    stream = torch.cuda.current_stream().cuda_stream
+
+    def barrier():
+        if dist is not None:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    def max_over_ranks(x: float) -> float:
+        if dist is None:
+            return x
+        t = torch.tensor([x], dtype=torch.float64, device="cuda")
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return float(t.item())
+
+    launches0 = C.launch_count()
+    extras = {}
+
+    if args.workload == "c3":
+        res = run_suite(C, W.c3_cases(args.suite_cases), stream, reps=max(3, args.steps))
+        med = statistics.median(r["gbs"] for r in res)
+        t_ms = statistics.median(r["ms"] for r in res)
+        val = max_over_ranks(med) if world == 1 else med * world
+        line = base_line(args, val, t_ms, world)
+        line["config"] = {"workload": "c3: %d seeded random rank 2-7 tensors of ~2e8 elements, fp64 and fp32; median over cases" % len(res),
+                          "l2": "inputs larger than L2"}
+        line["roofline"] = {"bound": "hbm", "achieved": med, "peak": peak, "unit": UNIT, "frac": med / peak,
+                            "traffic": None, "peak_kind": peak_kind}
+        line["suite"] = {"median_gbs": med, "min_gbs": min(r["gbs"] for r in res), "max_gbs": max(r["gbs"] for r in res),
+                         "cases": res if args.verbose else len(res)}
+        line["gpu_launches"] = C.launch_count() - launches0
+        if rank == 0:
+            print(json.dumps(line))
+        return 0
+
+    cases = _workload_cases(args.workload)
+    # device-resident inputs (seeded uniform values), one pair of buffers per case
+    plans = []
+    for ci, (name, dims, perm, elt) in enumerate(cases):
+        vol = _vol(dims)
+        g = torch.Generator(device="cuda")
+        g.manual_seed(2 + ci + 100 * rank)
+        tin = torch.rand(vol, dtype=torch.float32 if elt == 4 else torch.float64, device="cuda", generator=g)
+        tout = torch.empty_like(tin)
+        rc, h = C.cuttPlanMeasure(len(dims), dims, perm, elt, stream, tin.data_ptr(), tout.data_ptr())
+        if rc != 0:
+            raise SystemExit("cuttPlanMeasure failed: %d" % rc)
+        plans.append((name, dims, perm, elt, vol, tin, tout, h))
+    step_bytes = sum(2 * vol * elt for _, _, _, elt, vol, _, _, _ in plans)
+
+    def step():
+        for _, _, _, _, _, tin, tout, h in plans:
+            rc = C.cuttExecute(h, tin.data_ptr(), tout.data_ptr())
+            if rc != 0:
+                raise SystemExit("cuttExecute failed: %d" % rc)
+
+    for _ in range(max(3, args.warmup)):
+        step()
+    sampler = ClockSampler(_physical_gpu_index(local))
+    if rank == 0:
+        sampler.start()
+        time.sleep(0.3)
+    barrier()
+    launches_t0 = C.launch_count()
+    ev = [[torch.cuda.Event(enable_timing=True) for _ in range(len(plans) + 1)] for _ in range(args.steps)]
+    for k in range(args.steps):
+        ev[k][0].record()
+        for i, (_, _, _, _, _, tin, tout, h) in enumerate(plans):
+            rc = C.cuttExecute(h, tin.data_ptr(), tout.data_ptr())
+            ev[k][i + 1].record()
+    barrier()
+    launches_timed = C.launch_count() - launches_t0
+    total_ms = ev[0][0].elapsed_time(ev[-1][-1])
+    total_ms = max_over_ranks(total_ms)
+    clocks = sampler.stop() if rank == 0 else None
+    ms_per_step = total_ms / args.steps
+    value = world * step_bytes / (ms_per_step * 1e-3) / 1e9
+
+    # dominant kernel: the launch moving the most bytes
+    dom = max(range(len(plans)), key=lambda i: plans[i][4] * plans[i][3])
+    dom_ms = statistics.mean(ev[k][dom].elapsed_time(ev[k][dom + 1]) for k in range(args.steps))
+    dom_bytes = 2 * plans[dom][4] * plans[dom][3]
+    achieved = dom_bytes / (dom_ms * 1e-3) / 1e9
+    per_case = {}
+    for i, p in enumerate(plans):
+        ms = statistics.mean(ev[k][i].elapsed_time(ev[k][i + 1]) for k in range(args.steps))
+        per_case[p[0]] = {"ms": ms, "gbs": 2 * p[4] * p[3] / (ms * 1e-3) / 1e9, "plan": json.loads(C.plan_describe(p[7]))["label"]}
+
+    # same-GPU device-to-device copy of the dominant case's bytes, for context
+    torch.cuda.synchronize()
+    src, dst = plans[dom][5], plans[dom][6]
+    for _ in range(2):
+        dst.copy_(src)
+    e0 = torch.cuda.Event(enable_timing=True); e1 = torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(5):
+        dst.copy_(src)
+    e1.record()
+    torch.cuda.synchronize()
+    d2d = dom_bytes / (e0.elapsed_time(e1) / 5 * 1e-3) / 1e9
+
+    # end to end: host buffers in, host buffers out, through the C ABI
+    e2e_steps = max(1, min(args.steps, 3))
+    hbufs = []
+    for (name, dims, perm, elt, vol, tin, tout, h) in plans:
+        hin = torch.empty(vol, dtype=tin.dtype, pin_memory=True)
+        hin.copy_(tin)
+        hout = torch.empty(vol, dtype=tin.dtype, pin_memory=True)
+        hbufs.append((dims, perm, elt, hin, hout))
+    torch.cuda.synchronize()
+
+    def e2e_step():
+        for dims, perm, elt, hin, hout in hbufs:
+            rc = C.transpose_host(dims, perm, elt, hin.data_ptr(), hout.data_ptr())
+            if rc != 0:
+                raise SystemExit("cutt_c_transpose_host failed: %d" % rc)
+
+    e2e_step()
+    barrier()
+    t0 = time.perf_counter()
+    for _ in range(e2e_steps):
+        e2e_step()
+    barrier()
+    e2e_s = max_over_ranks((time.perf_counter() - t0) / e2e_steps)
+    e2e_val = world * step_bytes / e2e_s / 1e9
+    # the host round trip must reproduce the device result
+    for (dims, perm, elt, hin, hout), p in zip(hbufs, plans):
+        if not torch.equal(hout, p[6].cpu()):
+            raise SystemExit("end-to-end result differs from the device-resident result")
+
+    line = base_line(args, value, ms_per_step, world)
+    line["config"] = {"workload": "c2: rank-2 transpose (14142,14142) perm (1,0), fp32 then fp64 per step"
+                      if args.workload == "c2" else args.workload,
+                      "cases": [[p[0], p[1], p[2], p[3]] for p in plans],
+                      "l2": "inputs larger than L2 (0.8 GB and 1.6 GB per side)", "per_case": per_case,
+                      "d2d_copy_gbs": d2d}
+    line["roofline"] = {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": UNIT,
+                        "frac": achieved / peak, "traffic": _traffic_note(plans[dom][0]),
+                        "kernel": "permute_tiles_kernel (%s)" % plans[dom][0], "peak_kind": peak_kind,
+                        "frac_of_same_run_d2d_copy": achieved / d2d}
+    line["e2e"] = {"value": e2e_val, "unit": UNIT, "h2d_bytes_per_step": step_bytes // 2,
+                   "d2h_bytes_per_step": step_bytes // 2, "steps": e2e_steps}
+    line["gpu_launches"] = launches_timed
+    line["clocks"] = clocks
+
+    if rank == 0 and world == 1 and not args.no_cpu_baseline:
+        line["cpu_baseline"] = cpu_baseline(cases)
+    if rank == 0 and not args.no_extras and world == 1:
+        try:
+            res = run_suite(C, W.c3_cases(args.suite_cases), stream, reps=5)
+            med = statistics.median(r["gbs"] for r in res)
+            extras["c3_suite"] = {"cases": len(res), "median_gbs": med, "frac_of_peak": med / peak,
+                                  "frac_of_8000": med / 8000.0,
+                                  "min_gbs": min(r["gbs"] for r in res), "max_gbs": max(r["gbs"] for r in res)}
+        except Exception as e:  # extras never fail the headline
+            extras["c3_suite"] = {"error": repr(e)}
+    if extras:
+        line["extras"] = extras
+    for p in plans:
+        C.cuttDestroy(p[7])
+    if rank == 0:
+        print(json.dumps(line))
+    if dist is not None:
+        dist.destroy_process_group()
+    return 0
+
+
+def _traffic_note(case_name):
+    """DRAM bytes per launch of the dominant kernel from the committed ncu capture, if any."""
+    p = os.path.join(ROOT, "profiles", "traffic.json")
+    try:
+        with open(p) as f:
+            return json.load(f).get(case_name)
+    except Exception:
+        return None
+
+
+def base_line(args, value, ms_per_step, world):
+    return {"metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps,
+            "warmup": max(3, args.warmup), "ms_per_step": ms_per_step, "higher_is_better": True,
+            "scaling": "weak", "vs_baseline": None, "dtype": "b32+b64 (bit moves)", "data": "synthetic"}
+
+
+def run_suite(C, cases, stream, reps=5):
+    """cuttPlanMeasure + timed cuttExecute for every case, fp64 then fp32."""
+    import torch
+    out = []
+    maxvol = max(_vol(d) for d, _ in cases)
+    buf_in = torch.rand(maxvol, dtype=torch.float64, device="cuda")
+    buf_out = torch.empty_like(buf_in)
+    for ci, (dims, perm) in enumerate(cases):
+        vol = _vol(dims)
+        for elt in (8, 4):
+            rc, h = C.cuttPlanMeasure(len(dims), dims, perm, elt, stream, buf_in.data_ptr(), buf_out.data_ptr())
+            if rc != 0:
+                raise RuntimeError("plan failed %s %s" % (dims, perm))
+            C.cuttExecute(h, buf_in.data_ptr(), buf_out.data_ptr())
+            ts = []
+            for _ in range(reps):
+                e0 = torch.cuda.Event(enable_timing=True); e1 = torch.cuda.Event(enable_timing=True)
+                e0.record()
+                C.cuttExecute(h, buf_in.data_ptr(), buf_out.data_ptr())
+                e1.record()
+                torch.cuda.synchronize()
+                ts.append(e0.elapsed_time(e1))
+            ms = statistics.median(ts)
+            label = json.loads(C.plan_describe(h))["label"]
+            C.cuttDestroy(h)
+            out.append({"case": ci, "dims": dims, "perm": perm, "elt": elt, "ms": ms,
+                        "gbs": 2 * vol * elt / (ms * 1e-3) / 1e9, "plan": label})
+    return out
+
+
+def cpu_baseline(cases):
+    import numpy as np
+    import oracle
+    bufs = []
+    for name, dims, perm, elt in cases:
+        a = np.random.default_rng(5).random(_vol(dims), dtype=np.float32 if elt == 4 else np.float64)
+        bufs.append((dims, perm, a))
+    nbytes = sum(2 * a.size * a.dtype.itemsize for _, _, a in bufs)
+    for dims, perm, a in bufs:  # warm (page faults of the output allocator)
+        oracle.transpose_blocked(dims, perm, a)
+    n = 0
+    t0 = time.perf_counter()
+    while True:
+        for dims, perm, a in bufs:
+            oracle.transpose_blocked(dims, perm, a)
+        n += 1
+        if time.perf_counter() - t0 > 10.0 or n >= 8:
+            break
+    dt = (time.perf_counter() - t0) / n
+    return {"value": nbytes / dt / 1e9, "unit": UNIT, "cores": oracle.num_threads(), "kind": "port",
+            "sample": "%d full steps of the same workload, blocked OpenMP loop nest (oracle/host_transpose.c)" % n}
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--workload", default="c2", choices=["c1", "c2", "c3", "c4"])
+    ap.add_argument("--suite-cases", type=int, default=100)
+    ap.add_argument("--no-extras", action="store_true")
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--verbose", action="store_true")
+    args = ap.parse_args()
+    if args.impl == "reference":
+        return run_reference(args)
+    return run_ours(args)
+
+
+if __name__ == "__main__":
+    sys.exit(main())
