@@ -73,7 +73,7 @@ def lib() -> ctypes.CDLL:
     L.cutt_c_plan_candidate.argtypes = [up, ctypes.c_int, ip, ip, ctypes.c_size_t, vp, ctypes.c_int]
     L.cutt_c_plan_params.argtypes = [up, ctypes.c_int, ip, ip, ctypes.c_size_t, vp, ctypes.c_int,
                                      ctypes.c_uint, ctypes.c_uint, ctypes.c_uint, ctypes.c_int,
-                                     ctypes.c_int, ctypes.c_int, ctypes.c_int, ctypes.c_int]
+                                     ctypes.c_int, ctypes.c_int, ctypes.c_int, ctypes.c_int, ctypes.c_int]
     L.cutt_c_transpose_host.argtypes = [ctypes.c_int, ip, ip, ctypes.c_size_t, vp, vp]
     L.cutt_c_launch_count.restype = ctypes.c_ulonglong
     L.cutt_c_clear_plan_cache.restype = None
@@ -140,11 +140,11 @@ def plan_candidate(dim, permutation, sizeofType, index, stream=0):
 
 
 def plan_params(dim, permutation, sizeofType, stream=0, method=2, tin=256, tout=256, vtarget=16384,
-                extend=0, loop_order=0, max_vec=16, nthreads=256, stages=2):
+                extend=0, loop_order=0, max_vec=16, max_v=16, nthreads=256, stages=2):
     h = ctypes.c_uint(0)
     rc = lib().cutt_c_plan_params(ctypes.byref(h), len(dim), _iarr(dim), _iarr(permutation), sizeofType,
                                   stream, method, tin, tout, vtarget, extend, loop_order, max_vec,
-                                  nthreads, stages)
+                                  max_v, nthreads, stages)
     return rc, h.value
 
 

@@ -201,6 +201,7 @@ bool adopt_candidate(Plan& p, const DeviceInfo& dev, const Candidate& c) {
   if (p.cand.desc.in.vec > 1 || p.cand.desc.out.vec > 1) {
     TileParams tp = c.params;
     tp.maxVecBytes = p.elt;
+    tp.maxVBytes = p.elt;
     Candidate f;
     if (build_tile(p.prob, tp, dev, f) && finalize_tiles(dev, f, p.fallbackGrid)) {
       p.fallback = f;
@@ -459,7 +460,7 @@ int cutt_c_plan_candidate(unsigned int* handle, int rank, const int* dim, const 
 int cutt_c_plan_params(unsigned int* handle, int rank, const int* dim, const int* permutation,
                        size_t sizeofType, void* stream, int method, unsigned tinBytes,
                        unsigned toutBytes, unsigned vtargetBytes, int extend, int loopOrder,
-                       int maxVecBytes, int nthreads, int stages) {
+                       int maxVecBytes, int maxVBytes, int nthreads, int stages) {
   PlanRequest req;
   req.mode = kByParams;
   req.method = method;
@@ -469,6 +470,7 @@ int cutt_c_plan_params(unsigned int* handle, int rank, const int* dim, const int
   req.params.extend = extend;
   req.params.loopOrder = loopOrder;
   req.params.maxVecBytes = maxVecBytes;
+  req.params.maxVBytes = maxVBytes;
   if (nthreads != 64 && nthreads != 128 && nthreads != 256 && nthreads != 512) return CUTT_INVALID_PARAMETER;
   if (stages != 1 && stages != 2) return CUTT_INVALID_PARAMETER;
   req.params.nthreads = nthreads;

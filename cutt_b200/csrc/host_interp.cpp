@@ -11,28 +11,34 @@
 
 using namespace cuttb;
 
-template <int ELT, int WIN, int WOUT>
+template <int ELT, int WIN, int WOUT, int V, bool WIDE>
 static void run_desc(const TileDesc& D, const unsigned char* in, unsigned char* out) {
-  std::vector<RowEnt> tabIn(D.in.nrows), tabOut(D.out.nrows);
-  for (uint32_t r = 0; r < D.in.nrows; r++) tabIn[r] = make_row(D.in, r);
-  for (uint32_t r = 0; r < D.out.nrows; r++) tabOut[r] = make_row(D.out, r);
+  std::vector<unsigned char> tables(D.tableBytes + 16);
+  for (uint32_t tid = 0; tid < D.nthreads; tid++) build_tables<WIDE>(D, tables.data(), tid, D.nthreads);
   std::vector<unsigned char> sbuf(D.stageBytes);
   for (uint32_t tile = 0; tile < D.numTiles; tile++) {
     TileCtx c;
     decode_tile(D, tile, c);
     memset(sbuf.data(), 0xEE, sbuf.size());
     for (uint32_t tid = 0; tid < D.nthreads; tid++)
-      tile_load<ELT, WIN>(D, c, tabIn.data(), sbuf.data(), in, tid);
+      tile_load<ELT, WIN, WIDE>(D, c, tables.data(), sbuf.data(), in, tid);
     for (uint32_t tid = 0; tid < D.nthreads; tid++)
-      tile_store<ELT, WOUT>(D, c, tabOut.data(), sbuf.data(), out, tid);
+      tile_store<ELT, WOUT, V, WIDE>(D, c, tables.data(), sbuf.data(), out, tid);
   }
 }
 
 static int dispatch(const TileDesc& D, const unsigned char* in, unsigned char* out) {
-#define CASE(E, A, B) if (D.elt == E && D.in.vec == A && D.out.vec == B) { run_desc<E, A, B>(D, in, out); return 0; }
-  CASE(4, 1, 1) CASE(4, 1, 2) CASE(4, 1, 4) CASE(4, 2, 1) CASE(4, 2, 2) CASE(4, 2, 4)
-  CASE(4, 4, 1) CASE(4, 4, 2) CASE(4, 4, 4)
-  CASE(8, 1, 1) CASE(8, 1, 2) CASE(8, 2, 1) CASE(8, 2, 2)
+#define CASE(E, A, B, V) \
+  if (D.elt == E && D.in.vec == A && D.out.vec == B && D.vblk == V) { \
+    if (D.wide) { if (V != 1) return 4; run_desc<E, A, B, 1, true>(D, in, out); } \
+    else run_desc<E, A, B, V, false>(D, in, out); \
+    return 0; }
+#define CASES_V(E, A, B) CASE(E, A, B, 1) CASE(E, A, B, 2) CASE(E, A, B, 4)
+  CASES_V(4, 1, 1) CASES_V(4, 1, 2) CASES_V(4, 1, 4) CASES_V(4, 2, 1) CASES_V(4, 2, 2) CASES_V(4, 2, 4)
+  CASES_V(4, 4, 1) CASES_V(4, 4, 2) CASES_V(4, 4, 4)
+  CASE(8, 1, 1, 1) CASE(8, 1, 1, 2) CASE(8, 1, 2, 1) CASE(8, 1, 2, 2)
+  CASE(8, 2, 1, 1) CASE(8, 2, 1, 2) CASE(8, 2, 2, 1) CASE(8, 2, 2, 2)
+#undef CASES_V
 #undef CASE
   return 4;
 }
@@ -68,14 +74,14 @@ int cutt_hostcheck_run(int rank, const int* dim, const int* perm, int elt, int i
 // Same, for an explicit parameter choice (used to force odd tile shapes in tests).
 int cutt_hostcheck_run_params(int rank, const int* dim, const int* perm, int elt,
                               unsigned tinBytes, unsigned toutBytes, unsigned vtargetBytes,
-                              int extend, int loopOrder, int maxVecBytes, int nthreads,
+                              int extend, int loopOrder, int maxVecBytes, int maxVBytes, int nthreads,
                               const void* in, void* out, char* label, int labelLen) {
   Problem P;
   if (!problem_from_cutt(rank, dim, perm, elt, P)) return 2;
   if (P.identity) { memcpy(out, in, (size_t)P.volume * elt); return 0; }
   TileParams tp;
   tp.tinBytes = tinBytes; tp.toutBytes = toutBytes; tp.vtargetBytes = vtargetBytes;
-  tp.extend = extend; tp.loopOrder = loopOrder; tp.maxVecBytes = maxVecBytes; tp.nthreads = nthreads;
+  tp.extend = extend; tp.loopOrder = loopOrder; tp.maxVecBytes = maxVecBytes; tp.maxVBytes = maxVBytes; tp.nthreads = nthreads;
   Candidate c;
   if (!build_tile(P, tp, g_dev, c)) return 5;
   if (label && labelLen > 0) snprintf(label, labelLen, "%s", describe(P, c).c_str());

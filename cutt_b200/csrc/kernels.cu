@@ -25,20 +25,16 @@ __device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commi
 template <int N>
 __device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;\n" ::"n"(N) : "memory"); }
 
-template <int ELT, int WIN, int WOUT>
+template <int ELT, int WIN, int WOUT, int V, bool WIDE>
 __global__ void __launch_bounds__(512)
 permute_tiles_kernel(const __grid_constant__ TileDesc D, const unsigned char* __restrict__ in,
                      const __grid_constant__ PeerPtrs outs) {
   extern __shared__ __align__(16) unsigned char smem[];
-  RowEnt* tabIn = reinterpret_cast<RowEnt*>(smem);
-  RowEnt* tabOut = tabIn + D.in.nrows;
-  unsigned char* stage0 = smem + D.tableBytes;
   const uint32_t tid = threadIdx.x;
-
-  for (uint32_t r = tid; r < D.in.nrows; r += blockDim.x) tabIn[r] = make_row(D.in, r);
-  for (uint32_t r = tid; r < D.out.nrows; r += blockDim.x) tabOut[r] = make_row(D.out, r);
+  build_tables<WIDE>(D, smem, tid, blockDim.x);
   __syncthreads();
 
+  const uint32_t stage0 = (uint32_t)__cvta_generic_to_shared(smem) + D.tableBytes;
   uint32_t tile = blockIdx.x;
   if (tile >= D.numTiles) return;
   TileCtx cur, nxt;
@@ -46,20 +42,20 @@ permute_tiles_kernel(const __grid_constant__ TileDesc D, const unsigned char* __
   nxt = cur;
 
   if (D.stages >= 2) {
-    tile_load<ELT, WIN>(D, cur, tabIn, stage0, in, tid);
+    tile_load<ELT, WIN, WIDE>(D, cur, smem, stage0, in, tid);
     cp_async_commit();
     uint32_t s = 0;
     for (; tile < D.numTiles; tile += gridDim.x) {
       const uint32_t tn = tile + gridDim.x;
       if (tn < D.numTiles) {
         decode_tile(D, tn, nxt);
-        tile_load<ELT, WIN>(D, nxt, tabIn, stage0 + (s ^ 1u) * D.stageBytes, in, tid);
+        tile_load<ELT, WIN, WIDE>(D, nxt, smem, stage0 + (s ^ 1u) * D.stageBytes, in, tid);
       }
       cp_async_commit();
       cp_async_wait<1>();
       __syncthreads();
       unsigned char* o = D.peerLoopDim >= 0 ? outs.p[cur.peer] : outs.p[0];
-      tile_store<ELT, WOUT>(D, cur, tabOut, stage0 + s * D.stageBytes, o, tid);
+      tile_store<ELT, WOUT, V, WIDE>(D, cur, smem, stage0 + s * D.stageBytes, o, tid);
       __syncthreads();
       cur = nxt;
       s ^= 1u;
@@ -67,12 +63,12 @@ permute_tiles_kernel(const __grid_constant__ TileDesc D, const unsigned char* __
   } else {
     for (; tile < D.numTiles; tile += gridDim.x) {
       decode_tile(D, tile, cur);
-      tile_load<ELT, WIN>(D, cur, tabIn, stage0, in, tid);
+      tile_load<ELT, WIN, WIDE>(D, cur, smem, stage0, in, tid);
       cp_async_commit();
       cp_async_wait<0>();
       __syncthreads();
       unsigned char* o = D.peerLoopDim >= 0 ? outs.p[cur.peer] : outs.p[0];
-      tile_store<ELT, WOUT>(D, cur, tabOut, stage0, o, tid);
+      tile_store<ELT, WOUT, V, WIDE>(D, cur, smem, stage0, o, tid);
       __syncthreads();
     }
   }
@@ -80,11 +76,18 @@ permute_tiles_kernel(const __grid_constant__ TileDesc D, const unsigned char* __
 
 typedef void (*TilesKernel)(const TileDesc, const unsigned char*, const PeerPtrs);
 
-static TilesKernel pick_tiles_kernel(int elt, int win, int wout) {
-#define CASE(E, A, B) if (elt == E && win == A && wout == B) return permute_tiles_kernel<E, A, B>;
-  CASE(4, 1, 1) CASE(4, 1, 2) CASE(4, 1, 4) CASE(4, 2, 1) CASE(4, 2, 2) CASE(4, 2, 4)
-  CASE(4, 4, 1) CASE(4, 4, 2) CASE(4, 4, 4)
-  CASE(8, 1, 1) CASE(8, 1, 2) CASE(8, 2, 1) CASE(8, 2, 2)
+static TilesKernel pick_tiles_kernel(const TileDesc& D) {
+  const int elt = D.elt, win = D.in.vec, wout = D.out.vec, v = D.vblk;
+#define CASE(E, A, B, VV) \
+  if (elt == E && win == A && wout == B && v == VV) { \
+    if (D.wide) return VV == 1 ? permute_tiles_kernel<E, A, B, 1, true> : nullptr; \
+    return permute_tiles_kernel<E, A, B, VV, false>; }
+#define CASES_V(E, A, B) CASE(E, A, B, 1) CASE(E, A, B, 2) CASE(E, A, B, 4)
+  CASES_V(4, 1, 1) CASES_V(4, 1, 2) CASES_V(4, 1, 4) CASES_V(4, 2, 1) CASES_V(4, 2, 2) CASES_V(4, 2, 4)
+  CASES_V(4, 4, 1) CASES_V(4, 4, 2) CASES_V(4, 4, 4)
+  CASE(8, 1, 1, 1) CASE(8, 1, 1, 2) CASE(8, 1, 2, 1) CASE(8, 1, 2, 2)
+  CASE(8, 2, 1, 1) CASE(8, 2, 1, 2) CASE(8, 2, 2, 1) CASE(8, 2, 2, 2)
+#undef CASES_V
 #undef CASE
   return nullptr;
 }
@@ -114,7 +117,7 @@ static cudaError_t ensure_smem(TilesKernel k, int bytes) {
 
 int tiles_blocks_per_sm(const Candidate& c) {
   const TileDesc& D = c.desc;
-  TilesKernel k = pick_tiles_kernel(D.elt, D.in.vec, D.out.vec);
+  TilesKernel k = pick_tiles_kernel(D);
   if (!k) return -1;
   if (ensure_smem(k, c.smemBytes) != cudaSuccess) return -1;
   int nb = 0;
@@ -132,7 +135,7 @@ bool tiles_pointers_aligned(const Candidate& c, const void* in, const void* out)
 cudaError_t launch_tiles(const Candidate& c, int gridBlocks, const void* in, const PeerPtrs& outs,
                          cudaStream_t stream) {
   const TileDesc& D = c.desc;
-  TilesKernel k = pick_tiles_kernel(D.elt, D.in.vec, D.out.vec);
+  TilesKernel k = pick_tiles_kernel(D);
   if (!k) return cudaErrorInvalidValue;
   cudaError_t e = ensure_smem(k, c.smemBytes);
   if (e != cudaSuccess) return e;

@@ -10,7 +10,13 @@
 // elements in global memory; the run is made of the leading dimensions in that
 // side's stride order, the rows enumerate the remaining tile dimensions.  In shared
 // memory the tile is kept in input order (a run of the input side is contiguous),
-// with padding so that the gather performed by the output side spreads over banks.
+// padded and skewed so that the gather performed by the output side spreads over banks.
+//
+// Output side register blocking: when the fastest input dimension (dimension 0) is a
+// row dimension of the output side, rows are handled in groups of V along it.  A thread
+// then reads W vectors of V elements from shared memory (V consecutive along dimension 0,
+// for W consecutive positions of the output run) and writes V vectors of W elements to
+// global memory; the V x W transpose happens in registers.
 //
 // At most two dimensions may have 1 < t_j < d_j with d_j not a multiple of t_j
 // ("partial" dimensions, slots 0 and 1); the last tile along such a dimension is
@@ -68,38 +74,62 @@ CUTT_HD uint32_t fdiv(uint32_t n, const FastDiv& f) {
   return (t + ((n - t) >> f.sh1)) >> f.sh2;
 }
 
-// One entry of a side's row table (built per thread block in shared memory).
-struct __attribute__((aligned(16))) RowEnt {
-  int64_t goff;     // global offset of the run start, relative to the tile origin (elements)
-  uint32_t soff;    // shared-memory offset of the row base (elements)
-  uint16_t c0;      // coordinate of this row along partial dimension slot 0 (0 if none)
-  uint16_t c1;      // same for slot 1
+// Row-table entries (built per thread block in shared memory).  goff: global offset of
+// the run start relative to the tile origin, in elements; soffB: shared-memory offset of
+// the row base in bytes.  The narrow form is used when every goff fits 32 bits.
+struct RowEntN {
+  uint32_t goff;
+  uint32_t soffB;
+};
+struct __attribute__((aligned(16))) RowEntW {
+  int64_t goff;
+  uint32_t soffB;
+  uint32_t pad_;
+};
+template <bool WIDE> struct RowEntSel { typedef RowEntN type; };
+template <> struct RowEntSel<true> { typedef RowEntW type; };
+
+// Coordinates of a row along the two partial dimensions (elements; 0 if not applicable).
+struct RowCoord {
+  uint16_t c0;
+  uint16_t c1;
+};
+
+// Skew of a dimension's shared-memory placement: position c is moved by
+// ((c >> shift) & mask) * unitB bytes so that lanes that are W positions apart do not
+// meet in the same bank group.
+struct Skew {
+  uint32_t shift;
+  uint32_t mask;   // 0: no skew
+  uint32_t unitB;
 };
 
 // A tile dimension that enumerates rows of one side.
 struct RowDim {
-  uint32_t ext;     // tile extent
-  uint32_t sstride; // shared-memory stride (elements)
-  int64_t gstride;  // global stride on this side (elements)
-  int32_t slot;     // partial slot (0/1) this dimension feeds, or -1
-  int32_t pad_;
+  uint32_t ext;      // positions along this dimension within the tile
+  uint32_t sstrideB; // shared-memory stride per position (bytes)
+  int64_t gstride;   // global stride per position on this side (elements)
+  int32_t slot;      // partial slot (0/1) this dimension feeds, or -1
+  uint32_t cmul;     // elements per position (V for the register-blocked dimension, else 1)
+  Skew skew;
+  uint32_t pad_;
 };
 
-// A dimension inside the output side's run: needed to turn a position along the run
-// into a shared-memory offset (the gather).
+// A dimension inside the output side's run: turns a position along the run into a
+// shared-memory offset (the gather).
 struct RunDim {
-  FastDiv div;      // division by ext
-  uint32_t sstride; // shared-memory stride (elements)
-  uint32_t pad_;
+  FastDiv div;       // division by the tile extent
+  uint32_t sstrideB; // shared-memory stride (bytes)
+  Skew skew;
 };
 
 struct Side {
   uint32_t run;        // elements per run in a full tile
   uint32_t runPrefix;  // run length = runPrefix * (extent of the run's last dimension)
   int32_t runSlot;     // partial slot that shortens the run in the last tile, or -1
-  uint32_t nrows;      // rows per tile
+  uint32_t nrows;      // rows (output side: row groups of V) per tile
   uint32_t nRowDims;
-  uint32_t vec;        // elements per memory access on this side (1, 2 or 4)
+  uint32_t vec;        // elements per global memory access on this side (1, 2 or 4)
   uint32_t tq;         // threads along the run (power of two, <= block size)
   uint32_t tqShift;    // log2(tq)
   RowDim rowDim[kMaxDims];
@@ -123,11 +153,14 @@ struct TileDesc {
   uint32_t nOutRunDims;
   uint32_t tileElems;   // shared-memory elements per stage (with padding)
   uint32_t stageBytes;  // bytes per stage, rounded up to 16
-  uint32_t tableBytes;  // bytes of the two row tables
+  uint32_t tableBytes;  // bytes of all tables in front of the stages, rounded up to 16
   uint32_t stages;      // shared-memory stages (1 or 2)
   uint32_t smemGatherContig; // 1 if `out.vec` consecutive run positions are contiguous and aligned in smem
+  uint32_t vblk;        // V: rows of the output side handled together along dimension 0 (1, 2 or 4)
+  uint32_t wide;        // 1: 64-bit row offsets
   int32_t peerLoopDim;  // loop dimension whose coordinate selects the destination GPU, or -1
   uint32_t pad_;
+  int64_t vstep;        // output offset between the V rows of a group (elements)
   int64_t inBase;       // element offset added to the input pointer
   int64_t outBase;      // element offset added to the output pointer
   Side in;
@@ -136,6 +169,22 @@ struct TileDesc {
   LoopDim loop[kMaxDims];
 };
 
+// Shared-memory layout in front of the stage buffers.
+struct TableLayout {
+  uint32_t tabIn, tabOut, coordIn, coordOut, qtab, total;
+};
+CUTT_HD TableLayout table_layout(const TileDesc& D) {
+  TableLayout L;
+  const uint32_t esz = D.wide ? (uint32_t)sizeof(RowEntW) : (uint32_t)sizeof(RowEntN);
+  L.tabIn = 0;
+  L.tabOut = L.tabIn + D.in.nrows * esz;
+  L.coordIn = L.tabOut + D.out.nrows * esz;
+  L.coordOut = L.coordIn + D.in.nrows * (uint32_t)sizeof(RowCoord);
+  L.qtab = (L.coordOut + D.out.nrows * (uint32_t)sizeof(RowCoord) + 15u) & ~15u;
+  L.total = (L.qtab + D.out.run * 4u + 15u) & ~15u;
+  return L;
+}
+
 // Per-tile context derived from the tile index.
 struct TileCtx {
   int64_t inOff;
@@ -143,6 +192,7 @@ struct TileCtx {
   uint32_t rem0;     // remaining extent along partial slot 0 (huge if the tile is not short)
   uint32_t rem1;     // same for slot 1
   uint32_t peer;
+  uint32_t partial;  // 1 if the tile is short along a partial dimension
 };
 
 CUTT_HD void decode_tile(const TileDesc& D, uint32_t tile, TileCtx& c) {
@@ -151,6 +201,7 @@ CUTT_HD void decode_tile(const TileDesc& D, uint32_t tile, TileCtx& c) {
   c.rem0 = 0xffffffffu;
   c.rem1 = 0xffffffffu;
   c.peer = 0;
+  c.partial = 0;
   uint32_t id = tile;
   for (uint32_t k = 0; k < D.nLoopDims; k++) {
     const LoopDim& L = D.loop[k];
@@ -162,49 +213,83 @@ CUTT_HD void decode_tile(const TileDesc& D, uint32_t tile, TileCtx& c) {
     else c.outOff += (int64_t)cc * L.ostep;
     if (L.slot >= 0) {
       uint32_t left = L.d - cc * L.t;
-      left = left < L.t ? left : L.t;
-      if (L.slot == 0) c.rem0 = left; else c.rem1 = left;
+      if (left < L.t) {
+        c.partial = 1;
+        if (L.slot == 0) c.rem0 = left; else c.rem1 = left;
+      }
     }
   }
 }
 
+CUTT_HD uint32_t skew_bytes(const Skew& s, uint32_t pos) {
+  return ((pos >> s.shift) & s.mask) * s.unitB;
+}
+
 // Row `r` of one side: mixed-radix decode over the side's row dimensions.
-CUTT_HD RowEnt make_row(const Side& S, uint32_t r) {
-  RowEnt e;
-  e.goff = 0;
-  e.soff = 0;
-  e.c0 = 0;
-  e.c1 = 0;
+CUTT_HD void make_row(const Side& S, uint32_t r, int64_t& goff, uint32_t& soffB, RowCoord& rc) {
+  goff = 0;
+  soffB = 0;
+  rc.c0 = 0;
+  rc.c1 = 0;
   for (uint32_t k = 0; k < S.nRowDims; k++) {
     const RowDim& R = S.rowDim[k];
     uint32_t cc = r % R.ext;
     r /= R.ext;
-    e.goff += (int64_t)cc * R.gstride;
-    e.soff += cc * R.sstride;
-    if (R.slot == 0) e.c0 = (uint16_t)cc;
-    if (R.slot == 1) e.c1 = (uint16_t)cc;
+    goff += (int64_t)cc * R.gstride;
+    soffB += cc * R.sstrideB + skew_bytes(R.skew, cc);
+    if (R.slot == 0) rc.c0 = (uint16_t)(cc * R.cmul);
+    if (R.slot == 1) rc.c1 = (uint16_t)(cc * R.cmul);
   }
-  return e;
 }
 
 // Valid run length of a side in the tile described by `c`.
 CUTT_HD uint32_t run_valid(const Side& S, const TileCtx& c) {
   if (S.runSlot < 0) return S.run;
-  uint32_t v = S.runPrefix * (S.runSlot == 0 ? c.rem0 : c.rem1);
+  uint32_t rem = S.runSlot == 0 ? c.rem0 : c.rem1;
+  if (rem == 0xffffffffu) return S.run;
+  uint32_t v = S.runPrefix * rem;
   return v < S.run ? v : S.run;
 }
 
-// Shared-memory offset of position q along the output side's run.
+// Shared-memory byte offset of position q along the output side's run.
 CUTT_HD uint32_t out_run_soff(const TileDesc& D, uint32_t q) {
   uint32_t s = 0;
   for (uint32_t k = 0; k + 1 < D.nOutRunDims; k++) {
     const RunDim& R = D.outRunDim[k];
     uint32_t nq = fdiv(q, R.div);
-    s += (q - nq * R.div.d) * R.sstride;
+    uint32_t cc = q - nq * R.div.d;
+    s += cc * R.sstrideB + skew_bytes(R.skew, cc);
     q = nq;
   }
-  // the last run dimension needs no modulo
-  return s + q * D.outRunDim[D.nOutRunDims - 1].sstride;
+  const RunDim& R = D.outRunDim[D.nOutRunDims - 1];  // the last run dimension needs no modulo
+  return s + q * R.sstrideB + skew_bytes(R.skew, q);
+}
+
+// Fills the shared-memory tables; thread `tid` of `nthreads` does its share.
+template <bool WIDE>
+CUTT_HD void build_tables(const TileDesc& D, unsigned char* tables, uint32_t tid, uint32_t nthreads) {
+  typedef typename RowEntSel<WIDE>::type Ent;
+  const TableLayout L = table_layout(D);
+  Ent* tabIn = reinterpret_cast<Ent*>(tables + L.tabIn);
+  Ent* tabOut = reinterpret_cast<Ent*>(tables + L.tabOut);
+  RowCoord* coIn = reinterpret_cast<RowCoord*>(tables + L.coordIn);
+  RowCoord* coOut = reinterpret_cast<RowCoord*>(tables + L.coordOut);
+  uint32_t* qtab = reinterpret_cast<uint32_t*>(tables + L.qtab);
+  for (uint32_t r = tid; r < D.in.nrows; r += nthreads) {
+    int64_t g; uint32_t s; RowCoord rc;
+    make_row(D.in, r, g, s, rc);
+    tabIn[r].goff = (decltype(tabIn[r].goff))g;
+    tabIn[r].soffB = s;
+    coIn[r] = rc;
+  }
+  for (uint32_t r = tid; r < D.out.nrows; r += nthreads) {
+    int64_t g; uint32_t s; RowCoord rc;
+    make_row(D.out, r, g, s, rc);
+    tabOut[r].goff = (decltype(tabOut[r].goff))g;
+    tabOut[r].soffB = s;
+    coOut[r] = rc;
+  }
+  for (uint32_t q = tid; q < D.out.run; q += nthreads) qtab[q] = out_run_soff(D, q);
 }
 
 }  // namespace cuttb

@@ -1,11 +1,12 @@
 // Per-thread phases of the tiled permutation kernel.  The same functions run on the
 // device (inside permute_tiles_kernel, one call per thread) and on the host (inside
 // the plan interpreter that the CPU tests use to check descriptors without a GPU):
-// only the three copy primitives differ.
+// only the copy primitives differ.
 //
 // Phase "load":  global input  -> shared tile (contiguous runs, shared memory in input order)
 // Phase "store": shared tile   -> global output (contiguous runs of the output, gathered
-//                from shared memory through the output run's strides)
+//                from shared memory through the output run's offset table, V x W blocks
+//                transposed in registers)
 //
 // Role in the reference: these two phases are what transposePacked / transposePackedSplit /
 // transposeTiled / transposeTiledCopy (src/cuttkernel.cu:38-426) do between their two
@@ -16,110 +17,159 @@
 
 namespace cuttb {
 
-template <int BYTES> struct VecT;
-template <> struct VecT<4>  { uint32_t w[1]; };
-template <> struct VecT<8>  { uint32_t w[2]; };
-template <> struct VecT<16> { uint32_t w[4]; };
+// Shared-memory address: a 32-bit shared-window address on the device, a pointer on the host.
+#if defined(__CUDA_ARCH__)
+typedef uint32_t sptr_t;
+#else
+typedef unsigned char* sptr_t;
+#endif
 
 // global -> shared, BYTES in {4, 8, 16}; asynchronous on the device.
 template <int BYTES>
-CUTT_HD void copy_g2s(unsigned char* sdst, const unsigned char* gsrc) {
+CUTT_HD void copy_g2s(sptr_t sdst, const unsigned char* gsrc) {
 #if defined(__CUDA_ARCH__)
-  unsigned int saddr = (unsigned int)__cvta_generic_to_shared(sdst);
   if (BYTES == 16) {
-    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;\n" ::"r"(saddr), "l"(gsrc) : "memory");
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;\n" ::"r"(sdst), "l"(gsrc) : "memory");
   } else {
-    asm volatile("cp.async.ca.shared.global [%0], [%1], %2;\n" ::"r"(saddr), "l"(gsrc), "n"(BYTES) : "memory");
+    asm volatile("cp.async.ca.shared.global [%0], [%1], %2;\n" ::"r"(sdst), "l"(gsrc), "n"(BYTES) : "memory");
   }
 #else
   memcpy(sdst, gsrc, BYTES);
 #endif
 }
 
+// shared -> registers: BYTES/4 32-bit words
 template <int BYTES>
-CUTT_HD void lds(void* dst, const unsigned char* ssrc) {
+CUTT_HD void lds(uint32_t* dst, sptr_t ssrc) {
 #if defined(__CUDA_ARCH__)
-  if (BYTES == 4) *(uint32_t*)dst = *(const uint32_t*)ssrc;
-  else if (BYTES == 8) *(uint2*)dst = *(const uint2*)ssrc;
-  else *(uint4*)dst = *(const uint4*)ssrc;
+  if (BYTES == 4) {
+    asm volatile("ld.shared.u32 %0, [%1];\n" : "=r"(dst[0]) : "r"(ssrc));
+  } else if (BYTES == 8) {
+    asm volatile("ld.shared.v2.u32 {%0, %1}, [%2];\n" : "=r"(dst[0]), "=r"(dst[1]) : "r"(ssrc));
+  } else {
+    asm volatile("ld.shared.v4.u32 {%0, %1, %2, %3}, [%4];\n"
+                 : "=r"(dst[0]), "=r"(dst[1]), "=r"(dst[2]), "=r"(dst[3]) : "r"(ssrc));
+  }
 #else
   memcpy(dst, ssrc, BYTES);
 #endif
 }
 
+// registers -> global
 template <int BYTES>
-CUTT_HD void stg(unsigned char* gdst, const void* src) {
+CUTT_HD void stg(unsigned char* gdst, const uint32_t* src) {
 #if defined(__CUDA_ARCH__)
-  if (BYTES == 4) *(uint32_t*)gdst = *(const uint32_t*)src;
-  else if (BYTES == 8) *(uint2*)gdst = *(const uint2*)src;
-  else *(uint4*)gdst = *(const uint4*)src;
+  if (BYTES == 4) *reinterpret_cast<uint32_t*>(gdst) = src[0];
+  else if (BYTES == 8) *reinterpret_cast<uint2*>(gdst) = make_uint2(src[0], src[1]);
+  else *reinterpret_cast<uint4*>(gdst) = make_uint4(src[0], src[1], src[2], src[3]);
 #else
   memcpy(gdst, src, BYTES);
 #endif
 }
 
-template <int ELT, int W>
-CUTT_HD void tile_load(const TileDesc& D, const TileCtx& c, const RowEnt* tab,
-                       unsigned char* sbuf, const unsigned char* gin, uint32_t tid) {
+template <int ELT, int W, bool WIDE, bool PARTIAL>
+CUTT_HD void tile_load_impl(const TileDesc& D, const TileCtx& c, const unsigned char* tables,
+                            sptr_t sbuf, const unsigned char* gin, uint32_t tid) {
+  typedef typename RowEntSel<WIDE>::type Ent;
   const Side& S = D.in;
+  const TableLayout L = table_layout(D);
+  const Ent* tab = reinterpret_cast<const Ent*>(tables + L.tabIn);
+  const RowCoord* co = reinterpret_cast<const RowCoord*>(tables + L.coordIn);
   const uint32_t tq = tid & (S.tq - 1);
   const uint32_t tr = tid >> S.tqShift;
   const uint32_t Tr = D.nthreads >> S.tqShift;
-  const uint32_t valid = run_valid(S, c);
-  const uint32_t rem0 = c.rem0, rem1 = c.rem1;
-  const unsigned char* gbase = gin + c.inOff * ELT;
+  const uint32_t valid = PARTIAL ? run_valid(S, c) : S.run;
+  const uint32_t q0 = tq * W;
+  if (q0 >= valid) return;
   const uint32_t qstep = S.tq * W;
+  const uint32_t qstepB = qstep * ELT;
+  const unsigned char* gbase = gin + (c.inOff + q0) * ELT;
+  const sptr_t sbase = sbuf + q0 * ELT;
   for (uint32_t row = tr; row < S.nrows; row += Tr) {
-    const RowEnt e = tab[row];
-    if (e.c0 < rem0 && e.c1 < rem1) {
-      const unsigned char* g = gbase + e.goff * ELT;
-      unsigned char* s = sbuf + (size_t)e.soff * ELT;
-      for (uint32_t q = tq * W; q < valid; q += qstep)
-        copy_g2s<ELT * W>(s + (size_t)q * ELT, g + (size_t)q * ELT);
+    if (PARTIAL) {
+      const RowCoord rc = co[row];
+      if (!(rc.c0 < c.rem0 && rc.c1 < c.rem1)) continue;
+    }
+    const Ent e = tab[row];
+    const unsigned char* g = gbase + (WIDE ? (int64_t)e.goff * ELT : (int64_t)((uint64_t)(uint32_t)e.goff * ELT));
+    sptr_t s = sbase + e.soffB;
+    copy_g2s<ELT * W>(s, g);
+    for (uint32_t q = q0 + qstep; q < valid; q += qstep) {
+      g += qstepB;
+      s += qstepB;
+      copy_g2s<ELT * W>(s, g);
     }
   }
 }
 
-template <int ELT, int W>
-CUTT_HD void tile_store(const TileDesc& D, const TileCtx& c, const RowEnt* tab,
-                        const unsigned char* sbuf, unsigned char* gout, uint32_t tid) {
+template <int ELT, int W, int V, bool WIDE, bool PARTIAL>
+CUTT_HD void tile_store_impl(const TileDesc& D, const TileCtx& c, const unsigned char* tables,
+                             sptr_t sbuf, unsigned char* gout, uint32_t tid) {
+  typedef typename RowEntSel<WIDE>::type Ent;
+  constexpr int EW = ELT / 4;  // 32-bit words per element
   const Side& S = D.out;
+  const TableLayout L = table_layout(D);
+  const Ent* tab = reinterpret_cast<const Ent*>(tables + L.tabOut);
+  const RowCoord* co = reinterpret_cast<const RowCoord*>(tables + L.coordOut);
+  const uint32_t* qtab = reinterpret_cast<const uint32_t*>(tables + L.qtab);
   const uint32_t tq = tid & (S.tq - 1);
   const uint32_t tr = tid >> S.tqShift;
   const uint32_t Tr = D.nthreads >> S.tqShift;
-  const uint32_t valid = run_valid(S, c);
-  const uint32_t rem0 = c.rem0, rem1 = c.rem1;
-  unsigned char* gbase = gout + c.outOff * ELT;
+  const uint32_t valid = PARTIAL ? run_valid(S, c) : S.run;
   const uint32_t qstep = S.tq * W;
+  const bool contig = (W > 1) && (V == 1) && D.smemGatherContig;
+  const int64_t vstepB = D.vstep * ELT;
+  unsigned char* gbase = gout + c.outOff * ELT;
   for (uint32_t q = tq * W; q < valid; q += qstep) {
     uint32_t so[W];
-    so[0] = out_run_soff(D, q);
-    if (W > 1) {
-      if (D.smemGatherContig) {
 #pragma unroll
-        for (int i = 1; i < W; i++) so[i] = so[0] + i;
-      } else {
-#pragma unroll
-        for (int i = 1; i < W; i++) so[i] = out_run_soff(D, q + i);
-      }
-    }
+    for (int i = 0; i < W; i++) so[i] = qtab[q + i];
     unsigned char* gq = gbase + (size_t)q * ELT;
-#pragma unroll 4
+#pragma unroll 2
     for (uint32_t row = tr; row < S.nrows; row += Tr) {
-      const RowEnt e = tab[row];
-      if (e.c0 < rem0 && e.c1 < rem1) {
-        VecT<ELT * W> v;
-        if (W > 1 && D.smemGatherContig) {
-          lds<ELT * W>(&v, sbuf + (size_t)(e.soff + so[0]) * ELT);
-        } else {
+      if (PARTIAL) {
+        const RowCoord rc = co[row];
+        if (!(rc.c0 < c.rem0 && rc.c1 < c.rem1)) continue;
+      }
+      const Ent e = tab[row];
+      const sptr_t sb = sbuf + e.soffB;
+      unsigned char* g = gq + (WIDE ? (int64_t)e.goff * ELT : (int64_t)((uint64_t)(uint32_t)e.goff * ELT));
+      if (contig) {
+        uint32_t x[W * EW];
+        lds<ELT * W>(x, sb + so[0]);
+        stg<ELT * W>(g, x);
+      } else {
+        uint32_t x[W][V * EW];
 #pragma unroll
-          for (int i = 0; i < W; i++)
-            lds<ELT>(&v.w[i * (ELT / 4)], sbuf + (size_t)(e.soff + so[i]) * ELT);
+        for (int i = 0; i < W; i++) lds<ELT * V>(x[i], sb + so[i]);
+#pragma unroll
+        for (int j = 0; j < V; j++) {
+          uint32_t y[W * EW];
+#pragma unroll
+          for (int i = 0; i < W; i++) {
+#pragma unroll
+            for (int w = 0; w < EW; w++) y[i * EW + w] = x[i][j * EW + w];
+          }
+          stg<ELT * W>(g, y);
+          g += vstepB;
         }
-        stg<ELT * W>(gq + e.goff * ELT, &v);
       }
     }
   }
+}
+
+template <int ELT, int W, bool WIDE>
+CUTT_HD void tile_load(const TileDesc& D, const TileCtx& c, const unsigned char* tables,
+                       sptr_t sbuf, const unsigned char* gin, uint32_t tid) {
+  if (c.partial) tile_load_impl<ELT, W, WIDE, true>(D, c, tables, sbuf, gin, tid);
+  else tile_load_impl<ELT, W, WIDE, false>(D, c, tables, sbuf, gin, tid);
+}
+
+template <int ELT, int W, int V, bool WIDE>
+CUTT_HD void tile_store(const TileDesc& D, const TileCtx& c, const unsigned char* tables,
+                        sptr_t sbuf, unsigned char* gout, uint32_t tid) {
+  if (c.partial) tile_store_impl<ELT, W, V, WIDE, true>(D, c, tables, sbuf, gout, tid);
+  else tile_store_impl<ELT, W, V, WIDE, false>(D, c, tables, sbuf, gout, tid);
 }
 
 }  // namespace cuttb

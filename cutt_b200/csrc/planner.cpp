@@ -60,12 +60,15 @@ bool problem_from_cutt(int rank, const int* dim, const int* perm, int elt, Probl
   return canonicalize(rank, d.data(), is.data(), os.data(), elt, -1, P);
 }
 
-// chunk of about `want` elements out of d, with equal-sized chunks except possibly the last
-static int64_t balanced_chunk(int64_t d, int64_t want) {
+// chunk of about `want` elements out of d, with equal-sized chunks except possibly the last;
+// chunks are rounded up to a multiple of `mult` (vector width) when that is small against them
+static int64_t balanced_chunk(int64_t d, int64_t want, int64_t mult = 1) {
   if (want >= d) return d;
   if (want < 1) want = 1;
   int64_t n = ceil_div(d, want);
-  return ceil_div(d, n);
+  int64_t c = ceil_div(d, n);
+  if (mult > 1 && c >= 2 * mult) c = ceil_div(c, mult) * mult;
+  return c < d ? c : d;
 }
 
 static uint32_t ilog2_exact(uint32_t x) { uint32_t l = 0; while ((1u << l) < x) l++; return l; }
@@ -112,7 +115,7 @@ bool build_tile(const Problem& P, const TileParams& tp, const DeviceInfo& dev, C
       if (P.d[j] <= want + want / 2 && P.d[j] <= kMaxChunk) {
         t[j] = P.d[j]; cum *= P.d[j]; expect *= P.d[j];
       } else {
-        t[j] = balanced_chunk(P.d[j], std::min(want, kMaxChunk));
+        t[j] = balanced_chunk(P.d[j], std::min(want, kMaxChunk), 16 / elt);
         break;
       }
     }
@@ -130,7 +133,7 @@ bool build_tile(const Problem& P, const TileParams& tp, const DeviceInfo& dev, C
       if (P.d[j] <= want + want / 2 && P.d[j] <= kMaxChunk) {
         t[j] = P.d[j]; cum *= P.d[j]; expect *= P.d[j];
       } else {
-        t[j] = balanced_chunk(P.d[j], std::min(want, kMaxChunk));
+        t[j] = balanced_chunk(P.d[j], std::min(want, kMaxChunk), 16 / elt);
         break;
       }
     }
@@ -154,7 +157,7 @@ bool build_tile(const Problem& P, const TileParams& tp, const DeviceInfo& dev, C
     }
     if (pick < 0) break;
     int64_t want = ceil_div(vtarget * t[pick], V);
-    int64_t nt = balanced_chunk(P.d[pick], std::min(want, kMaxChunk));
+    int64_t nt = balanced_chunk(P.d[pick], std::min(want, kMaxChunk), 16 / elt);
     if (nt <= t[pick]) break;
     t[pick] = nt;
     if (nt < P.d[pick]) break;  // chunked: the target is met (or the chunk limit was hit)
@@ -239,7 +242,29 @@ bool build_tile(const Problem& P, const TileParams& tp, const DeviceInfo& dev, C
   const uint32_t win = side_vec(true);
   const uint32_t wout = side_vec(false);
 
-  // shared-memory strides: input order, padded where the output run starts
+  // 64-bit row offsets are needed when a tile spans 2^32 elements or more on either side
+  bool wide = false;
+  {
+    int64_t spanIn = 1, spanOut = 1;
+    for (int j = 0; j < r; j++) { spanIn += (t[j] - 1) * P.is[j]; spanOut += (t[j] - 1) * P.os[j]; }
+    wide = spanIn >= (1ll << 32) || spanOut >= (1ll << 32);
+  }
+
+  // register blocking of the output side along dimension 0
+  uint32_t V = 1;
+  if (!wide && r > 0 && t[0] > 1 && inRun[0] && !outRun[0] && P.is[0] == 1) {
+    for (int v = std::min(16, tp.maxVBytes) / elt; v > 1; v /= 2) {
+      if (t[0] % v == 0 && P.d[0] % v == 0) { V = (uint32_t)v; break; }
+    }
+  }
+  D.vblk = V;
+  D.vstep = P.os[0];
+
+  // shared-memory strides (elements): input order; rows aligned to A elements; the
+  // dimension that starts the output run gets an odd stride (in units of A) and a skew
+  const int64_t A = std::max(win, V);
+  Skew skewOf[kMaxDims];
+  for (int j = 0; j < r; j++) { skewOf[j].shift = 0; skewOf[j].mask = 0; skewOf[j].unitB = 0; }
   int64_t ss[kMaxDims];
   {
     int p0 = nOutRun > 0 ? outRunOrder[0] : -1;
@@ -247,15 +272,27 @@ bool build_tile(const Problem& P, const TileParams& tp, const DeviceInfo& dev, C
     for (int j = 0; j < r; j++) {
       if (t[j] == 1) { ss[j] = 0; continue; }
       if (!inRun[j]) {
-        // rows start on a multiple of the input vector width
-        s = ceil_div(s, (int64_t)win) * win;
-        if (j == p0) { while (((s / win) & 1) == 0) s += win; }
+        if (j == p0) {
+          // lanes per shared-memory wavefront for one output-side access
+          uint32_t G = 128u / (V * elt);
+          if (wout > 1 && t[j] > (int64_t)G) {
+            skewOf[j].shift = ilog2_exact(G);
+            skewOf[j].mask = wout - 1;
+            skewOf[j].unitB = (uint32_t)(A * elt);
+            s += (int64_t)(wout - 1) * A;  // room for the skew inside every row's pitch
+          }
+          s = ceil_div(s, A) * A;
+          while (((s / A) & 1) == 0) s += A;
+        } else {
+          s = ceil_div(s, A) * A;
+        }
       }
       ss[j] = s;
-      s *= t[j];
+      s = s * t[j];
     }
     int64_t elems = 1;
-    for (int j = 0; j < r; j++) if (t[j] > 1) elems += (t[j] - 1) * ss[j];
+    for (int j = 0; j < r; j++)
+      if (t[j] > 1) elems += (t[j] - 1) * ss[j] + (skewOf[j].mask ? (int64_t)skewOf[j].mask * A : 0);
     if (elems > (int64_t)dev.maxSmemPerBlock / elt) return false;
     D.tileElems = (uint32_t)elems;
     D.stageBytes = (uint32_t)((elems * elt + 15) / 16 * 16);
@@ -267,6 +304,7 @@ bool build_tile(const Problem& P, const TileParams& tp, const DeviceInfo& dev, C
     int last = input ? inRunLast : outRunLast;
     int64_t run = 1, prefix = 1;
     for (int j = 0; j < r; j++) if (inrun[j]) { run *= t[j]; if (j != last) prefix *= t[j]; }
+    if (run > 16384) return false;
     S.run = (uint32_t)run;
     S.runPrefix = (uint32_t)prefix;
     S.runSlot = last >= 0 ? slotOf[last] : -1;
@@ -276,11 +314,14 @@ bool build_tile(const Problem& P, const TileParams& tp, const DeviceInfo& dev, C
     for (int j = 0; j < r; j++) {
       if (t[j] == 1 || inrun[j]) continue;
       RowDim& R = S.rowDim[S.nRowDims++];
-      R.ext = (uint32_t)t[j];
-      R.sstride = (uint32_t)ss[j];
-      R.gstride = input ? P.is[j] : P.os[j];
+      const int64_t blk = (!input && j == 0) ? V : 1;
+      R.ext = (uint32_t)(t[j] / blk);
+      R.sstrideB = (uint32_t)(ss[j] * blk * elt);
+      R.gstride = (input ? P.is[j] : P.os[j]) * blk;
       R.slot = slotOf[j];
-      nrows *= t[j];
+      R.cmul = (uint32_t)blk;
+      R.skew = skewOf[j];
+      nrows *= R.ext;
     }
     if (nrows > 8192) return false;
     S.nrows = (uint32_t)nrows;
@@ -289,8 +330,7 @@ bool build_tile(const Problem& P, const TileParams& tp, const DeviceInfo& dev, C
   };
   if (!fill_side(D.in, true)) return false;
   if (!fill_side(D.out, false)) return false;
-  D.tableBytes = (D.in.nrows + D.out.nrows) * (uint32_t)sizeof(RowEnt);
-  if (D.tableBytes > 48 * 1024) return false;
+  D.wide = wide ? 1 : 0;
 
   // gather description of the output run
   D.nOutRunDims = 0;
@@ -298,21 +338,26 @@ bool build_tile(const Problem& P, const TileParams& tp, const DeviceInfo& dev, C
     int j = outRunOrder[k];
     RunDim& R = D.outRunDim[D.nOutRunDims++];
     R.div = make_fastdiv((uint32_t)t[j]);
-    R.sstride = (uint32_t)ss[j];
+    R.sstrideB = (uint32_t)(ss[j] * elt);
+    R.skew = skewOf[j];
   }
   if (D.nOutRunDims == 0) {
     D.outRunDim[0].div = make_fastdiv(1);
-    D.outRunDim[0].sstride = 0;
+    D.outRunDim[0].sstrideB = 0;
+    D.outRunDim[0].skew = skewOf[0];
+    D.outRunDim[0].skew.mask = 0;
     D.nOutRunDims = 1;
   }
   D.smemGatherContig = 0;
-  if (wout > 1 && nOutRun > 0) {
+  if (wout > 1 && nOutRun > 0 && V == 1) {
     int j0 = outRunOrder[0];
-    bool ok = ss[j0] == 1 && t[j0] % wout == 0;
+    bool ok = ss[j0] == 1 && t[j0] % wout == 0 && skewOf[j0].mask == 0;
     for (int j = 0; j < r && ok; j++)
-      if (j != j0 && t[j] > 1 && ss[j] % wout != 0) ok = false;
+      if (j != j0 && t[j] > 1 && (ss[j] % wout != 0 || (skewOf[j].unitB / elt) % wout != 0)) ok = false;
     D.smemGatherContig = ok ? 1 : 0;
   }
+  D.tableBytes = table_layout(D).total;
+  if (D.tableBytes > 64 * 1024) return false;
 
   // loop dimensions
   {
@@ -353,9 +398,9 @@ bool build_tile(const Problem& P, const TileParams& tp, const DeviceInfo& dev, C
   char buf[512];
   std::string ts;
   for (int j = 0; j < r; j++) { snprintf(buf, sizeof buf, "%s%lld", j ? "," : "", (long long)t[j]); ts += buf; }
-  snprintf(buf, sizeof buf, "tiles t=[%s] in=%ux%u/v%u out=%ux%u/v%u smem=%d st=%d lo=%d nt=%d",
-           ts.c_str(), D.in.nrows, D.in.run, D.in.vec, D.out.nrows, D.out.run, D.out.vec,
-           out.smemBytes, D.stages, tp.loopOrder, tp.nthreads);
+  snprintf(buf, sizeof buf, "tiles t=[%s] in=%ux%u/w%u out=%ux%u/w%u V%u%s smem=%d st=%d lo=%d nt=%d",
+           ts.c_str(), D.in.nrows, D.in.run, D.in.vec, D.out.nrows, D.out.run, D.out.vec, D.vblk,
+           D.wide ? " wide" : "", out.smemBytes, D.stages, tp.loopOrder, tp.nthreads);
   out.label = buf;
   out.cost = model_cost(P, out, dev);
   return true;

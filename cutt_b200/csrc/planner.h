@@ -56,7 +56,8 @@ struct TileParams {
   int extend = 0;              // which dimension grows when the tile is below target: 0 next in output order, 1 next in input order
   int nthreads = 256;
   int stages = 2;
-  int maxVecBytes = 16;
+  int maxVecBytes = 16;        // widest global access
+  int maxVBytes = 16;          // widest shared-memory vector of the register-blocked store side
   int loopOrder = 0;           // tile index runs fastest along 0: input order, 1: output order
 };
 

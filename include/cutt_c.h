@@ -51,7 +51,7 @@ int cutt_c_plan_candidate(unsigned int* handle, int rank, const int* dim, const 
 int cutt_c_plan_params(unsigned int* handle, int rank, const int* dim, const int* permutation,
                        size_t sizeofType, void* stream, int method, unsigned tinBytes,
                        unsigned toutBytes, unsigned vtargetBytes, int extend, int loopOrder,
-                       int maxVecBytes, int nthreads, int stages);
+                       int maxVecBytes, int maxVBytes, int nthreads, int stages);
 
 /* Convenience for callers holding HOST buffers: plans (cost model, cached), copies hin to the
  * device, executes, copies the result to hout, and synchronises.  Scratch device buffers are

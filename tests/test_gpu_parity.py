@@ -74,7 +74,7 @@ def test_every_candidate(native, oracle_mod, dims, perm):
 
 
 @pytest.mark.parametrize("kw", [
-    dict(max_vec=4), dict(max_vec=8), dict(stages=1), dict(nthreads=128), dict(nthreads=512),
+    dict(max_vec=4, max_v=4), dict(max_vec=8, max_v=8), dict(max_v=4), dict(max_vec=4), dict(stages=1), dict(nthreads=128), dict(nthreads=512),
     dict(nthreads=64, stages=1), dict(tin=128, tout=1024), dict(tin=1024, tout=128, vtarget=32768),
     dict(loop_order=1, extend=1), dict(method=3),
 ])

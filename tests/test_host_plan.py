@@ -1,0 +1,129 @@
+"""CPU tests of the plan builder and the kernels' index arithmetic.
+
+libcutt_hostcheck.so (test-only) runs a plan's tile descriptor on host memory by calling
+the same per-thread load/store phase functions the CUDA kernel calls.  Every result is
+compared bit for bit with the CPU oracle."""
+import ctypes
+import itertools
+import json
+import os
+import random
+
+import numpy as np
+import pytest
+
+from helpers import README_CASE, TEST3_CASES, TEST4_CASE, dims_of_test1, random_case, raw_bits, volume
+
+
+@pytest.fixture(scope="module")
+def hc(native):
+    path = os.path.join(os.path.dirname(native.lib_path()), "libcutt_hostcheck.so")
+    lib = ctypes.CDLL(path)
+    ip = ctypes.POINTER(ctypes.c_int)
+    lib.cutt_hostcheck_num_candidates.argtypes = [ctypes.c_int, ip, ip, ctypes.c_int]
+    lib.cutt_hostcheck_run.argtypes = [ctypes.c_int, ip, ip, ctypes.c_int, ctypes.c_int,
+                                       ctypes.c_void_p, ctypes.c_void_p, ctypes.c_char_p, ctypes.c_int]
+    lib.cutt_hostcheck_run_params.argtypes = [ctypes.c_int, ip, ip, ctypes.c_int, ctypes.c_uint, ctypes.c_uint,
+                                              ctypes.c_uint, ctypes.c_int, ctypes.c_int, ctypes.c_int, ctypes.c_int,
+                                              ctypes.c_int, ctypes.c_void_p, ctypes.c_void_p, ctypes.c_char_p, ctypes.c_int]
+    lib.cutt_hostcheck_fastdiv.restype = ctypes.c_longlong
+    lib.cutt_hostcheck_fastdiv.argtypes = [ctypes.c_uint, ctypes.c_ulonglong, ctypes.c_ulonglong]
+    return lib
+
+
+def _iarr(v):
+    return (ctypes.c_int * len(v))(*v)
+
+
+def _check_candidates(hc, oracle_mod, dims, perm, elts=(4, 8), max_cands=None, seed=0):
+    for elt in elts:
+        n = hc.cutt_hostcheck_num_candidates(len(dims), _iarr(dims), _iarr(perm), elt)
+        assert n > 0, (dims, perm, elt)
+        a = raw_bits(volume(dims), elt, seed + elt)
+        want = oracle_mod.transpose_blocked(dims, perm, a)
+        idx = range(n) if max_cands is None or n <= max_cands else sorted(random.Random(seed).sample(range(n), max_cands))
+        for i in idx:
+            out = np.full_like(a, 0xAB)
+            lab = ctypes.create_string_buffer(2048)
+            rc = hc.cutt_hostcheck_run(len(dims), _iarr(dims), _iarr(perm), elt, i, a.ctypes.data,
+                                       out.ctypes.data, lab, 2048)
+            assert rc == 0, (rc, dims, perm, elt, i)
+            assert np.array_equal(out, want), (dims, perm, elt, i, lab.value.decode())
+
+
+def test_fastdiv(hc):
+    for d in [1, 2, 3, 5, 7, 31, 32, 33, 549, 1000, 14142, 65535, 65536, 65537,
+              2**31 - 1, 2**31, 2**31 + 1, 2**32 - 1]:
+        assert hc.cutt_hostcheck_fastdiv(d, 2**32 - 1, 99991) == 0, d
+
+
+@pytest.mark.parametrize("rank", [2, 3, 4, 5])
+def test_all_permutations_small(hc, oracle_mod, rank):
+    dims = dims_of_test1(rank)
+    for perm in itertools.permutations(range(rank)):
+        _check_candidates(hc, oracle_mod, dims, list(perm), max_cands=3, seed=rank)
+
+
+def test_all_permutations_rank6_sampled(hc, oracle_mod):
+    dims = dims_of_test1(6)
+    perms = list(itertools.permutations(range(6)))
+    for perm in random.Random(6).sample(perms, 40):
+        _check_candidates(hc, oracle_mod, dims, list(perm), elts=(4,), max_cands=2, seed=6)
+
+
+@pytest.mark.parametrize("dims,perm", [README_CASE, TEST4_CASE] + [c for c in TEST3_CASES if volume(c[0]) < 3_000_000])
+def test_reference_shapes(hc, oracle_mod, dims, perm):
+    _check_candidates(hc, oracle_mod, dims, perm, max_cands=4, seed=1)
+
+
+@pytest.mark.parametrize("dims,perm", [
+    ([129, 130], [1, 0]), ([1000, 3], [1, 0]), ([3, 1000], [1, 0]), ([300, 301], [1, 0]),
+    ([64, 48, 20], [2, 1, 0]), ([19, 16, 39], [2, 1, 0]), ([8, 6, 30, 50], [3, 0, 2, 1]),
+    ([4, 3, 5, 40, 7, 24], [4, 1, 5, 0, 3, 2]), ([130, 4, 70], [0, 2, 1]), ([260, 70, 3], [1, 2, 0]),
+    ([2, 2, 2, 2, 2, 2, 2, 2, 2, 2, 2], [10, 9, 8, 7, 6, 5, 4, 3, 2, 1, 0]),
+    ([512, 66, 5], [1, 0, 2]), ([70, 66, 6, 4], [1, 0, 3, 2]),
+])
+def test_every_candidate(hc, oracle_mod, dims, perm):
+    _check_candidates(hc, oracle_mod, dims, perm, seed=3)
+
+
+def test_random_shapes(hc, oracle_mod):
+    rng = random.Random(77)
+    for rank in range(2, 13):
+        for rep in range(5):
+            dims, perm = random_case(rng, rank, 120_000)
+            _check_candidates(hc, oracle_mod, dims, perm, max_cands=4, seed=rank * 10 + rep)
+
+
+@pytest.mark.parametrize("kw", [
+    dict(mv=4, mV=4), dict(mv=8, mV=8), dict(mv=16, mV=4), dict(mv=4, mV=16), dict(nt=128), dict(nt=512),
+    dict(tin=128, tout=1024), dict(tin=1024, tout=128, vt=32768), dict(lo=1, ext=1), dict(tin=64, tout=64, vt=2048),
+])
+def test_forced_parameters(hc, oracle_mod, kw):
+    rng = random.Random(5)
+    cases = [([64, 48, 20], [2, 1, 0]), ([130, 257], [1, 0]), ([8, 6, 30, 50], [3, 0, 2, 1]),
+             ([256, 64, 12], [1, 0, 2]), ([96, 40, 33], [0, 2, 1]), ([132, 260, 3], [1, 0, 2])]
+    cases += [random_case(rng, r, 100_000) for r in (3, 4, 5, 6)]
+    for dims, perm in cases:
+        if perm == sorted(perm):
+            continue
+        for elt in (4, 8):
+            a = raw_bits(volume(dims), elt, 11)
+            out = np.full_like(a, 0xCD)
+            lab = ctypes.create_string_buffer(2048)
+            rc = hc.cutt_hostcheck_run_params(
+                len(dims), _iarr(dims), _iarr(perm), elt, kw.get("tin", 256), kw.get("tout", 256),
+                kw.get("vt", 16384), kw.get("ext", 0), kw.get("lo", 0), kw.get("mv", 16), kw.get("mV", 16),
+                kw.get("nt", 256), a.ctypes.data, out.ctypes.data, lab, 2048)
+            assert rc == 0, (rc, dims, perm, kw)
+            assert np.array_equal(out, oracle_mod.transpose_blocked(dims, perm, a)), (dims, perm, elt, lab.value.decode())
+
+
+def test_candidate_descriptions_are_json(hc):
+    dims, perm = [64, 48, 20], [2, 1, 0]
+    a = raw_bits(volume(dims), 4, 1)
+    out = np.empty_like(a)
+    lab = ctypes.create_string_buffer(2048)
+    assert hc.cutt_hostcheck_run(3, _iarr(dims), _iarr(perm), 4, 0, a.ctypes.data, out.ctypes.data, lab, 2048) == 0
+    d = json.loads(lab.value.decode())
+    assert d["fused_dims"] == [64, 48, 20] and d["elt"] == 4 and d["num_tiles"] >= 1
