@@ -15,15 +15,16 @@ template <int ELT, int WIN, int WOUT, int V, bool WIDE>
 static void run_desc(const TileDesc& D, const unsigned char* in, unsigned char* out) {
   std::vector<unsigned char> tables(D.tableBytes + 16);
   for (uint32_t tid = 0; tid < D.nthreads; tid++) build_tables<WIDE>(D, tables.data(), tid, D.nthreads);
+  const Tables<WIDE> T = make_tables<WIDE>(D, tables.data());
   std::vector<unsigned char> sbuf(D.stageBytes);
   for (uint32_t tile = 0; tile < D.numTiles; tile++) {
     TileCtx c;
     decode_tile(D, tile, c);
     memset(sbuf.data(), 0xEE, sbuf.size());
     for (uint32_t tid = 0; tid < D.nthreads; tid++)
-      tile_load<ELT, WIN, WIDE>(D, c, tables.data(), sbuf.data(), in, tid);
+      tile_load<ELT, WIN, WIDE>(D, c, T, sbuf.data(), in, tid);
     for (uint32_t tid = 0; tid < D.nthreads; tid++)
-      tile_store<ELT, WOUT, V, WIDE>(D, c, tables.data(), sbuf.data(), out, tid);
+      tile_store<ELT, WOUT, V, WIDE>(D, c, T, sbuf.data(), out, tid);
   }
 }
 

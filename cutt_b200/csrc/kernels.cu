@@ -31,44 +31,53 @@ permute_tiles_kernel(const __grid_constant__ TileDesc D, const unsigned char* __
                      const __grid_constant__ PeerPtrs outs) {
   extern __shared__ __align__(16) unsigned char smem[];
   const uint32_t tid = threadIdx.x;
-  build_tables<WIDE>(D, smem, tid, blockDim.x);
-  __syncthreads();
-
-  const uint32_t stage0 = (uint32_t)__cvta_generic_to_shared(smem) + D.tableBytes;
+  const uint32_t G = gridDim.x;
   uint32_t tile = blockIdx.x;
   if (tile >= D.numTiles) return;
-  TileCtx cur, nxt;
-  decode_tile(D, tile, cur);
-  nxt = cur;
+  // Per-tile contexts are decoded by one thread, two tiles ahead, and read by everybody
+  // after the barriers that separate the phases.
+  TileCtx* ctxs = reinterpret_cast<TileCtx*>(smem + table_layout(D).ctx);
+  if (tid == 0) {
+    decode_tile(D, tile, ctxs[0]);
+    if (tile + G < D.numTiles) decode_tile(D, tile + G, ctxs[1]);
+  }
+  build_tables<WIDE>(D, smem, tid, blockDim.x);
+  __syncthreads();
+  const Tables<WIDE> T = make_tables<WIDE>(D, smem);
+  const uint32_t stage0 = (uint32_t)__cvta_generic_to_shared(smem) + D.tableBytes;
 
+  TileCtx cur = ctxs[0];
+  TileCtx nxt = cur;
   if (D.stages >= 2) {
-    tile_load<ELT, WIN, WIDE>(D, cur, smem, stage0, in, tid);
+    tile_load<ELT, WIN, WIDE>(D, cur, T, stage0, in, tid);
     cp_async_commit();
     uint32_t s = 0;
-    for (; tile < D.numTiles; tile += gridDim.x) {
-      const uint32_t tn = tile + gridDim.x;
-      if (tn < D.numTiles) {
-        decode_tile(D, tn, nxt);
-        tile_load<ELT, WIN, WIDE>(D, nxt, smem, stage0 + (s ^ 1u) * D.stageBytes, in, tid);
+    for (uint32_t it = 0; tile < D.numTiles; tile += G, it++) {
+      if (tile + G < D.numTiles) {
+        nxt = ctxs[(it + 1) & 1];
+        tile_load<ELT, WIN, WIDE>(D, nxt, T, stage0 + (s ^ 1u) * D.stageBytes, in, tid);
       }
       cp_async_commit();
+      // slot it&1 held this tile's context; everybody copied it to registers two barriers ago
+      if (tid == 0 && tile + 2 * (uint64_t)G < D.numTiles) decode_tile(D, tile + 2 * G, ctxs[it & 1]);
       cp_async_wait<1>();
       __syncthreads();
       unsigned char* o = D.peerLoopDim >= 0 ? outs.p[cur.peer] : outs.p[0];
-      tile_store<ELT, WOUT, V, WIDE>(D, cur, smem, stage0 + s * D.stageBytes, o, tid);
+      tile_store<ELT, WOUT, V, WIDE>(D, cur, T, stage0 + s * D.stageBytes, o, tid);
       __syncthreads();
       cur = nxt;
       s ^= 1u;
     }
   } else {
-    for (; tile < D.numTiles; tile += gridDim.x) {
-      decode_tile(D, tile, cur);
-      tile_load<ELT, WIN, WIDE>(D, cur, smem, stage0, in, tid);
+    for (uint32_t it = 0; tile < D.numTiles; tile += G, it++) {
+      if (it > 0) cur = ctxs[it & 1];
+      tile_load<ELT, WIN, WIDE>(D, cur, T, stage0, in, tid);
       cp_async_commit();
+      if (tid == 0 && tile + 2 * (uint64_t)G < D.numTiles) decode_tile(D, tile + 2 * G, ctxs[it & 1]);
       cp_async_wait<0>();
       __syncthreads();
       unsigned char* o = D.peerLoopDim >= 0 ? outs.p[cur.peer] : outs.p[0];
-      tile_store<ELT, WOUT, V, WIDE>(D, cur, smem, stage0, o, tid);
+      tile_store<ELT, WOUT, V, WIDE>(D, cur, T, stage0, o, tid);
       __syncthreads();
     }
   }

@@ -171,7 +171,7 @@ struct TileDesc {
 
 // Shared-memory layout in front of the stage buffers.
 struct TableLayout {
-  uint32_t tabIn, tabOut, coordIn, coordOut, qtab, total;
+  uint32_t tabIn, tabOut, coordIn, coordOut, qtab, ctx, total;
 };
 CUTT_HD TableLayout table_layout(const TileDesc& D) {
   TableLayout L;
@@ -181,12 +181,13 @@ CUTT_HD TableLayout table_layout(const TileDesc& D) {
   L.coordIn = L.tabOut + D.out.nrows * esz;
   L.coordOut = L.coordIn + D.in.nrows * (uint32_t)sizeof(RowCoord);
   L.qtab = (L.coordOut + D.out.nrows * (uint32_t)sizeof(RowCoord) + 15u) & ~15u;
-  L.total = (L.qtab + D.out.run * 4u + 15u) & ~15u;
+  L.ctx = (L.qtab + D.out.run * 4u + 15u) & ~15u;
+  L.total = L.ctx + 2u * 32u;  // two per-tile contexts, written by one thread, read by all
   return L;
 }
 
 // Per-tile context derived from the tile index.
-struct TileCtx {
+struct __attribute__((aligned(16))) TileCtx {
   int64_t inOff;
   int64_t outOff;
   uint32_t rem0;     // remaining extent along partial slot 0 (huge if the tile is not short)

@@ -67,14 +67,50 @@ CUTT_HD void stg(unsigned char* gdst, const uint32_t* src) {
 #endif
 }
 
+// Pointers to the shared-memory tables (computed once per thread block).
+template <bool WIDE>
+struct Tables {
+  typedef typename RowEntSel<WIDE>::type Ent;
+  const Ent* tabIn;
+  const Ent* tabOut;
+  const RowCoord* coIn;
+  const RowCoord* coOut;
+  const uint32_t* qtab;
+};
+
+template <bool WIDE>
+CUTT_HD Tables<WIDE> make_tables(const TileDesc& D, const unsigned char* tables) {
+  typedef typename RowEntSel<WIDE>::type Ent;
+  const TableLayout L = table_layout(D);
+  Tables<WIDE> T;
+  T.tabIn = reinterpret_cast<const Ent*>(tables + L.tabIn);
+  T.tabOut = reinterpret_cast<const Ent*>(tables + L.tabOut);
+  T.coIn = reinterpret_cast<const RowCoord*>(tables + L.coordIn);
+  T.coOut = reinterpret_cast<const RowCoord*>(tables + L.coordOut);
+  T.qtab = reinterpret_cast<const uint32_t*>(tables + L.qtab);
+  return T;
+}
+
+// Rows of a side with at most one row dimension need no table: offsets are multiples of
+// the row index and a short tile simply has fewer rows.
+CUTT_HD uint32_t single_dim_rows(const Side& S, const TileCtx& c) {
+  uint32_t nr = S.nrows;
+  if (S.nRowDims == 1 && S.rowDim[0].slot >= 0) {
+    const uint32_t rem = S.rowDim[0].slot == 0 ? c.rem0 : c.rem1;
+    if (rem != 0xffffffffu) {
+      const uint32_t cm = S.rowDim[0].cmul;
+      const uint32_t v = (rem + cm - 1) / cm;
+      nr = v < nr ? v : nr;
+    }
+  }
+  return nr;
+}
+
 template <int ELT, int W, bool WIDE, bool PARTIAL>
-CUTT_HD void tile_load_impl(const TileDesc& D, const TileCtx& c, const unsigned char* tables,
+CUTT_HD void tile_load_impl(const TileDesc& D, const TileCtx& c, const Tables<WIDE>& T,
                             sptr_t sbuf, const unsigned char* gin, uint32_t tid) {
   typedef typename RowEntSel<WIDE>::type Ent;
   const Side& S = D.in;
-  const TableLayout L = table_layout(D);
-  const Ent* tab = reinterpret_cast<const Ent*>(tables + L.tabIn);
-  const RowCoord* co = reinterpret_cast<const RowCoord*>(tables + L.coordIn);
   const uint32_t tq = tid & (S.tq - 1);
   const uint32_t tr = tid >> S.tqShift;
   const uint32_t Tr = D.nthreads >> S.tqShift;
@@ -85,12 +121,33 @@ CUTT_HD void tile_load_impl(const TileDesc& D, const TileCtx& c, const unsigned 
   const uint32_t qstepB = qstep * ELT;
   const unsigned char* gbase = gin + (c.inOff + q0) * ELT;
   const sptr_t sbase = sbuf + q0 * ELT;
+  if (S.nRowDims <= 1) {
+    const RowDim& R = S.rowDim[0];
+    const uint32_t nr = PARTIAL ? single_dim_rows(S, c) : S.nrows;
+    const int64_t gstepB = S.nRowDims ? R.gstride * (int64_t)(Tr * ELT) : 0;
+    const unsigned char* g0 = gbase + (S.nRowDims ? R.gstride * (int64_t)(tr * ELT) : 0);
+    const bool skewed = S.nRowDims && R.skew.mask != 0;
+#pragma unroll 4
+    for (uint32_t row = tr; row < nr; row += Tr) {
+      sptr_t s = sbase + row * R.sstrideB;
+      if (skewed) s += skew_bytes(R.skew, row);
+      const unsigned char* g = g0;
+      copy_g2s<ELT * W>(s, g);
+      for (uint32_t q = q0 + qstep; q < valid; q += qstep) {
+        g += qstepB;
+        s += qstepB;
+        copy_g2s<ELT * W>(s, g);
+      }
+      g0 += gstepB;
+    }
+    return;
+  }
   for (uint32_t row = tr; row < S.nrows; row += Tr) {
     if (PARTIAL) {
-      const RowCoord rc = co[row];
+      const RowCoord rc = T.coIn[row];
       if (!(rc.c0 < c.rem0 && rc.c1 < c.rem1)) continue;
     }
-    const Ent e = tab[row];
+    const Ent e = T.tabIn[row];
     const unsigned char* g = gbase + (WIDE ? (int64_t)e.goff * ELT : (int64_t)((uint64_t)(uint32_t)e.goff * ELT));
     sptr_t s = sbase + e.soffB;
     copy_g2s<ELT * W>(s, g);
@@ -102,16 +159,38 @@ CUTT_HD void tile_load_impl(const TileDesc& D, const TileCtx& c, const unsigned 
   }
 }
 
+// One (row group, run position) item of the store side: W shared-memory vectors of V
+// elements in, V global vectors of W elements out.
+template <int ELT, int W, int V>
+CUTT_HD void store_item(sptr_t sb, const uint32_t* so, bool contig, unsigned char* g, int64_t vstepB) {
+  constexpr int EW = ELT / 4;  // 32-bit words per element
+  if (contig) {
+    uint32_t x[W * EW];
+    lds<ELT * W>(x, sb + so[0]);
+    stg<ELT * W>(g, x);
+  } else {
+    uint32_t x[W][V * EW];
+#pragma unroll
+    for (int i = 0; i < W; i++) lds<ELT * V>(x[i], sb + so[i]);
+#pragma unroll
+    for (int j = 0; j < V; j++) {
+      uint32_t y[W * EW];
+#pragma unroll
+      for (int i = 0; i < W; i++) {
+#pragma unroll
+        for (int w = 0; w < EW; w++) y[i * EW + w] = x[i][j * EW + w];
+      }
+      stg<ELT * W>(g, y);
+      g += vstepB;
+    }
+  }
+}
+
 template <int ELT, int W, int V, bool WIDE, bool PARTIAL>
-CUTT_HD void tile_store_impl(const TileDesc& D, const TileCtx& c, const unsigned char* tables,
+CUTT_HD void tile_store_impl(const TileDesc& D, const TileCtx& c, const Tables<WIDE>& T,
                              sptr_t sbuf, unsigned char* gout, uint32_t tid) {
   typedef typename RowEntSel<WIDE>::type Ent;
-  constexpr int EW = ELT / 4;  // 32-bit words per element
   const Side& S = D.out;
-  const TableLayout L = table_layout(D);
-  const Ent* tab = reinterpret_cast<const Ent*>(tables + L.tabOut);
-  const RowCoord* co = reinterpret_cast<const RowCoord*>(tables + L.coordOut);
-  const uint32_t* qtab = reinterpret_cast<const uint32_t*>(tables + L.qtab);
   const uint32_t tq = tid & (S.tq - 1);
   const uint32_t tr = tid >> S.tqShift;
   const uint32_t Tr = D.nthreads >> S.tqShift;
@@ -120,56 +199,53 @@ CUTT_HD void tile_store_impl(const TileDesc& D, const TileCtx& c, const unsigned
   const bool contig = (W > 1) && (V == 1) && D.smemGatherContig;
   const int64_t vstepB = D.vstep * ELT;
   unsigned char* gbase = gout + c.outOff * ELT;
+  const bool single = S.nRowDims <= 1;
+  const RowDim& R = S.rowDim[0];
+  const uint32_t nr = single ? (PARTIAL ? single_dim_rows(S, c) : S.nrows) : S.nrows;
+  const int64_t gstepB = (single && S.nRowDims) ? R.gstride * (int64_t)(Tr * ELT) : 0;
+  const int64_t g0off = (single && S.nRowDims) ? R.gstride * (int64_t)(tr * ELT) : 0;
+  const bool skewed = single && S.nRowDims && R.skew.mask != 0;
   for (uint32_t q = tq * W; q < valid; q += qstep) {
     uint32_t so[W];
 #pragma unroll
-    for (int i = 0; i < W; i++) so[i] = qtab[q + i];
+    for (int i = 0; i < W; i++) so[i] = T.qtab[q + i];
     unsigned char* gq = gbase + (size_t)q * ELT;
+    if (single) {
+      unsigned char* g = gq + g0off;
 #pragma unroll 2
-    for (uint32_t row = tr; row < S.nrows; row += Tr) {
-      if (PARTIAL) {
-        const RowCoord rc = co[row];
-        if (!(rc.c0 < c.rem0 && rc.c1 < c.rem1)) continue;
+      for (uint32_t row = tr; row < nr; row += Tr) {
+        sptr_t sb = sbuf + row * R.sstrideB;
+        if (skewed) sb += skew_bytes(R.skew, row);
+        store_item<ELT, W, V>(sb, so, contig, g, vstepB);
+        g += gstepB;
       }
-      const Ent e = tab[row];
-      const sptr_t sb = sbuf + e.soffB;
-      unsigned char* g = gq + (WIDE ? (int64_t)e.goff * ELT : (int64_t)((uint64_t)(uint32_t)e.goff * ELT));
-      if (contig) {
-        uint32_t x[W * EW];
-        lds<ELT * W>(x, sb + so[0]);
-        stg<ELT * W>(g, x);
-      } else {
-        uint32_t x[W][V * EW];
-#pragma unroll
-        for (int i = 0; i < W; i++) lds<ELT * V>(x[i], sb + so[i]);
-#pragma unroll
-        for (int j = 0; j < V; j++) {
-          uint32_t y[W * EW];
-#pragma unroll
-          for (int i = 0; i < W; i++) {
-#pragma unroll
-            for (int w = 0; w < EW; w++) y[i * EW + w] = x[i][j * EW + w];
-          }
-          stg<ELT * W>(g, y);
-          g += vstepB;
+    } else {
+#pragma unroll 2
+      for (uint32_t row = tr; row < nr; row += Tr) {
+        if (PARTIAL) {
+          const RowCoord rc = T.coOut[row];
+          if (!(rc.c0 < c.rem0 && rc.c1 < c.rem1)) continue;
         }
+        const Ent e = T.tabOut[row];
+        unsigned char* g = gq + (WIDE ? (int64_t)e.goff * ELT : (int64_t)((uint64_t)(uint32_t)e.goff * ELT));
+        store_item<ELT, W, V>(sbuf + e.soffB, so, contig, g, vstepB);
       }
     }
   }
 }
 
 template <int ELT, int W, bool WIDE>
-CUTT_HD void tile_load(const TileDesc& D, const TileCtx& c, const unsigned char* tables,
+CUTT_HD void tile_load(const TileDesc& D, const TileCtx& c, const Tables<WIDE>& T,
                        sptr_t sbuf, const unsigned char* gin, uint32_t tid) {
-  if (c.partial) tile_load_impl<ELT, W, WIDE, true>(D, c, tables, sbuf, gin, tid);
-  else tile_load_impl<ELT, W, WIDE, false>(D, c, tables, sbuf, gin, tid);
+  if (c.partial) tile_load_impl<ELT, W, WIDE, true>(D, c, T, sbuf, gin, tid);
+  else tile_load_impl<ELT, W, WIDE, false>(D, c, T, sbuf, gin, tid);
 }
 
 template <int ELT, int W, int V, bool WIDE>
-CUTT_HD void tile_store(const TileDesc& D, const TileCtx& c, const unsigned char* tables,
+CUTT_HD void tile_store(const TileDesc& D, const TileCtx& c, const Tables<WIDE>& T,
                         sptr_t sbuf, unsigned char* gout, uint32_t tid) {
-  if (c.partial) tile_store_impl<ELT, W, V, WIDE, true>(D, c, tables, sbuf, gout, tid);
-  else tile_store_impl<ELT, W, V, WIDE, false>(D, c, tables, sbuf, gout, tid);
+  if (c.partial) tile_store_impl<ELT, W, V, WIDE, true>(D, c, T, sbuf, gout, tid);
+  else tile_store_impl<ELT, W, V, WIDE, false>(D, c, T, sbuf, gout, tid);
 }
 
 }  // namespace cuttb
