@@ -20,6 +20,7 @@ static void run_desc(const TileDesc& D, const unsigned char* in, unsigned char* 
   for (uint32_t tile = 0; tile < D.numTiles; tile++) {
     TileCtx c;
     decode_tile(D, tile, c);
+    if (!c.valid) continue;
     memset(sbuf.data(), 0xEE, sbuf.size());
     for (uint32_t tid = 0; tid < D.nthreads; tid++)
       tile_load<ELT, WIN, WIDE>(D, c, T, sbuf.data(), in, tid);
@@ -76,6 +77,7 @@ int cutt_hostcheck_run(int rank, const int* dim, const int* perm, int elt, int i
 int cutt_hostcheck_run_params(int rank, const int* dim, const int* perm, int elt,
                               unsigned tinBytes, unsigned toutBytes, unsigned vtargetBytes,
                               int extend, int loopOrder, int maxVecBytes, int maxVBytes, int nthreads,
+                              int groupIn, int groupOut,
                               const void* in, void* out, char* label, int labelLen) {
   Problem P;
   if (!problem_from_cutt(rank, dim, perm, elt, P)) return 2;
@@ -83,6 +85,7 @@ int cutt_hostcheck_run_params(int rank, const int* dim, const int* perm, int elt
   TileParams tp;
   tp.tinBytes = tinBytes; tp.toutBytes = toutBytes; tp.vtargetBytes = vtargetBytes;
   tp.extend = extend; tp.loopOrder = loopOrder; tp.maxVecBytes = maxVecBytes; tp.maxVBytes = maxVBytes; tp.nthreads = nthreads;
+  tp.groupIn = groupIn; tp.groupOut = groupOut;
   Candidate c;
   if (!build_tile(P, tp, g_dev, c)) return 5;
   if (label && labelLen > 0) snprintf(label, labelLen, "%s", describe(P, c).c_str());

@@ -49,13 +49,13 @@ permute_tiles_kernel(const __grid_constant__ TileDesc D, const unsigned char* __
   TileCtx cur = ctxs[0];
   TileCtx nxt = cur;
   if (D.stages >= 2) {
-    tile_load<ELT, WIN, WIDE>(D, cur, T, stage0, in, tid);
+    if (cur.valid) tile_load<ELT, WIN, WIDE>(D, cur, T, stage0, in, tid);
     cp_async_commit();
     uint32_t s = 0;
     for (uint32_t it = 0; tile < D.numTiles; tile += G, it++) {
       if (tile + G < D.numTiles) {
         nxt = ctxs[(it + 1) & 1];
-        tile_load<ELT, WIN, WIDE>(D, nxt, T, stage0 + (s ^ 1u) * D.stageBytes, in, tid);
+        if (nxt.valid) tile_load<ELT, WIN, WIDE>(D, nxt, T, stage0 + (s ^ 1u) * D.stageBytes, in, tid);
       }
       cp_async_commit();
       // slot it&1 held this tile's context; everybody copied it to registers two barriers ago
@@ -63,7 +63,7 @@ permute_tiles_kernel(const __grid_constant__ TileDesc D, const unsigned char* __
       cp_async_wait<1>();
       __syncthreads();
       unsigned char* o = D.peerLoopDim >= 0 ? outs.p[cur.peer] : outs.p[0];
-      tile_store<ELT, WOUT, V, WIDE>(D, cur, T, stage0 + s * D.stageBytes, o, tid);
+      if (cur.valid) tile_store<ELT, WOUT, V, WIDE>(D, cur, T, stage0 + s * D.stageBytes, o, tid);
       __syncthreads();
       cur = nxt;
       s ^= 1u;
@@ -71,13 +71,13 @@ permute_tiles_kernel(const __grid_constant__ TileDesc D, const unsigned char* __
   } else {
     for (uint32_t it = 0; tile < D.numTiles; tile += G, it++) {
       if (it > 0) cur = ctxs[it & 1];
-      tile_load<ELT, WIN, WIDE>(D, cur, T, stage0, in, tid);
+      if (cur.valid) tile_load<ELT, WIN, WIDE>(D, cur, T, stage0, in, tid);
       cp_async_commit();
       if (tid == 0 && tile + 2 * (uint64_t)G < D.numTiles) decode_tile(D, tile + 2 * G, ctxs[it & 1]);
       cp_async_wait<0>();
       __syncthreads();
       unsigned char* o = D.peerLoopDim >= 0 ? outs.p[cur.peer] : outs.p[0];
-      tile_store<ELT, WOUT, V, WIDE>(D, cur, T, stage0, o, tid);
+      if (cur.valid) tile_store<ELT, WOUT, V, WIDE>(D, cur, T, stage0, o, tid);
       __syncthreads();
     }
   }

@@ -135,14 +135,31 @@ struct Side {
   RowDim rowDim[kMaxDims];
 };
 
+// One digit of the tile index.  A dimension normally contributes one digit ("whole").  The
+// chunked dimension of a run may be split into an inner digit (a small group of neighbouring
+// tiles, placed first so that blocks running at the same time touch neighbouring memory) and
+// an outer digit; positions past the end of the dimension are skipped.
 struct LoopDim {
   FastDiv div;      // division by n
-  uint32_t n;       // tiles along this dimension
+  uint32_t n;       // positions of this digit
   uint32_t t;       // tile extent
   uint32_t d;       // full extent
-  int32_t slot;     // partial slot fed by this dimension, or -1
-  int64_t istep;    // input offset per tile step (istride * t)
-  int64_t ostep;    // output offset per tile step (ostride * t); unused for the peer dimension
+  int32_t slot;     // partial slot fed by this dimension, or -1 (whole digits only)
+  uint32_t part;    // 0 whole, 1 inner digit, 2 outer digit of a split dimension
+  uint32_t which;   // split dimension index (0/1) for part != 0
+  uint32_t mul;     // tile positions per step of this digit (group size for an outer digit, else 1)
+  uint32_t pad_;
+  int64_t istep;    // input offset per step (istride * t * mul)
+  int64_t ostep;    // output offset per step; unused for the peer dimension
+};
+
+struct SplitDim {
+  uint32_t used;
+  uint32_t n;       // tile positions along the dimension
+  uint32_t t;
+  uint32_t d;
+  int32_t slot;
+  uint32_t pad_[3];
 };
 
 struct TileDesc {
@@ -166,7 +183,8 @@ struct TileDesc {
   Side in;
   Side out;
   RunDim outRunDim[kMaxDims];
-  LoopDim loop[kMaxDims];
+  LoopDim loop[kMaxDims + 2];
+  SplitDim split[2];
 };
 
 // Shared-memory layout in front of the stage buffers.
@@ -194,7 +212,16 @@ struct __attribute__((aligned(16))) TileCtx {
   uint32_t rem1;     // same for slot 1
   uint32_t peer;
   uint32_t partial;  // 1 if the tile is short along a partial dimension
+  uint32_t valid;    // 0: the tile index falls past the end of a split dimension (nothing to do)
+  uint32_t pad_;
 };
+
+CUTT_HD void set_rem(TileCtx& c, int32_t slot, uint32_t left, uint32_t t) {
+  if (slot >= 0 && left < t) {
+    c.partial = 1;
+    if (slot == 0) c.rem0 = left; else c.rem1 = left;
+  }
+}
 
 CUTT_HD void decode_tile(const TileDesc& D, uint32_t tile, TileCtx& c) {
   c.inOff = D.inBase;
@@ -203,7 +230,10 @@ CUTT_HD void decode_tile(const TileDesc& D, uint32_t tile, TileCtx& c) {
   c.rem1 = 0xffffffffu;
   c.peer = 0;
   c.partial = 0;
+  c.valid = 1;
+  c.pad_ = 0;
   uint32_t id = tile;
+  uint32_t pos0 = 0, pos1 = 0;
   for (uint32_t k = 0; k < D.nLoopDims; k++) {
     const LoopDim& L = D.loop[k];
     uint32_t q = fdiv(id, L.div);
@@ -212,13 +242,23 @@ CUTT_HD void decode_tile(const TileDesc& D, uint32_t tile, TileCtx& c) {
     c.inOff += (int64_t)cc * L.istep;
     if ((int32_t)k == D.peerLoopDim) c.peer = cc;
     else c.outOff += (int64_t)cc * L.ostep;
-    if (L.slot >= 0) {
-      uint32_t left = L.d - cc * L.t;
-      if (left < L.t) {
-        c.partial = 1;
-        if (L.slot == 0) c.rem0 = left; else c.rem1 = left;
-      }
+    if (L.part == 0) {
+      set_rem(c, L.slot, L.d - cc * L.t, L.t);
+    } else if (L.which == 0) {
+      pos0 += cc * L.mul;
+    } else {
+      pos1 += cc * L.mul;
     }
+  }
+  if (D.split[0].used) {
+    const SplitDim& S = D.split[0];
+    if (pos0 >= S.n) c.valid = 0;
+    else set_rem(c, S.slot, S.d - pos0 * S.t, S.t);
+  }
+  if (D.split[1].used) {
+    const SplitDim& S = D.split[1];
+    if (pos1 >= S.n) c.valid = 0;
+    else set_rem(c, S.slot, S.d - pos1 * S.t, S.t);
   }
 }
 

@@ -110,7 +110,7 @@ bool build_tile(const Problem& P, const TileParams& tp, const DeviceInfo& dev, C
   {
     int64_t cum = 1, expect = 1;
     for (int j = 0; j < r; j++) {
-      if (P.is[j] != expect || j == P.peerDim || cum >= tin) break;
+      if (P.is[j] != expect || j == P.peerDim || cum * 4 >= tin * 3) break;
       int64_t want = ceil_div(tin, cum);
       if (P.d[j] <= want + want / 2 && P.d[j] <= kMaxChunk) {
         t[j] = P.d[j]; cum *= P.d[j]; expect *= P.d[j];
@@ -128,7 +128,7 @@ bool build_tile(const Problem& P, const TileParams& tp, const DeviceInfo& dev, C
       if (P.os[j] != expect || j == P.peerDim) break;
       if (t[j] == P.d[j]) { cum *= P.d[j]; expect *= P.d[j]; continue; }
       if (t[j] > 1) break;  // already chunked by the input run: the output run ends here
-      if (cum >= tout) break;
+      if (cum * 4 >= tout * 3) break;
       int64_t want = ceil_div(tout, cum);
       if (P.d[j] <= want + want / 2 && P.d[j] <= kMaxChunk) {
         t[j] = P.d[j]; cum *= P.d[j]; expect *= P.d[j];
@@ -359,27 +359,57 @@ bool build_tile(const Problem& P, const TileParams& tp, const DeviceInfo& dev, C
   D.tableBytes = table_layout(D).total;
   if (D.tableBytes > 64 * 1024) return false;
 
-  // loop dimensions
+  // loop dimensions (digits of the tile index, fastest first)
   {
     int order[kMaxDims];
     for (int k = 0; k < r; k++) order[k] = tp.loopOrder == 0 ? k : oo[k];
+    // optional inner groups along the chunked dimensions of the two runs
+    int splitDim[2] = {-1, -1};
+    int64_t splitS[2] = {1, 1};
+    if (tp.groupIn > 1 && inRunLast >= 0 && t[inRunLast] < P.d[inRunLast] && inRunLast != P.peerDim &&
+        ceil_div(P.d[inRunLast], t[inRunLast]) >= 2 * tp.groupIn) {
+      splitDim[0] = inRunLast; splitS[0] = tp.groupIn;
+    }
+    if (tp.groupOut > 1 && outRunLast >= 0 && t[outRunLast] < P.d[outRunLast] && outRunLast != P.peerDim &&
+        outRunLast != splitDim[0] && ceil_div(P.d[outRunLast], t[outRunLast]) >= 2 * tp.groupOut) {
+      splitDim[1] = outRunLast; splitS[1] = tp.groupOut;
+    }
     int64_t ntiles = 1;
     D.nLoopDims = 0;
-    for (int k = 0; k < r; k++) {
-      int j = order[k];
-      int64_t n = ceil_div(P.d[j], t[j]);
-      if (n <= 1) continue;
+    auto push = [&](int j, int64_t n, int64_t mul, uint32_t part, uint32_t which) {
       LoopDim& L = D.loop[D.nLoopDims];
       L.n = (uint32_t)n;
       L.div = make_fastdiv((uint32_t)n);
       L.t = (uint32_t)t[j];
       L.d = (uint32_t)P.d[j];
-      L.slot = slotOf[j];
-      L.istep = P.is[j] * t[j];
-      L.ostep = P.os[j] * t[j];
+      L.slot = part == 0 ? slotOf[j] : -1;
+      L.part = part;
+      L.which = which;
+      L.mul = (uint32_t)mul;
+      L.istep = P.is[j] * t[j] * mul;
+      L.ostep = P.os[j] * t[j] * mul;
       if (j == P.peerDim) D.peerLoopDim = (int32_t)D.nLoopDims;
       D.nLoopDims++;
       ntiles *= n;
+    };
+    for (int w = 0; w < 2; w++) {
+      D.split[w].used = 0;
+      if (splitDim[w] < 0) continue;
+      int j = splitDim[w];
+      D.split[w].used = 1;
+      D.split[w].n = (uint32_t)ceil_div(P.d[j], t[j]);
+      D.split[w].t = (uint32_t)t[j];
+      D.split[w].d = (uint32_t)P.d[j];
+      D.split[w].slot = slotOf[j];
+      push(j, splitS[w], 1, 1, (uint32_t)w);
+    }
+    for (int k = 0; k < r; k++) {
+      int j = order[k];
+      int64_t n = ceil_div(P.d[j], t[j]);
+      if (n <= 1) continue;
+      int w = j == splitDim[0] ? 0 : (j == splitDim[1] ? 1 : -1);
+      if (w >= 0) push(j, ceil_div(n, splitS[w]), splitS[w], 2, (uint32_t)w);
+      else push(j, n, 1, 0, 0);
       if (ntiles >= (1ll << 31)) return false;
     }
     D.numTiles = (uint32_t)ntiles;
@@ -401,6 +431,10 @@ bool build_tile(const Problem& P, const TileParams& tp, const DeviceInfo& dev, C
   snprintf(buf, sizeof buf, "tiles t=[%s] in=%ux%u/w%u out=%ux%u/w%u V%u%s smem=%d st=%d lo=%d nt=%d",
            ts.c_str(), D.in.nrows, D.in.run, D.in.vec, D.out.nrows, D.out.run, D.out.vec, D.vblk,
            D.wide ? " wide" : "", out.smemBytes, D.stages, tp.loopOrder, tp.nthreads);
+  if (D.split[0].used || D.split[1].used) {
+    snprintf(buf + strlen(buf), sizeof buf - strlen(buf), " g=%d/%d", D.split[0].used ? tp.groupIn : 1,
+             D.split[1].used ? tp.groupOut : 1);
+  }
   out.label = buf;
   out.cost = model_cost(P, out, dev);
   return true;
@@ -445,21 +479,27 @@ std::vector<Candidate> enumerate_candidates(const Problem& P, const DeviceInfo& 
     return res;
   }
   std::set<std::string> seen;
-  const uint32_t runs[] = {128, 256, 512, 1024};
-  const uint32_t vols[] = {8192, 16384, 32768};
+  const uint32_t runs[] = {128, 256, 512, 1024, 2048};
+  const uint32_t vols[] = {8192, 16384, 32768, 65536};
+  const int groups[][2] = {{1, 1}, {2, 1}, {4, 1}, {1, 4}, {2, 4}};
   for (uint32_t tinB : runs)
     for (uint32_t toutB : runs)
       for (uint32_t vB : vols)
         for (int ext = 0; ext < 2; ext++)
-          for (int lo = 0; lo < 2; lo++) {
-            TileParams tp;
-            tp.tinBytes = tinB; tp.toutBytes = toutB; tp.vtargetBytes = vB;
-            tp.extend = ext; tp.loopOrder = lo;
-            Candidate c;
-            if (!build_tile(P, tp, dev, c)) continue;
-            if (!seen.insert(c.label).second) continue;
-            res.push_back(c);
-          }
+          for (int lo = 0; lo < 2; lo++)
+            for (const auto& g : groups)
+              for (int nt = 256; nt <= 512; nt *= 2) {
+                TileParams tp;
+                tp.tinBytes = tinB; tp.toutBytes = toutB; tp.vtargetBytes = vB;
+                tp.extend = ext; tp.loopOrder = lo;
+                tp.groupIn = g[0]; tp.groupOut = g[1];
+                tp.nthreads = nt;
+                Candidate c;
+                if (!build_tile(P, tp, dev, c)) continue;
+                if (nt == 512 && c.smemBytes < 40 * 1024) continue;  // small tiles: more blocks instead
+                if (!seen.insert(c.label).second) continue;
+                res.push_back(c);
+              }
   std::stable_sort(res.begin(), res.end(), [](const Candidate& a, const Candidate& b) { return a.cost < b.cost; });
   return res;
 }

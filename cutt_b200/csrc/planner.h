@@ -59,6 +59,8 @@ struct TileParams {
   int maxVecBytes = 16;        // widest global access
   int maxVBytes = 16;          // widest shared-memory vector of the register-blocked store side
   int loopOrder = 0;           // tile index runs fastest along 0: input order, 1: output order
+  int groupIn = 1;             // neighbouring tiles along the input run's chunked dimension taken first
+  int groupOut = 1;            // then this many along the output run's chunked dimension
 };
 
 struct Candidate {

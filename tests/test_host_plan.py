@@ -25,7 +25,7 @@ def hc(native):
                                        ctypes.c_void_p, ctypes.c_void_p, ctypes.c_char_p, ctypes.c_int]
     lib.cutt_hostcheck_run_params.argtypes = [ctypes.c_int, ip, ip, ctypes.c_int, ctypes.c_uint, ctypes.c_uint,
                                               ctypes.c_uint, ctypes.c_int, ctypes.c_int, ctypes.c_int, ctypes.c_int,
-                                              ctypes.c_int, ctypes.c_void_p, ctypes.c_void_p, ctypes.c_char_p, ctypes.c_int]
+                                              ctypes.c_int, ctypes.c_int, ctypes.c_int, ctypes.c_void_p, ctypes.c_void_p, ctypes.c_char_p, ctypes.c_int]
     lib.cutt_hostcheck_fastdiv.restype = ctypes.c_longlong
     lib.cutt_hostcheck_fastdiv.argtypes = [ctypes.c_uint, ctypes.c_ulonglong, ctypes.c_ulonglong]
     return lib
@@ -98,6 +98,7 @@ def test_random_shapes(hc, oracle_mod):
 @pytest.mark.parametrize("kw", [
     dict(mv=4, mV=4), dict(mv=8, mV=8), dict(mv=16, mV=4), dict(mv=4, mV=16), dict(nt=128), dict(nt=512),
     dict(tin=128, tout=1024), dict(tin=1024, tout=128, vt=32768), dict(lo=1, ext=1), dict(tin=64, tout=64, vt=2048),
+    dict(gi=2, tin=64, tout=64, vt=1024), dict(gi=4, go=4, tin=32, tout=32, vt=512), dict(go=2, lo=1, tin=64, tout=128, vt=2048),
 ])
 def test_forced_parameters(hc, oracle_mod, kw):
     rng = random.Random(5)
@@ -114,7 +115,7 @@ def test_forced_parameters(hc, oracle_mod, kw):
             rc = hc.cutt_hostcheck_run_params(
                 len(dims), _iarr(dims), _iarr(perm), elt, kw.get("tin", 256), kw.get("tout", 256),
                 kw.get("vt", 16384), kw.get("ext", 0), kw.get("lo", 0), kw.get("mv", 16), kw.get("mV", 16),
-                kw.get("nt", 256), a.ctypes.data, out.ctypes.data, lab, 2048)
+                kw.get("nt", 256), kw.get("gi", 1), kw.get("go", 1), a.ctypes.data, out.ctypes.data, lab, 2048)
             assert rc == 0, (rc, dims, perm, kw)
             assert np.array_equal(out, oracle_mod.transpose_blocked(dims, perm, a)), (dims, perm, elt, lab.value.decode())
 
