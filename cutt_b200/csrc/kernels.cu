@@ -58,10 +58,12 @@ permute_tiles_kernel(const __grid_constant__ TileDesc D, const unsigned char* __
         if (nxt.valid) tile_load<ELT, WIN, WIDE>(D, nxt, T, stage0 + (s ^ 1u) * D.stageBytes, in, tid);
       }
       cp_async_commit();
-      // slot it&1 held this tile's context; everybody copied it to registers two barriers ago
-      if (tid == 0 && tile + 2 * (uint64_t)G < D.numTiles) decode_tile(D, tile + 2 * G, ctxs[it & 1]);
       cp_async_wait<1>();
       __syncthreads();
+      // Slot it&1 held this tile's context.  Every thread copied it to registers before the
+      // barrier above (at the top of the previous iteration, or in the prologue), and nobody
+      // reads the slot again before the barrier below, so thread 0 may overwrite it here.
+      if (tid == 0 && tile + 2 * (uint64_t)G < D.numTiles) decode_tile(D, tile + 2 * G, ctxs[it & 1]);
       unsigned char* o = D.peerLoopDim >= 0 ? outs.p[cur.peer] : outs.p[0];
       if (cur.valid) tile_store<ELT, WOUT, V, WIDE>(D, cur, T, stage0 + s * D.stageBytes, o, tid);
       __syncthreads();
@@ -73,9 +75,10 @@ permute_tiles_kernel(const __grid_constant__ TileDesc D, const unsigned char* __
       if (it > 0) cur = ctxs[it & 1];
       if (cur.valid) tile_load<ELT, WIN, WIDE>(D, cur, T, stage0, in, tid);
       cp_async_commit();
-      if (tid == 0 && tile + 2 * (uint64_t)G < D.numTiles) decode_tile(D, tile + 2 * G, ctxs[it & 1]);
       cp_async_wait<0>();
       __syncthreads();
+      // every thread has read slot it&1 (this tile) before the barrier above
+      if (tid == 0 && tile + 2 * (uint64_t)G < D.numTiles) decode_tile(D, tile + 2 * G, ctxs[it & 1]);
       unsigned char* o = D.peerLoopDim >= 0 ? outs.p[cur.peer] : outs.p[0];
       if (cur.valid) tile_store<ELT, WOUT, V, WIDE>(D, cur, T, stage0, o, tid);
       __syncthreads();
