@@ -6,27 +6,74 @@
 #include <cstdio>
 #include <cstring>
 #include <vector>
+#define CUTT_HOSTCHECK_BOUNDS 1
 #include "permute_tile_impl.h"
 #include "planner.h"
 
 using namespace cuttb;
 
+// Mirrors permute_tiles_kernel for an emulated grid of `grid` blocks, one block after the
+// other: same shared-memory layout (tables, the two context slots, the stage buffers), same
+// order of decode / load / store steps per block.  Threads of a block run one after the
+// other inside each step, so data races are not modelled, layout overlaps are.
 template <int ELT, int WIN, int WOUT, int V, bool WIDE>
 static void run_desc(const TileDesc& D, const unsigned char* in, unsigned char* out) {
-  std::vector<unsigned char> tables(D.tableBytes + 16);
-  for (uint32_t tid = 0; tid < D.nthreads; tid++) build_tables<WIDE>(D, tables.data(), tid, D.nthreads);
-  const Tables<WIDE> T = make_tables<WIDE>(D, tables.data());
-  std::vector<unsigned char> sbuf(D.stageBytes);
-  for (uint32_t tile = 0; tile < D.numTiles; tile++) {
-    TileCtx c;
-    decode_tile(D, tile, c);
-    if (!c.valid) continue;
-    memset(sbuf.data(), 0xEE, sbuf.size());
-    for (uint32_t tid = 0; tid < D.nthreads; tid++)
-      tile_load<ELT, WIN, WIDE>(D, c, T, sbuf.data(), in, tid);
-    for (uint32_t tid = 0; tid < D.nthreads; tid++)
-      tile_store<ELT, WOUT, V, WIDE>(D, c, T, sbuf.data(), out, tid);
+  const uint32_t G = D.numTiles < 3 ? D.numTiles : 3;
+  std::vector<unsigned char> smem(D.tableBytes + D.stages * D.stageBytes);
+  host_bounds().s0 = smem.data() + D.tableBytes;
+  host_bounds().s1 = smem.data() + smem.size();
+  for (uint32_t block = 0; block < G; block++) {
+    memset(smem.data(), 0xEE, smem.size());
+    TileCtx* ctxs = reinterpret_cast<TileCtx*>(smem.data() + table_layout(D).ctx);
+    uint32_t tile = block;
+    decode_tile(D, tile, ctxs[0]);
+    if (tile + G < D.numTiles) decode_tile(D, tile + G, ctxs[1]);
+    for (uint32_t tid = 0; tid < D.nthreads; tid++) build_tables<WIDE>(D, smem.data(), tid, D.nthreads);
+    const Tables<WIDE> T = make_tables<WIDE>(D, smem.data());
+    unsigned char* stage0 = smem.data() + D.tableBytes;
+    TileCtx cur = ctxs[0], nxt = cur;
+    auto load = [&](const TileCtx& c, unsigned char* st) {
+      if (!c.valid) return;
+      for (uint32_t tid = 0; tid < D.nthreads; tid++) tile_load<ELT, WIN, WIDE>(D, c, T, st, in, tid);
+    };
+    auto store = [&](const TileCtx& c, unsigned char* st) {
+      if (!c.valid) return;
+      for (uint32_t tid = 0; tid < D.nthreads; tid++) tile_store<ELT, WOUT, V, WIDE>(D, c, T, st, out, tid);
+    };
+    if (D.stages >= 2) {
+      load(cur, stage0);
+      uint32_t st = 0;
+      for (uint32_t it = 0; tile < D.numTiles; tile += G, it++) {
+        if (tile + G < D.numTiles) {
+          nxt = ctxs[(it + 1) & 1];
+          load(nxt, stage0 + (st ^ 1u) * D.stageBytes);
+        }
+        if (tile + 2 * (uint64_t)G < D.numTiles) decode_tile(D, tile + 2 * G, ctxs[it & 1]);
+        store(cur, stage0 + st * D.stageBytes);
+        cur = nxt;
+        st ^= 1u;
+      }
+    } else {
+      for (uint32_t it = 0; tile < D.numTiles; tile += G, it++) {
+        if (it > 0) cur = ctxs[it & 1];
+        load(cur, stage0);
+        if (tile + 2 * (uint64_t)G < D.numTiles) decode_tile(D, tile + 2 * G, ctxs[it & 1]);
+        store(cur, stage0);
+      }
+    }
   }
+}
+
+static int dispatch(const TileDesc& D, const unsigned char* in, unsigned char* out);
+
+// Every global and shared access of the phases is range- and alignment-checked; accesses
+// that fail are skipped and counted, and the run then reports code 9.
+static int dispatch_checked(const TileDesc& D, const unsigned char* in, unsigned char* out, size_t bytes) {
+  HostBounds& b = host_bounds();
+  b.gin0 = in; b.gin1 = in + bytes; b.gout0 = out; b.gout1 = out + bytes; b.violations = 0;
+  int rc = dispatch(D, in, out);
+  if (rc == 0 && b.violations) { fprintf(stderr, "hostcheck: %lld out-of-range or misaligned accesses\n", b.violations); return 9; }
+  return rc;
 }
 
 static int dispatch(const TileDesc& D, const unsigned char* in, unsigned char* out) {
@@ -70,7 +117,7 @@ int cutt_hostcheck_run(int rank, const int* dim, const int* perm, int elt, int i
     memcpy(out, in, (size_t)P.volume * elt);
     return 0;
   }
-  return dispatch(c.desc, (const unsigned char*)in, (unsigned char*)out);
+  return dispatch_checked(c.desc, (const unsigned char*)in, (unsigned char*)out, (size_t)P.volume * elt);
 }
 
 // Same, for an explicit parameter choice (used to force odd tile shapes in tests).
@@ -89,7 +136,7 @@ int cutt_hostcheck_run_params(int rank, const int* dim, const int* perm, int elt
   Candidate c;
   if (!build_tile(P, tp, g_dev, c)) return 5;
   if (label && labelLen > 0) snprintf(label, labelLen, "%s", describe(P, c).c_str());
-  return dispatch(c.desc, (const unsigned char*)in, (unsigned char*)out);
+  return dispatch_checked(c.desc, (const unsigned char*)in, (unsigned char*)out, (size_t)P.volume * elt);
 }
 
 // Exhaustive-ish self check of the division helper: returns the number of mismatches.

@@ -187,6 +187,8 @@ struct TileDesc {
   SplitDim split[2];
 };
 
+constexpr uint32_t kTileCtxBytes = 48;  // sizeof(TileCtx), checked below
+
 // Shared-memory layout in front of the stage buffers.
 struct TableLayout {
   uint32_t tabIn, tabOut, coordIn, coordOut, qtab, ctx, total;
@@ -200,7 +202,7 @@ CUTT_HD TableLayout table_layout(const TileDesc& D) {
   L.coordOut = L.coordIn + D.in.nrows * (uint32_t)sizeof(RowCoord);
   L.qtab = (L.coordOut + D.out.nrows * (uint32_t)sizeof(RowCoord) + 15u) & ~15u;
   L.ctx = (L.qtab + D.out.run * 4u + 15u) & ~15u;
-  L.total = L.ctx + 2u * 32u;  // two per-tile contexts, written by one thread, read by all
+  L.total = L.ctx + 2u * kTileCtxBytes;  // two per-tile contexts, written by one thread, read by all
   return L;
 }
 
@@ -215,6 +217,8 @@ struct __attribute__((aligned(16))) TileCtx {
   uint32_t valid;    // 0: the tile index falls past the end of a split dimension (nothing to do)
   uint32_t pad_;
 };
+
+static_assert(sizeof(TileCtx) == kTileCtxBytes, "table_layout reserves kTileCtxBytes per context");
 
 CUTT_HD void set_rem(TileCtx& c, int32_t slot, uint32_t left, uint32_t t) {
   if (slot >= 0 && left < t) {

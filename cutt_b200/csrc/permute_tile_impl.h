@@ -24,6 +24,19 @@ typedef uint32_t sptr_t;
 typedef unsigned char* sptr_t;
 #endif
 
+// Host-side interpreter only: address ranges that every access is checked against.
+#if !defined(__CUDA_ARCH__) && defined(CUTT_HOSTCHECK_BOUNDS)
+struct HostBounds {
+  const unsigned char *gin0, *gin1, *gout0, *gout1, *s0, *s1;
+  long long violations;
+};
+inline HostBounds& host_bounds() { static thread_local HostBounds b = {}; return b; }
+#define CUTT_CHECK_RANGE(p, n, lo, hi) \
+  do { if ((const unsigned char*)(p) < (lo) || (const unsigned char*)(p) + (n) > (hi) || ((uintptr_t)(p) % (n)) != 0) { host_bounds().violations++; return; } } while (0)
+#else
+#define CUTT_CHECK_RANGE(p, n, lo, hi) do { } while (0)
+#endif
+
 // global -> shared, BYTES in {4, 8, 16}; asynchronous on the device.
 template <int BYTES>
 CUTT_HD void copy_g2s(sptr_t sdst, const unsigned char* gsrc) {
@@ -34,6 +47,8 @@ CUTT_HD void copy_g2s(sptr_t sdst, const unsigned char* gsrc) {
     asm volatile("cp.async.ca.shared.global [%0], [%1], %2;\n" ::"r"(sdst), "l"(gsrc), "n"(BYTES) : "memory");
   }
 #else
+  CUTT_CHECK_RANGE(gsrc, BYTES, host_bounds().gin0, host_bounds().gin1);
+  CUTT_CHECK_RANGE(sdst, BYTES, host_bounds().s0, host_bounds().s1);
   memcpy(sdst, gsrc, BYTES);
 #endif
 }
@@ -51,6 +66,7 @@ CUTT_HD void lds(uint32_t* dst, sptr_t ssrc) {
                  : "=r"(dst[0]), "=r"(dst[1]), "=r"(dst[2]), "=r"(dst[3]) : "r"(ssrc));
   }
 #else
+  CUTT_CHECK_RANGE(ssrc, BYTES, host_bounds().s0, host_bounds().s1);
   memcpy(dst, ssrc, BYTES);
 #endif
 }
@@ -63,6 +79,7 @@ CUTT_HD void stg(unsigned char* gdst, const uint32_t* src) {
   else if (BYTES == 8) *reinterpret_cast<uint2*>(gdst) = make_uint2(src[0], src[1]);
   else *reinterpret_cast<uint4*>(gdst) = make_uint4(src[0], src[1], src[2], src[3]);
 #else
+  CUTT_CHECK_RANGE(gdst, BYTES, host_bounds().gout0, host_bounds().gout1);
   memcpy(gdst, src, BYTES);
 #endif
 }
