@@ -297,7 +297,7 @@ cuttResult make_plan(cuttHandle* handle, int rank, const int* dim, const int* pe
         // candidate once, cold, on stream 0; here: one warm-up and the best of three runs on
         // the plan's stream, after the same memset + device synchronisation).
         lk.unlock();
-        const size_t topk = env_size("CUTT_MEASURE_TOPK", 12);
+        const size_t topk = env_size("CUTT_MEASURE_TOPK", 24);
         cudaEvent_t e0, e1;
         if (cudaEventCreate(&e0) != cudaSuccess || cudaEventCreate(&e1) != cudaSuccess)
           return CUTT_INTERNAL_ERROR;
