@@ -20,7 +20,7 @@ __all__ = [
     "CUTT_INTERNAL_ERROR", "CUTT_UNDEFINED_ERROR", "CuttError", "lib", "lib_path",
     "cuttPlan", "cuttPlanMeasure", "cuttExecute", "cuttDestroy", "plan_describe",
     "num_candidates", "plan_candidate", "plan_params", "transpose_host", "launch_count",
-    "clear_plan_cache", "Plan",
+    "clear_plan_cache", "plan_cache_save", "plan_cache_load", "plan_cache_size", "Plan",
 ]
 
 # cuttResult (src/cutt.h:34-41): fixed values
@@ -78,6 +78,11 @@ def lib() -> ctypes.CDLL:
     L.cutt_c_launch_count.restype = ctypes.c_ulonglong
     L.cutt_c_clear_plan_cache.restype = None
     L.cutt_c_version.restype = ctypes.c_char_p
+    L.cutt_c_plan_cache_save.argtypes = [ctypes.c_char_p]
+    L.cutt_c_plan_cache_load.argtypes = [ctypes.c_char_p]
+    L.cutt_c_plan_cache_save.restype = ctypes.c_int
+    L.cutt_c_plan_cache_load.restype = ctypes.c_int
+    L.cutt_c_plan_cache_size.restype = ctypes.c_int
     for name in ("cutt_c_plan", "cutt_c_plan_measure", "cutt_c_execute", "cutt_c_destroy",
                  "cutt_c_plan_describe", "cutt_c_num_candidates", "cutt_c_plan_candidate",
                  "cutt_c_plan_params", "cutt_c_transpose_host"):
@@ -159,6 +164,18 @@ def launch_count() -> int:
 
 def clear_plan_cache() -> None:
     lib().cutt_c_clear_plan_cache()
+
+
+def plan_cache_save(path: str) -> int:
+    return lib().cutt_c_plan_cache_save(path.encode())
+
+
+def plan_cache_load(path: str) -> int:
+    return lib().cutt_c_plan_cache_load(path.encode())
+
+
+def plan_cache_size() -> int:
+    return lib().cutt_c_plan_cache_size()
 
 
 class Plan:

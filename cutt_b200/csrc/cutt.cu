@@ -79,6 +79,10 @@ class PlanCache {
   }
   void clear() { map_.clear(); order_.clear(); }
   size_t size() const { return map_.size(); }
+  // least recently used first, so that re-inserting in this order restores the recency order
+  template <typename F> void for_each_oldest_first(F f) const {
+    for (auto it = order_.rbegin(); it != order_.rend(); ++it) f(it->first, it->second);
+  }
 
  private:
   size_t cap_;
@@ -532,6 +536,54 @@ unsigned long long cutt_c_launch_count(void) { return launch_count(); }
 void cutt_c_clear_plan_cache(void) {
   std::lock_guard<std::mutex> lk(g_mutex);
   plan_cache().clear();
+}
+
+// One line per entry: key, method and the tile parameters of the measured winner.
+int cutt_c_plan_cache_save(const char* path) {
+  if (!path) return CUTT_INVALID_PARAMETER;
+  std::lock_guard<std::mutex> lk(g_mutex);
+  FILE* f = fopen(path, "w");
+  if (!f) return CUTT_INTERNAL_ERROR;
+  fprintf(f, "# cutt-b200 plan cache v1\n");
+  plan_cache().for_each_oldest_first([&](const std::string& k, const CachedChoice& c) {
+    const TileParams& t = c.params;
+    fprintf(f, "%s %d %u %u %u %d %d %d %d %d %d %d %d\n", k.c_str(), (int)c.method, t.tinBytes, t.toutBytes,
+            t.vtargetBytes, t.extend, t.nthreads, t.stages, t.maxVecBytes, t.maxVBytes, t.loopOrder,
+            t.groupIn, t.groupOut);
+  });
+  fclose(f);
+  return CUTT_SUCCESS;
+}
+
+int cutt_c_plan_cache_load(const char* path) {
+  if (!path) return CUTT_INVALID_PARAMETER;
+  std::lock_guard<std::mutex> lk(g_mutex);
+  FILE* f = fopen(path, "r");
+  if (!f) return CUTT_INVALID_PARAMETER;
+  char line[1024];
+  int n = 0;
+  while (fgets(line, sizeof line, f)) {
+    if (line[0] == '#') continue;
+    char key[512];
+    int method;
+    CachedChoice c;
+    TileParams& t = c.params;
+    if (sscanf(line, "%511s %d %u %u %u %d %d %d %d %d %d %d %d", key, &method, &t.tinBytes, &t.toutBytes,
+               &t.vtargetBytes, &t.extend, &t.nthreads, &t.stages, &t.maxVecBytes, &t.maxVBytes,
+               &t.loopOrder, &t.groupIn, &t.groupOut) != 13)
+      continue;
+    if (method < 0 || method > (int)kMethodNaive) continue;
+    c.method = (Method)method;
+    plan_cache().put(key, c);
+    n++;
+  }
+  fclose(f);
+  return n > 0 ? CUTT_SUCCESS : CUTT_INVALID_PARAMETER;
+}
+
+int cutt_c_plan_cache_size(void) {
+  std::lock_guard<std::mutex> lk(g_mutex);
+  return (int)plan_cache().size();
 }
 
 const char* cutt_c_version(void) { return "cutt-b200 0.1 (sm_100a)"; }

@@ -65,6 +65,12 @@ unsigned long long cutt_c_launch_count(void);
 /* Empties the plan cache (the cuttPlanMeasure winners). */
 void cutt_c_clear_plan_cache(void);
 
+/* Writes / reads the plan cache as a text file, so that winners measured in one process are
+ * reused by cuttPlan and cuttPlanMeasure in the next.  Keys include the device ordinal. */
+int cutt_c_plan_cache_save(const char* path);
+int cutt_c_plan_cache_load(const char* path);
+int cutt_c_plan_cache_size(void);
+
 const char* cutt_c_version(void);
 
 #ifdef __cplusplus
