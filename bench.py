@@ -9,6 +9,10 @@ Workloads (all data synthetic, seeded):
        objects, no collective, weak scaling.
   c4   rank-6 fp32 tensor with tiny leading dimensions.
   c3   the 100-case random rank 2-7 suite (fp64 and fp32); value = median over cases.
+  c5a  rank-4 fp32 (1024,1024,32,256), permutation (1,0,2,3), sharded on the last dimension over
+       the N ranks: slab mode, no communication (strong scaling: the 34 GB tensor is fixed).
+  c5b  same tensor, permutation (3,2,0,1): the sharded dimension moves, every rank stores its
+       tiles into the peers' output slabs from inside the kernel (NVLink all-to-all).
 
 Metric: effective GB/s = 2 * volume * sizeofType / time  (the reference's definition,
 src/cuttTimer.cpp:92,134-138), whole job over all ranks.  One JSON line on stdout (rank 0).
@@ -227,6 +231,9 @@ def run_ours(args):
             print(json.dumps(line))
         return 0
 
+    if args.workload in ("c5a", "c5b"):
+        return run_sharded(args, C, W, dist, world, rank, local, peak, peak_kind, barrier, max_over_ranks)
+
     cases = _workload_cases(args.workload)
     # device-resident inputs (seeded uniform values), one pair of buffers per case
     plans = []
@@ -366,6 +373,69 @@ def run_ours(args):
     return 0
 
 
+def run_sharded(args, C, W, dist, world, rank, local, peak, peak_kind, barrier, max_over_ranks):
+    """C5: the 2^33-element fp32 tensor sharded over the ranks (strong scaling)."""
+    import torch
+    from cutt_b200.multigpu import ShardedTranspose
+    dims = list(W.C5_DIMS)
+    if args.c5_scale > 1:           # smaller stand-in for quick checks: shrink dim 2
+        dims[2] = max(1, dims[2] // args.c5_scale)
+    perm = W.C5A_PERM if args.workload == "c5a" else W.C5B_PERM
+    elt = 4
+    vol = _vol(dims)
+    loc = vol // world
+    g = torch.Generator(device="cuda")
+    g.manual_seed(5 + rank)
+    inp = torch.rand(loc, dtype=torch.float32, device="cuda", generator=g)
+    st = ShardedTranspose(dims, perm, elt, measure_input=inp)
+    launches0 = C.launch_count()
+    for _ in range(max(3, args.warmup)):
+        st.execute(inp)
+    st.finish()
+    sampler = ClockSampler(_physical_gpu_index(local))
+    if rank == 0:
+        sampler.start()
+        time.sleep(0.3)
+    barrier()
+    l0 = C.launch_count()
+    e0 = torch.cuda.Event(enable_timing=True)
+    e1 = torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(args.steps):
+        st.execute(inp)
+    e1.record()
+    barrier()
+    ms = max_over_ranks(e0.elapsed_time(e1)) / args.steps
+    launches = C.launch_count() - l0
+    clocks = sampler.stop() if rank == 0 else None
+    total_bytes = 2 * vol * elt
+    value = total_bytes / (ms * 1e-3) / 1e9
+    per_gpu = value / world
+    line = base_line(args, value, ms, world)
+    line["scaling"] = "strong"
+    line["dtype"] = "b32 (bit moves)"
+    line["config"] = {"workload": "%s: rank-4 fp32 %s perm %s sharded on the last dim over %d GPU(s), mode %s"
+                      % (args.workload, dims, perm, world, "slab" if st.mode == 0 else "all-to-all by peer stores"),
+                      "l2": "inputs larger than L2 (%.1f GB per side per GPU)" % (loc * elt / 1e9),
+                      "per_gpu_gbs": per_gpu, "plan": json.loads(C.plan_describe(st.handle))["label"]}
+    line["roofline"] = {"bound": "hbm", "achieved": per_gpu, "peak": peak, "unit": UNIT, "frac": per_gpu / peak,
+                        "traffic": None, "kernel": "permute_tiles_kernel (per GPU)", "peak_kind": peak_kind}
+    if st.mode == 1 and world > 1:
+        remote = (world - 1) / world * loc * elt          # bytes each GPU sends over NVLink per step
+        nv = remote / (ms * 1e-3) / 1e9
+        line["nvlink"] = {"remote_gbs_per_gpu_per_direction": nv, "frac_of_770_measured": nv / 770.0,
+                          "frac_of_900_nominal": nv / 900.0}
+    line["gpu_launches"] = launches
+    line["clocks"] = clocks
+    line["e2e"] = None
+    st.close()
+    if rank == 0:
+        print(json.dumps(line))
+    if dist is not None:
+        dist.destroy_process_group()
+    return 0
+
+
 def _traffic_note(case_name):
     """DRAM bytes per launch of the dominant kernel from the committed ncu capture, if any."""
     p = os.path.join(ROOT, "profiles", "traffic.json")
@@ -441,7 +511,8 @@ def main():
     ap.add_argument("--steps", type=int, default=20)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--workload", default="c2", choices=["c1", "c2", "c3", "c4"])
+    ap.add_argument("--workload", default="c2", choices=["c1", "c2", "c3", "c4", "c5a", "c5b"])
+    ap.add_argument("--c5-scale", type=int, default=1, help="divide dim 2 of the C5 tensor (quick checks)")
     ap.add_argument("--suite-cases", type=int, default=100)
     ap.add_argument("--no-extras", action="store_true")
     ap.add_argument("--no-cpu-baseline", action="store_true")

@@ -12,6 +12,7 @@
 // memory; measured winners are remembered in an LRU plan cache that cuttPlan consults.
 #include "../../include/cutt.h"
 #include "../../include/cutt_c.h"
+#include "../../include/cutt_mg.h"
 
 #include <cstdio>
 #include <cstdlib>
@@ -45,6 +46,11 @@ struct Plan {
   NaiveDesc naive;
   int numSM = 148;
   std::string note;
+  // multi-GPU plans (cutt_mg.h)
+  int mgWorld = 0;
+  int mgMe = 0;
+  int mgMode = -1;
+  long long mgLocalVolume = 0;
 };
 
 struct CachedChoice {
@@ -176,7 +182,22 @@ bool finalize_tiles(const DeviceInfo& dev, Candidate& c, int& grid) {
   return true;
 }
 
-cudaError_t run_plan(const Plan& p, const void* in, void* out, cudaStream_t stream) {
+cudaError_t run_plan(const Plan& p, const void* in, void* out, cudaStream_t stream,
+                     void* const* peers = nullptr) {
+  if (p.mgMode == 1) {
+    // all-to-all: the kernel picks the destination slab per tile; element-aligned fallback
+    // when any of the slabs is not aligned for the plan's vector width
+    if (p.method != kMethodTiles || !peers) return cudaErrorInvalidValue;
+    PeerPtrs pp;
+    bool aligned = true;
+    for (int i = 0; i < kMaxPeers; i++) {
+      pp.p[i] = (unsigned char*)peers[i < p.mgWorld ? i : 0];
+      aligned = aligned && tiles_pointers_aligned(p.cand, in, pp.p[i]);
+    }
+    if (aligned) return launch_tiles(p.cand, p.grid, in, pp, stream);
+    if (p.haveFallback) return launch_tiles(p.fallback, p.fallbackGrid, in, pp, stream);
+    return cudaErrorInvalidValue;
+  }
   switch (p.method) {
     case kMethodMemcpy:
       return cudaMemcpyAsync(out, in, p.bytes, cudaMemcpyDeviceToDevice, stream);
@@ -221,6 +242,9 @@ struct PlanRequest {
   PlanMode mode = kByModel;
   void* idata = nullptr;
   void* odata = nullptr;
+  int world = 0;               // > 0: multi-GPU plan for rank `me`
+  int me = 0;
+  void* const* peers = nullptr;  // output slabs per rank (measure mode)
   int index = 0;
   int method = kMethodTiles;
   TileParams params;
@@ -246,20 +270,43 @@ cuttResult make_plan(cuttHandle* handle, int rank, const int* dim, const int* pe
   p->stream = stream;
   p->elt = (int)elt;
   p->numSM = dev.numSM;
-  size_t vol = 1;
-  for (int i = 0; i < rank; i++) vol *= (size_t)dim[i];
-  p->bytes = vol * elt;
-  if (rank <= 32) fill_naive(*p, rank, dim, perm);
-  else return CUTT_INVALID_PARAMETER;
-
+  if (rank > 32) return CUTT_INVALID_PARAMETER;
   const bool verbose = env_flag("CUTT_VERBOSE");
   bool ok = false;
-  const bool canon = problem_from_cutt(rank, dim, perm, (int)elt, p->prob);
-  const std::string key = problem_key(devId, rank, dim, perm, elt);
+  bool canon = false;
+  std::string key = problem_key(devId, rank, dim, perm, elt);
+  if (req.world > 0) {
+    ShardInfo info;
+    if (!problem_from_cutt_sharded(rank, dim, perm, (int)elt, req.world, req.me, p->prob, info))
+      return CUTT_INVALID_PARAMETER;
+    canon = true;
+    p->mgWorld = req.world;
+    p->mgMe = req.me;
+    p->mgMode = info.mode;
+    p->mgLocalVolume = info.localVolume;
+    p->bytes = (size_t)info.localVolume * elt;
+    if (info.mode == 0) fill_naive(*p, rank, info.localDim, perm);
+    key += "/mg" + std::to_string(req.world) + "." + std::to_string(req.me);
+  } else {
+    size_t vol = 1;
+    for (int i = 0; i < rank; i++) vol *= (size_t)dim[i];
+    p->bytes = vol * elt;
+    fill_naive(*p, rank, dim, perm);
+    canon = problem_from_cutt(rank, dim, perm, (int)elt, p->prob);
+  }
+  void* const* peers = req.peers;
+  void* measureOut = req.odata;
+  if (req.world > 0 && req.mode == kByMeasure) {
+    if (!peers) return CUTT_INVALID_PARAMETER;
+    measureOut = peers[req.me];
+    if (req.idata == measureOut) return CUTT_INVALID_PARAMETER;
+  }
 
   if (!canon) {
     p->method = kMethodNaive;  // fused rank beyond the tiled kernel's limit
     ok = true;
+  } else if (p->mgMode == 1 && req.mode != kByModel && req.mode != kByMeasure && req.mode != kByIndex) {
+    return CUTT_INVALID_PARAMETER;
   } else if (req.mode == kByParams) {
     if (req.method == kMethodNaive) { p->method = kMethodNaive; ok = true; }
     else if (req.method == kMethodCopy || req.method == kMethodMemcpy) {
@@ -274,6 +321,7 @@ cuttResult make_plan(cuttHandle* handle, int rank, const int* dim, const int* pe
   } else {
     std::vector<Candidate> cands = enumerate_candidates(p->prob, dev);
     if (cands.empty()) {
+      if (p->mgMode == 1) return CUTT_INTERNAL_ERROR;  // no local fallback can write peer slabs
       p->method = kMethodNaive;
       ok = true;
     } else if (req.mode == kByIndex) {
@@ -305,7 +353,7 @@ cuttResult make_plan(cuttHandle* handle, int rank, const int* dim, const int* pe
         cudaEvent_t e0, e1;
         if (cudaEventCreate(&e0) != cudaSuccess || cudaEventCreate(&e1) != cudaSuccess)
           return CUTT_INTERNAL_ERROR;
-        if (cudaMemsetAsync(req.odata, 0xFF, p->bytes, stream) != cudaSuccess ||
+        if (cudaMemsetAsync(measureOut, 0xFF, p->bytes, stream) != cudaSuccess ||
             cudaDeviceSynchronize() != cudaSuccess) {
           cudaEventDestroy(e0); cudaEventDestroy(e1);
           return CUTT_INTERNAL_ERROR;
@@ -315,11 +363,11 @@ cuttResult make_plan(cuttHandle* handle, int rank, const int* dim, const int* pe
         Plan trial = *p;
         for (size_t i = 0; i < cands.size() && i < topk; i++) {
           if (!adopt_candidate(trial, dev, cands[i])) continue;
-          bool fail = run_plan(trial, req.idata, req.odata, stream) != cudaSuccess;
+          bool fail = run_plan(trial, req.idata, measureOut, stream, peers) != cudaSuccess;
           double tmin = 1e30;
           for (int rep = 0; rep < 3 && !fail; rep++) {
             cudaEventRecord(e0, stream);
-            fail = run_plan(trial, req.idata, req.odata, stream) != cudaSuccess;
+            fail = run_plan(trial, req.idata, measureOut, stream, peers) != cudaSuccess;
             cudaEventRecord(e1, stream);
             if (cudaEventSynchronize(e1) != cudaSuccess) fail = true;
             float ms = 0.f;
@@ -395,6 +443,7 @@ cuttResult cuttExecute(cuttHandle handle, void* idata, void* odata) {
     p = it->second.get();
   }
   if (idata == odata) return CUTT_INVALID_PARAMETER;
+  if (p->mgMode == 1) return CUTT_INVALID_PARAMETER;  // needs the peers' slabs: cutt_mg_execute
   int dev = 0;
   if (cudaGetDevice(&dev) != cudaSuccess) return CUTT_INTERNAL_ERROR;
   if (dev != p->device) return CUTT_INVALID_DEVICE;
@@ -528,6 +577,103 @@ int cutt_c_transpose_host(int rank, const int* dim, const int* permutation, size
   if (r != CUTT_SUCCESS) return r;
   if (cudaMemcpyAsync(hout, dOut, bytes, cudaMemcpyDeviceToHost, 0) != cudaSuccess) return CUTT_INTERNAL_ERROR;
   if (cudaStreamSynchronize(0) != cudaSuccess) return CUTT_INTERNAL_ERROR;
+  return CUTT_SUCCESS;
+}
+
+// ---- multi-GPU extension (include/cutt_mg.h) ----
+
+int cutt_mg_plan(unsigned int* handle, int rank, const int* dim, const int* permutation,
+                 size_t sizeofType, void* stream, int world, int me) {
+  if (world < 1 || world > CUTT_MG_MAX_WORLD || me < 0 || me >= world) return CUTT_INVALID_PARAMETER;
+  PlanRequest req;
+  req.world = world;
+  req.me = me;
+  return (int)make_plan(handle, rank, dim, permutation, sizeofType, (cudaStream_t)stream, req);
+}
+
+int cutt_mg_plan_measure(unsigned int* handle, int rank, const int* dim, const int* permutation,
+                         size_t sizeofType, void* stream, int world, int me, void* idata,
+                         void* const* odata) {
+  if (world < 1 || world > CUTT_MG_MAX_WORLD || me < 0 || me >= world) return CUTT_INVALID_PARAMETER;
+  if (!idata || !odata) return CUTT_INVALID_PARAMETER;
+  PlanRequest req;
+  req.mode = kByMeasure;
+  req.world = world;
+  req.me = me;
+  req.idata = idata;
+  req.peers = odata;
+  return (int)make_plan(handle, rank, dim, permutation, sizeofType, (cudaStream_t)stream, req);
+}
+
+int cutt_mg_mode(unsigned int handle) {
+  std::lock_guard<std::mutex> lk(g_mutex);
+  auto it = g_plans.find(handle);
+  if (it == g_plans.end() || it->second->mgWorld == 0) return -1;
+  return it->second->mgMode;
+}
+
+long long cutt_mg_local_volume(unsigned int handle) {
+  std::lock_guard<std::mutex> lk(g_mutex);
+  auto it = g_plans.find(handle);
+  if (it == g_plans.end() || it->second->mgWorld == 0) return -1;
+  return it->second->mgLocalVolume;
+}
+
+int cutt_mg_execute(unsigned int handle, void* idata, void* const* odata) {
+  const Plan* p = nullptr;
+  {
+    std::lock_guard<std::mutex> lk(g_mutex);
+    auto it = g_plans.find(handle);
+    if (it == g_plans.end()) return CUTT_INVALID_PLAN;
+    p = it->second.get();
+  }
+  if (p->mgWorld == 0 || !odata || !idata) return CUTT_INVALID_PARAMETER;
+  for (int h = 0; h < p->mgWorld; h++)
+    if (!odata[h] || odata[h] == idata) return CUTT_INVALID_PARAMETER;
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess) return CUTT_INTERNAL_ERROR;
+  if (dev != p->device) return CUTT_INVALID_DEVICE;
+  return run_plan(*p, idata, odata[p->mgMe], p->stream, odata) == cudaSuccess ? CUTT_SUCCESS
+                                                                              : CUTT_INTERNAL_ERROR;
+}
+
+int cutt_mg_ipc_export(void* devptr, unsigned char token[CUTT_MG_IPC_BYTES]) {
+  static_assert(sizeof(cudaIpcMemHandle_t) == CUTT_MG_IPC_BYTES, "token size");
+  if (!devptr || !token) return CUTT_INVALID_PARAMETER;
+  cudaIpcMemHandle_t h;
+  if (cudaIpcGetMemHandle(&h, devptr) != cudaSuccess) { cudaGetLastError(); return CUTT_INTERNAL_ERROR; }
+  memcpy(token, &h, sizeof h);
+  return CUTT_SUCCESS;
+}
+
+int cutt_mg_ipc_open(const unsigned char token[CUTT_MG_IPC_BYTES], void** devptr) {
+  if (!devptr || !token) return CUTT_INVALID_PARAMETER;
+  cudaIpcMemHandle_t h;
+  memcpy(&h, token, sizeof h);
+  if (cudaIpcOpenMemHandle(devptr, h, cudaIpcMemLazyEnablePeerAccess) != cudaSuccess) {
+    cudaGetLastError();
+    return CUTT_INTERNAL_ERROR;
+  }
+  return CUTT_SUCCESS;
+}
+
+int cutt_mg_ipc_close(void* devptr) {
+  if (!devptr) return CUTT_INVALID_PARAMETER;
+  return cudaIpcCloseMemHandle(devptr) == cudaSuccess ? CUTT_SUCCESS : CUTT_INTERNAL_ERROR;
+}
+
+int cutt_mg_enable_peer_access(int world) {
+  int dev = 0, n = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || cudaGetDeviceCount(&n) != cudaSuccess) return CUTT_INTERNAL_ERROR;
+  if (world < 1 || world > n) return CUTT_INVALID_PARAMETER;
+  for (int d = 0; d < world; d++) {
+    if (d == dev) continue;
+    int can = 0;
+    if (cudaDeviceCanAccessPeer(&can, dev, d) != cudaSuccess || !can) return CUTT_INVALID_DEVICE;
+    cudaError_t e = cudaDeviceEnablePeerAccess(d, 0);
+    if (e != cudaSuccess && e != cudaErrorPeerAccessAlreadyEnabled) { cudaGetLastError(); return CUTT_INTERNAL_ERROR; }
+    cudaGetLastError();
+  }
   return CUTT_SUCCESS;
 }
 

@@ -16,6 +16,9 @@ using namespace cuttb;
 // other: same shared-memory layout (tables, the two context slots, the stage buffers), same
 // order of decode / load / store steps per block.  Threads of a block run one after the
 // other inside each step, so data races are not modelled, layout overlaps are.
+// Output base pointers per destination GPU (host emulation of PeerPtrs); null = single output.
+static unsigned char* const* g_peerOuts = nullptr;
+
 template <int ELT, int WIN, int WOUT, int V, bool WIDE>
 static void run_desc(const TileDesc& D, const unsigned char* in, unsigned char* out) {
   const uint32_t G = D.numTiles < 3 ? D.numTiles : 3;
@@ -38,7 +41,8 @@ static void run_desc(const TileDesc& D, const unsigned char* in, unsigned char* 
     };
     auto store = [&](const TileCtx& c, unsigned char* st) {
       if (!c.valid) return;
-      for (uint32_t tid = 0; tid < D.nthreads; tid++) tile_store<ELT, WOUT, V, WIDE>(D, c, T, st, out, tid);
+      unsigned char* o = (D.peerLoopDim >= 0 && g_peerOuts) ? g_peerOuts[c.peer] : out;
+      for (uint32_t tid = 0; tid < D.nthreads; tid++) tile_store<ELT, WOUT, V, WIDE>(D, c, T, st, o, tid);
     };
     if (D.stages >= 2) {
       load(cur, stage0);
@@ -137,6 +141,45 @@ int cutt_hostcheck_run_params(int rank, const int* dim, const int* perm, int elt
   if (!build_tile(P, tp, g_dev, c)) return 5;
   if (label && labelLen > 0) snprintf(label, labelLen, "%s", describe(P, c).c_str());
   return dispatch_checked(c.desc, (const unsigned char*)in, (unsigned char*)out, (size_t)P.volume * elt);
+}
+
+// Sharded permutation, rank `me` of `world`: `in` is the local input slab, `outs[h]` the output
+// slab of GPU h (all of them host arrays here).  Returns the mode (0 slab, 1 all-to-all) or a
+// negative code.  Candidate `index` of the enumeration is executed.
+int cutt_hostcheck_run_sharded(int rank, const int* dim, const int* perm, int elt, int world, int me,
+                               int index, const void* in, void* const* outs, char* label, int labelLen) {
+  Problem P;
+  ShardInfo info;
+  if (!problem_from_cutt_sharded(rank, dim, perm, elt, world, me, P, info)) return -2;
+  std::vector<Candidate> cands = enumerate_candidates(P, g_dev);
+  if (cands.empty()) return -3;
+  if (index < 0) index = 0;
+  index %= (int)cands.size();
+  const Candidate& c = cands[index];
+  if (label && labelLen > 0) snprintf(label, labelLen, "%s", describe(P, c).c_str());
+  const size_t bytes = (size_t)info.localVolume * elt;
+  if (c.method != kMethodTiles) {
+    if (info.mode != 0) return -4;
+    memcpy(outs[me], in, bytes);
+    return 0;
+  }
+  HostBounds& b = host_bounds();
+  b.gin0 = (const unsigned char*)in; b.gin1 = b.gin0 + bytes; b.violations = 0;
+  // outputs: accept any address inside any destination slab
+  const unsigned char* lo = (const unsigned char*)outs[0];
+  const unsigned char* hi = lo + bytes;
+  for (int h = 0; h < world; h++) {
+    const unsigned char* p = (const unsigned char*)outs[h];
+    if (p < lo) lo = p;
+    if (p + bytes > hi) hi = p + bytes;
+  }
+  b.gout0 = lo; b.gout1 = hi;
+  g_peerOuts = (unsigned char* const*)outs;
+  int rc = dispatch(c.desc, (const unsigned char*)in, (unsigned char*)outs[info.mode == 0 ? me : 0]);
+  g_peerOuts = nullptr;
+  if (rc) return -5;
+  if (b.violations) return -9;
+  return info.mode;
 }
 
 // Exhaustive-ish self check of the division helper: returns the number of mismatches.

@@ -60,6 +60,50 @@ bool problem_from_cutt(int rank, const int* dim, const int* perm, int elt, Probl
   return canonicalize(rank, d.data(), is.data(), os.data(), elt, -1, P);
 }
 
+bool problem_from_cutt_sharded(int rank, const int* dim, const int* perm, int elt, int world, int me,
+                               Problem& P, ShardInfo& info) {
+  info = ShardInfo();
+  if (rank < 2 || rank > 31 || world < 1 || world > kMaxPeers || me < 0 || me >= world) return false;
+  const int last = rank - 1;
+  const int s = perm[last];  // input dimension that is slowest in the output
+  if (dim[last] % world != 0 || dim[s] % world != 0) return false;
+  for (int i = 0; i < rank; i++) info.localDim[i] = dim[i];
+  info.localDim[last] = dim[last] / world;
+  info.localVolume = 1;
+  for (int i = 0; i < rank; i++) info.localVolume *= info.localDim[i];
+  if (s == last) {
+    info.mode = 0;
+    return problem_from_cutt(rank, info.localDim, perm, elt, P);
+  }
+  info.mode = 1;
+  // input strides of the local slab; output strides of one output slab (extent dim[s]/world last)
+  std::vector<int64_t> is(rank), os(rank);
+  int64_t acc = 1;
+  for (int i = 0; i < rank; i++) { is[i] = acc; acc *= info.localDim[i]; }
+  acc = 1;
+  for (int k = 0; k < rank; k++) {
+    os[perm[k]] = acc;
+    acc *= (perm[k] == s) ? dim[s] / world : dim[perm[k]];
+  }
+  // dimensions: all input dims with dim[s] cut to its inner part, plus the peer dimension
+  std::vector<int64_t> d2, is2, os2;
+  int peer = -1;
+  for (int i = 0; i < rank; i++) {
+    if (i == s) {
+      d2.push_back(dim[s] / world); is2.push_back(is[s]); os2.push_back(os[s]);
+      peer = (int)d2.size();
+      d2.push_back(world); is2.push_back(is[s] * (dim[s] / world)); os2.push_back(0);
+    } else {
+      d2.push_back(info.localDim[i]); is2.push_back(is[i]); os2.push_back(os[i]);
+    }
+  }
+  if (!canonicalize((int)d2.size(), d2.data(), is2.data(), os2.data(), elt, peer, P)) return false;
+  // this GPU's slab of input dimension `last` lands at this offset of every output slab
+  P.outBase = (int64_t)me * info.localDim[last] * os[last];
+  P.identity = false;
+  return true;
+}
+
 // chunk of about `want` elements out of d, with equal-sized chunks except possibly the last;
 // chunks are rounded up to a multiple of `mult` (vector width) when that is small against them
 static int64_t balanced_chunk(int64_t d, int64_t want, int64_t mult = 1) {
@@ -99,7 +143,11 @@ bool build_tile(const Problem& P, const TileParams& tp, const DeviceInfo& dev, C
   // output order
   int oo[kMaxDims];
   for (int j = 0; j < r; j++) oo[j] = j;
-  std::stable_sort(oo, oo + r, [&](int a, int b) { return P.os[a] < P.os[b]; });
+  // (the peer dimension has no output stride: it goes last and never joins a run)
+  std::stable_sort(oo, oo + r, [&](int a, int b) {
+    if ((a == P.peerDim) != (b == P.peerDim)) return b == P.peerDim;
+    return P.os[a] < P.os[b];
+  });
 
   const int64_t tin = std::max<int64_t>(1, tp.tinBytes / elt);
   const int64_t tout = std::max<int64_t>(1, tp.toutBytes / elt);

@@ -42,6 +42,21 @@ bool canonicalize(int rank, const int64_t* d, const int64_t* is, const int64_t* 
 // cuTT convention (dim[0] fastest, outDim[i] = dim[perm[i]]) -> Problem.
 bool problem_from_cutt(int rank, const int* dim, const int* perm, int elt, Problem& P);
 
+// A tensor sharded over `world` GPUs of one box: the input along its slowest dimension, the
+// output along ITS slowest dimension (= input dimension perm[rank-1]), both in equal parts.
+struct ShardInfo {
+  int mode = -1;            // 0 slab: each GPU permutes its own slab, no communication
+                            // 1 all-to-all: each GPU writes pieces of every GPU's output slab
+                            // -1 not shardable this way (extents not divisible)
+  int64_t localVolume = 0;  // elements of one input slab (= one output slab)
+  int localDim[32];         // extents of the local input slab (mode 0: a plain cuTT problem)
+};
+
+// Builds rank `me`'s part of the sharded permutation as a strided-copy Problem.  In mode 1 the
+// Problem carries a peer dimension: its coordinate names the GPU whose output slab is written.
+bool problem_from_cutt_sharded(int rank, const int* dim, const int* perm, int elt, int world, int me,
+                               Problem& P, ShardInfo& info);
+
 enum Method : int {
   kMethodCopy = 0,     // identity after fusion: contiguous copy kernel
   kMethodMemcpy = 1,   // identity: cudaMemcpyAsync device-to-device
