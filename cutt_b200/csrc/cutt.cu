@@ -637,12 +637,41 @@ int cutt_mg_execute(unsigned int handle, void* idata, void* const* odata) {
                                                                               : CUTT_INTERNAL_ERROR;
 }
 
+// Base address of the allocation that contains p (driver entry point looked up at run time so
+// that the library keeps linking with the CUDA runtime alone).
+static bool allocation_base(void* p, unsigned long long& base) {
+  typedef int (*GetRange)(unsigned long long*, size_t*, unsigned long long);
+  static GetRange fn = nullptr;
+  static bool tried = false;
+  if (!tried) {
+    tried = true;
+    void* sym = nullptr;
+    cudaDriverEntryPointQueryResult qr;
+    if (cudaGetDriverEntryPoint("cuMemGetAddressRange", &sym, cudaEnableDefault, &qr) == cudaSuccess &&
+        qr == cudaDriverEntryPointSuccess)
+      fn = (GetRange)sym;
+    else
+      cudaGetLastError();
+  }
+  if (!fn) return false;
+  size_t size = 0;
+  return fn(&base, &size, (unsigned long long)(uintptr_t)p) == 0;
+}
+
+static std::mutex g_ipcMutex;
+static std::unordered_map<void*, void*> g_ipcBases;  // mapped buffer address -> mapped allocation base
+
 int cutt_mg_ipc_export(void* devptr, unsigned char token[CUTT_MG_IPC_BYTES]) {
-  static_assert(sizeof(cudaIpcMemHandle_t) == CUTT_MG_IPC_BYTES, "token size");
+  static_assert(sizeof(cudaIpcMemHandle_t) == 64, "token layout");
   if (!devptr || !token) return CUTT_INVALID_PARAMETER;
+  unsigned long long base = 0;
+  if (!allocation_base(devptr, base)) return CUTT_INTERNAL_ERROR;
   cudaIpcMemHandle_t h;
-  if (cudaIpcGetMemHandle(&h, devptr) != cudaSuccess) { cudaGetLastError(); return CUTT_INTERNAL_ERROR; }
+  if (cudaIpcGetMemHandle(&h, (void*)(uintptr_t)base) != cudaSuccess) { cudaGetLastError(); return CUTT_INTERNAL_ERROR; }
+  memset(token, 0, CUTT_MG_IPC_BYTES);
   memcpy(token, &h, sizeof h);
+  unsigned long long off = (unsigned long long)(uintptr_t)devptr - base;
+  memcpy(token + 64, &off, sizeof off);
   return CUTT_SUCCESS;
 }
 
@@ -650,16 +679,30 @@ int cutt_mg_ipc_open(const unsigned char token[CUTT_MG_IPC_BYTES], void** devptr
   if (!devptr || !token) return CUTT_INVALID_PARAMETER;
   cudaIpcMemHandle_t h;
   memcpy(&h, token, sizeof h);
-  if (cudaIpcOpenMemHandle(devptr, h, cudaIpcMemLazyEnablePeerAccess) != cudaSuccess) {
+  unsigned long long off = 0;
+  memcpy(&off, token + 64, sizeof off);
+  void* base = nullptr;
+  if (cudaIpcOpenMemHandle(&base, h, cudaIpcMemLazyEnablePeerAccess) != cudaSuccess) {
     cudaGetLastError();
     return CUTT_INTERNAL_ERROR;
   }
+  *devptr = (unsigned char*)base + off;
+  std::lock_guard<std::mutex> lk(g_ipcMutex);
+  g_ipcBases[*devptr] = base;
   return CUTT_SUCCESS;
 }
 
 int cutt_mg_ipc_close(void* devptr) {
   if (!devptr) return CUTT_INVALID_PARAMETER;
-  return cudaIpcCloseMemHandle(devptr) == cudaSuccess ? CUTT_SUCCESS : CUTT_INTERNAL_ERROR;
+  void* base = nullptr;
+  {
+    std::lock_guard<std::mutex> lk(g_ipcMutex);
+    auto it = g_ipcBases.find(devptr);
+    if (it == g_ipcBases.end()) return CUTT_INVALID_PARAMETER;
+    base = it->second;
+    g_ipcBases.erase(it);
+  }
+  return cudaIpcCloseMemHandle(base) == cudaSuccess ? CUTT_SUCCESS : CUTT_INTERNAL_ERROR;
 }
 
 int cutt_mg_enable_peer_access(int world) {

@@ -484,6 +484,58 @@ bool build_tile(const Problem& P, const TileParams& tp, const DeviceInfo& dev, C
              D.split[1].used ? tp.groupOut : 1);
   }
   out.label = buf;
+
+  // features of the cost model
+  {
+    float* f = out.feat;
+    for (int i = 0; i < kNumFeatures; i++) f[i] = 0.f;
+    auto lg = [](double x) { return (float)std::log2(x < 1.0 ? 1.0 : x); };
+    int nslot = 0;
+    for (int j = 0; j < r; j++) if (slotOf[j] >= 0) nslot++;
+    // distance (bytes) between consecutive rows of each side = stride of its first row dimension
+    double inRowStride = 0, outRowStride = 0;
+    bool inAligned = true, outAligned = true;  // every run starts on a 32-byte sector boundary
+    for (int j = 0; j < r; j++) {
+      if (P.d[j] <= 1) continue;
+      if (!inRun[j]) { if (t[j] > 1 && inRowStride == 0) inRowStride = (double)P.is[j] * elt; if ((P.is[j] * elt) % 32) inAligned = false; }
+      else if (j == inRunLast && t[j] < P.d[j] && (P.is[j] * t[j] * elt) % 32) inAligned = false;
+      if (j == P.peerDim) continue;
+      if (!outRun[j]) { if (t[j] > 1 && outRowStride == 0) outRowStride = (double)P.os[j] * elt; if ((P.os[j] * elt) % 32) outAligned = false; }
+      else if (j == outRunLast && t[j] < P.d[j] && (P.os[j] * t[j] * elt) % 32) outAligned = false;
+    }
+    f[0] = (float)elt;
+    f[1] = lg((double)D.in.run * elt);
+    f[2] = lg((double)D.out.run * elt);
+    f[3] = (float)(D.in.vec * elt);
+    f[4] = (float)(D.out.vec * elt);
+    f[5] = (float)(D.vblk * elt);
+    f[6] = lg(D.in.nrows);
+    f[7] = lg((double)D.out.nrows * D.vblk);
+    f[8] = lg((double)D.tileElems * elt);
+    f[9] = (float)out.smemBytes / 1024.f;
+    f[10] = (float)tp.nthreads / 256.f;
+    f[11] = (float)tp.loopOrder;
+    f[12] = D.split[0].used ? (float)tp.groupIn : 1.f;
+    f[13] = D.split[1].used ? (float)tp.groupOut : 1.f;
+    f[14] = (float)out.blocksPerSM;
+    f[15] = lg(D.numTiles);
+    f[16] = (float)std::min(64.0, (double)D.numTiles / ((double)dev.numSM * out.blocksPerSM));
+    f[17] = D.in.nRowDims <= 1 ? 1.f : 0.f;
+    f[18] = D.out.nRowDims <= 1 ? 1.f : 0.f;
+    f[19] = (float)D.smemGatherContig;
+    f[20] = (r > 0 && t[0] == P.d[0]) ? 1.f : 0.f;
+    f[21] = inAligned ? 1.f : 0.f;
+    f[22] = outAligned ? 1.f : 0.f;
+    f[23] = lg((double)P.volume * elt);
+    f[24] = (float)nslot;
+    f[25] = lg(D.in.tq);
+    f[26] = lg(D.out.tq);
+    f[27] = (float)D.nLoopDims;
+    f[28] = lg(inRowStride);
+    f[29] = lg(outRowStride);
+    f[30] = (float)D.wide;
+    f[31] = (float)P.rank;
+  }
   out.cost = model_cost(P, out, dev);
   return true;
 }
@@ -553,7 +605,7 @@ std::vector<Candidate> enumerate_candidates(const Problem& P, const DeviceInfo& 
 }
 
 std::string describe(const Problem& P, const Candidate& c) {
-  char buf[1024];
+  char buf[2048];
   std::string dims, iss, oss;
   for (int j = 0; j < P.rank; j++) {
     snprintf(buf, sizeof buf, "%s%lld", j ? "," : "", (long long)P.d[j]); dims += buf;
@@ -562,10 +614,16 @@ std::string describe(const Problem& P, const Candidate& c) {
   }
   snprintf(buf, sizeof buf,
            "{\"method\": %d, \"label\": \"%s\", \"fused_dims\": [%s], \"istride\": [%s], \"ostride\": [%s], "
-           "\"elt\": %d, \"num_tiles\": %u, \"grid\": %d, \"smem\": %d, \"model_us\": %.2f}",
+           "\"elt\": %d, \"num_tiles\": %u, \"grid\": %d, \"smem\": %d, \"model_us\": %.2f, \"feat\": [",
            (int)c.method, c.label.c_str(), dims.c_str(), iss.c_str(), oss.c_str(), P.elt,
            c.method == kMethodTiles ? c.desc.numTiles : 0u, c.gridBlocks, c.smemBytes, c.cost * 1e6);
-  return buf;
+  std::string res = buf;
+  for (int i = 0; i < kNumFeatures; i++) {
+    snprintf(buf, sizeof buf, "%s%.4g", i ? "," : "", c.method == kMethodTiles ? (double)c.feat[i] : 0.0);
+    res += buf;
+  }
+  res += "]}";
+  return res;
 }
 
 }  // namespace cuttb

@@ -78,8 +78,11 @@ struct TileParams {
   int groupOut = 1;            // then this many along the output run's chunked dimension
 };
 
+constexpr int kNumFeatures = 32;
+
 struct Candidate {
   Method method = kMethodTiles;
+  float feat[kNumFeatures] = {0};  // inputs of the cost model (see candidate_features in planner.cpp)
   TileParams params;
   TileDesc desc;
   int smemBytes = 0;

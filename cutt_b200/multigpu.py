@@ -15,7 +15,7 @@ from typing import List, Sequence
 
 from . import CUTT_SUCCESS, CuttError, _iarr, lib
 
-IPC_BYTES = 64
+IPC_BYTES = 80
 
 
 def shard_shapes(dims: Sequence[int], perm: Sequence[int], world: int):

@@ -18,8 +18,10 @@
  * Both extents must be divisible by world, otherwise planning returns CUTT_INVALID_PARAMETER.
  *
  * Process model: one rank per GPU.  Ranks may be threads or processes.  With processes, each
- * rank exports its output slab with cutt_mg_ipc_export, the 64-byte tokens travel through any
- * host channel (torch.distributed, MPI, a pipe), and cutt_mg_ipc_open maps a peer's slab.
+ * rank exports its output slab with cutt_mg_ipc_export, the tokens travel through any
+ * host channel (torch.distributed, MPI, a pipe), and cutt_mg_ipc_open maps a peer's slab.  The
+ * buffer may sit anywhere inside a larger allocation (pooling allocators): the token records its
+ * offset and cutt_mg_ipc_open returns the address of the buffer itself.
  * Within one process cudaDeviceEnablePeerAccess (or cutt_mg_enable_peer_access) is enough.
  *
  * Completion: cutt_mg_execute is asynchronous on the plan's stream.  A rank's output slab is
@@ -39,7 +41,7 @@ extern "C" {
 #endif
 
 #define CUTT_MG_MAX_WORLD 8
-#define CUTT_MG_IPC_BYTES 64
+#define CUTT_MG_IPC_BYTES 80   /* CUDA IPC handle (64) + offset of the buffer inside its allocation (8) + reserved (8) */
 
 /* Plan for rank `me` of `world` on the current device.  dim/permutation describe the GLOBAL
  * tensor.  The handle lives in the same table as cuttPlan's (destroy with cuttDestroy /
