@@ -227,6 +227,7 @@ bool adopt_candidate(Plan& p, const DeviceInfo& dev, const Candidate& c) {
     TileParams tp = c.params;
     tp.maxVecBytes = p.elt;
     tp.maxVBytes = p.elt;
+    tp.allowAof = 0;
     Candidate f;
     if (build_tile(p.prob, tp, dev, f) && finalize_tiles(dev, f, p.fallbackGrid)) {
       p.fallback = f;

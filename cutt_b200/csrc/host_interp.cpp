@@ -19,7 +19,7 @@ using namespace cuttb;
 // Output base pointers per destination GPU (host emulation of PeerPtrs); null = single output.
 static unsigned char* const* g_peerOuts = nullptr;
 
-template <int ELT, int WIN, int WOUT, int V, bool WIDE>
+template <int ELT, int WIN, int WOUT, int V, bool WIDE, bool AOF>
 static void run_desc(const TileDesc& D, const unsigned char* in, unsigned char* out) {
   const uint32_t G = D.numTiles < 3 ? D.numTiles : 3;
   std::vector<unsigned char> smem(D.tableBytes + D.stages * D.stageBytes);
@@ -37,12 +37,12 @@ static void run_desc(const TileDesc& D, const unsigned char* in, unsigned char* 
     TileCtx cur = ctxs[0], nxt = cur;
     auto load = [&](const TileCtx& c, unsigned char* st) {
       if (!c.valid) return;
-      for (uint32_t tid = 0; tid < D.nthreads; tid++) tile_load<ELT, WIN, WIDE>(D, c, T, st, in, tid);
+      for (uint32_t tid = 0; tid < D.nthreads; tid++) tile_load<ELT, WIN, WIDE, AOF>(D, c, T, st, in, tid);
     };
     auto store = [&](const TileCtx& c, unsigned char* st) {
       if (!c.valid) return;
       unsigned char* o = (D.peerLoopDim >= 0 && g_peerOuts) ? g_peerOuts[c.peer] : out;
-      for (uint32_t tid = 0; tid < D.nthreads; tid++) tile_store<ELT, WOUT, V, WIDE>(D, c, T, st, o, tid);
+      for (uint32_t tid = 0; tid < D.nthreads; tid++) tile_store<ELT, WOUT, V, WIDE, AOF>(D, c, T, st, in, o, tid);
     };
     if (D.stages >= 2) {
       load(cur, stage0);
@@ -81,10 +81,17 @@ static int dispatch_checked(const TileDesc& D, const unsigned char* in, unsigned
 }
 
 static int dispatch(const TileDesc& D, const unsigned char* in, unsigned char* out) {
+  if (D.aof) {
+    if (D.wide || D.vblk != 1) return 4;
+#define ACASE(E, A, B) if (D.elt == E && D.in.vec == A && D.out.vec == B) { run_desc<E, A, B, 1, false, true>(D, in, out); return 0; }
+    ACASE(4, 4, 1) ACASE(4, 4, 2) ACASE(4, 4, 4) ACASE(8, 2, 1) ACASE(8, 2, 2)
+#undef ACASE
+    return 4;
+  }
 #define CASE(E, A, B, V) \
   if (D.elt == E && D.in.vec == A && D.out.vec == B && D.vblk == V) { \
-    if (D.wide) { if (V != 1) return 4; run_desc<E, A, B, 1, true>(D, in, out); } \
-    else run_desc<E, A, B, V, false>(D, in, out); \
+    if (D.wide) { if (V != 1) return 4; run_desc<E, A, B, 1, true, false>(D, in, out); } \
+    else run_desc<E, A, B, V, false, false>(D, in, out); \
     return 0; }
 #define CASES_V(E, A, B) CASE(E, A, B, 1) CASE(E, A, B, 2) CASE(E, A, B, 4)
   CASES_V(4, 1, 1) CASES_V(4, 1, 2) CASES_V(4, 1, 4) CASES_V(4, 2, 1) CASES_V(4, 2, 2) CASES_V(4, 2, 4)

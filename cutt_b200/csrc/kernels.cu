@@ -25,7 +25,7 @@ __device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commi
 template <int N>
 __device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;\n" ::"n"(N) : "memory"); }
 
-template <int ELT, int WIN, int WOUT, int V, bool WIDE>
+template <int ELT, int WIN, int WOUT, int V, bool WIDE, bool AOF>
 __global__ void __launch_bounds__(512)
 permute_tiles_kernel(const __grid_constant__ TileDesc D, const unsigned char* __restrict__ in,
                      const __grid_constant__ PeerPtrs outs) {
@@ -49,13 +49,13 @@ permute_tiles_kernel(const __grid_constant__ TileDesc D, const unsigned char* __
   TileCtx cur = ctxs[0];
   TileCtx nxt = cur;
   if (D.stages >= 2) {
-    if (cur.valid) tile_load<ELT, WIN, WIDE>(D, cur, T, stage0, in, tid);
+    if (cur.valid) tile_load<ELT, WIN, WIDE, AOF>(D, cur, T, stage0, in, tid);
     cp_async_commit();
     uint32_t s = 0;
     for (uint32_t it = 0; tile < D.numTiles; tile += G, it++) {
       if (tile + G < D.numTiles) {
         nxt = ctxs[(it + 1) & 1];
-        if (nxt.valid) tile_load<ELT, WIN, WIDE>(D, nxt, T, stage0 + (s ^ 1u) * D.stageBytes, in, tid);
+        if (nxt.valid) tile_load<ELT, WIN, WIDE, AOF>(D, nxt, T, stage0 + (s ^ 1u) * D.stageBytes, in, tid);
       }
       cp_async_commit();
       cp_async_wait<1>();
@@ -65,7 +65,7 @@ permute_tiles_kernel(const __grid_constant__ TileDesc D, const unsigned char* __
       // reads the slot again before the barrier below, so thread 0 may overwrite it here.
       if (tid == 0 && tile + 2 * (uint64_t)G < D.numTiles) decode_tile(D, tile + 2 * G, ctxs[it & 1]);
       unsigned char* o = D.peerLoopDim >= 0 ? outs.p[cur.peer] : outs.p[0];
-      if (cur.valid) tile_store<ELT, WOUT, V, WIDE>(D, cur, T, stage0 + s * D.stageBytes, o, tid);
+      if (cur.valid) tile_store<ELT, WOUT, V, WIDE, AOF>(D, cur, T, stage0 + s * D.stageBytes, in, o, tid);
       __syncthreads();
       cur = nxt;
       s ^= 1u;
@@ -73,14 +73,14 @@ permute_tiles_kernel(const __grid_constant__ TileDesc D, const unsigned char* __
   } else {
     for (uint32_t it = 0; tile < D.numTiles; tile += G, it++) {
       if (it > 0) cur = ctxs[it & 1];
-      if (cur.valid) tile_load<ELT, WIN, WIDE>(D, cur, T, stage0, in, tid);
+      if (cur.valid) tile_load<ELT, WIN, WIDE, AOF>(D, cur, T, stage0, in, tid);
       cp_async_commit();
       cp_async_wait<0>();
       __syncthreads();
       // every thread has read slot it&1 (this tile) before the barrier above
       if (tid == 0 && tile + 2 * (uint64_t)G < D.numTiles) decode_tile(D, tile + 2 * G, ctxs[it & 1]);
       unsigned char* o = D.peerLoopDim >= 0 ? outs.p[cur.peer] : outs.p[0];
-      if (cur.valid) tile_store<ELT, WOUT, V, WIDE>(D, cur, T, stage0, o, tid);
+      if (cur.valid) tile_store<ELT, WOUT, V, WIDE, AOF>(D, cur, T, stage0, in, o, tid);
       __syncthreads();
     }
   }
@@ -90,10 +90,23 @@ typedef void (*TilesKernel)(const TileDesc, const unsigned char*, const PeerPtrs
 
 static TilesKernel pick_tiles_kernel(const TileDesc& D) {
   const int elt = D.elt, win = D.in.vec, wout = D.out.vec, v = D.vblk;
+  if (D.aof) {  // aligned over-fetch: 16-byte loads, no register blocking, 32-bit offsets
+    if (D.wide || v != 1) return nullptr;
+    if (elt == 4 && win == 4) {
+      if (wout == 1) return permute_tiles_kernel<4, 4, 1, 1, false, true>;
+      if (wout == 2) return permute_tiles_kernel<4, 4, 2, 1, false, true>;
+      if (wout == 4) return permute_tiles_kernel<4, 4, 4, 1, false, true>;
+    }
+    if (elt == 8 && win == 2) {
+      if (wout == 1) return permute_tiles_kernel<8, 2, 1, 1, false, true>;
+      if (wout == 2) return permute_tiles_kernel<8, 2, 2, 1, false, true>;
+    }
+    return nullptr;
+  }
 #define CASE(E, A, B, VV) \
   if (elt == E && win == A && wout == B && v == VV) { \
-    if (D.wide) return VV == 1 ? permute_tiles_kernel<E, A, B, 1, true> : nullptr; \
-    return permute_tiles_kernel<E, A, B, VV, false>; }
+    if (D.wide) return VV == 1 ? permute_tiles_kernel<E, A, B, 1, true, false> : nullptr; \
+    return permute_tiles_kernel<E, A, B, VV, false, false>; }
 #define CASES_V(E, A, B) CASE(E, A, B, 1) CASE(E, A, B, 2) CASE(E, A, B, 4)
   CASES_V(4, 1, 1) CASES_V(4, 1, 2) CASES_V(4, 1, 4) CASES_V(4, 2, 1) CASES_V(4, 2, 2) CASES_V(4, 2, 4)
   CASES_V(4, 4, 1) CASES_V(4, 4, 2) CASES_V(4, 4, 4)
@@ -141,7 +154,9 @@ int tiles_blocks_per_sm(const Candidate& c) {
 
 bool tiles_pointers_aligned(const Candidate& c, const void* in, const void* out) {
   const TileDesc& D = c.desc;
-  return ((uintptr_t)in % (D.in.vec * D.elt) == 0) && ((uintptr_t)out % (D.out.vec * D.elt) == 0);
+  // aligned over-fetch reads whatever alignment the input has
+  const bool inOk = D.aof ? ((uintptr_t)in % D.elt == 0) : ((uintptr_t)in % (D.in.vec * D.elt) == 0);
+  return inOk && ((uintptr_t)out % (D.out.vec * D.elt) == 0);
 }
 
 cudaError_t launch_tiles(const Candidate& c, int gridBlocks, const void* in, const PeerPtrs& outs,

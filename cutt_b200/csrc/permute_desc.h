@@ -18,6 +18,13 @@
 // for W consecutive positions of the output run) and writes V vectors of W elements to
 // global memory; the V x W transpose happens in registers.
 //
+// Aligned over-fetch (aof): when input rows do not start on 16-byte boundaries, each row is
+// still fetched with 16-byte cp.async from the enclosing aligned range (a few elements of the
+// neighbouring rows come along and are ignored; vectors that would leave the buffer are replaced
+// by element copies).  The row then sits in shared memory displaced by its misalignment
+// `shift = (address / elt) mod (16 / elt)`; the store side recomputes that shift from the tile
+// origin and from per-row / per-position residues carried in the low bits of the table offsets.
+//
 // At most two dimensions may have 1 < t_j < d_j with d_j not a multiple of t_j
 // ("partial" dimensions, slots 0 and 1); the last tile along such a dimension is
 // short, which is handled by comparing coordinates with the remaining extent.
@@ -112,7 +119,8 @@ struct RowDim {
   int32_t slot;      // partial slot (0/1) this dimension feeds, or -1
   uint32_t cmul;     // elements per position (V for the register-blocked dimension, else 1)
   Skew skew;
-  uint32_t pad_;
+  uint32_t ishift;   // aligned over-fetch mode: input stride of this dimension modulo the vector
+                     // width (elements) if the dimension selects input rows, else 0
 };
 
 // A dimension inside the output side's run: turns a position along the run into a
@@ -121,6 +129,8 @@ struct RunDim {
   FastDiv div;       // division by the tile extent
   uint32_t sstrideB; // shared-memory stride (bytes)
   Skew skew;
+  uint32_t ishift;   // as RowDim::ishift
+  uint32_t pad_[3];
 };
 
 struct Side {
@@ -176,7 +186,8 @@ struct TileDesc {
   uint32_t vblk;        // V: rows of the output side handled together along dimension 0 (1, 2 or 4)
   uint32_t wide;        // 1: 64-bit row offsets
   int32_t peerLoopDim;  // loop dimension whose coordinate selects the destination GPU, or -1
-  uint32_t pad_;
+  uint32_t aof;         // 1: aligned over-fetch loads (see below)
+  int64_t inElems;      // elements of the input buffer (bounds of the over-fetch)
   int64_t vstep;        // output offset between the V rows of a group (elements)
   int64_t inBase;       // element offset added to the input pointer
   int64_t outBase;      // element offset added to the output pointer
@@ -276,15 +287,18 @@ CUTT_HD void make_row(const Side& S, uint32_t r, int64_t& goff, uint32_t& soffB,
   soffB = 0;
   rc.c0 = 0;
   rc.c1 = 0;
+  uint32_t resid = 0;
   for (uint32_t k = 0; k < S.nRowDims; k++) {
     const RowDim& R = S.rowDim[k];
     uint32_t cc = r % R.ext;
     r /= R.ext;
     goff += (int64_t)cc * R.gstride;
     soffB += cc * R.sstrideB + skew_bytes(R.skew, cc);
+    resid += cc * R.ishift;
     if (R.slot == 0) rc.c0 = (uint16_t)(cc * R.cmul);
     if (R.slot == 1) rc.c1 = (uint16_t)(cc * R.cmul);
   }
+  soffB |= resid & 3u;  // zero unless the side uses aligned over-fetch residues
 }
 
 // Valid run length of a side in the tile described by `c`.
@@ -298,16 +312,18 @@ CUTT_HD uint32_t run_valid(const Side& S, const TileCtx& c) {
 
 // Shared-memory byte offset of position q along the output side's run.
 CUTT_HD uint32_t out_run_soff(const TileDesc& D, uint32_t q) {
-  uint32_t s = 0;
+  uint32_t s = 0, resid = 0;
   for (uint32_t k = 0; k + 1 < D.nOutRunDims; k++) {
     const RunDim& R = D.outRunDim[k];
     uint32_t nq = fdiv(q, R.div);
     uint32_t cc = q - nq * R.div.d;
     s += cc * R.sstrideB + skew_bytes(R.skew, cc);
+    resid += cc * R.ishift;
     q = nq;
   }
   const RunDim& R = D.outRunDim[D.nOutRunDims - 1];  // the last run dimension needs no modulo
-  return s + q * R.sstrideB + skew_bytes(R.skew, q);
+  resid += q * R.ishift;
+  return (s + q * R.sstrideB + skew_bytes(R.skew, q)) | (resid & 3u);
 }
 
 // Fills the shared-memory tables; thread `tid` of `nthreads` does its share.

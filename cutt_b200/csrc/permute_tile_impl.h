@@ -176,6 +176,127 @@ CUTT_HD void tile_load_impl(const TileDesc& D, const TileCtx& c, const Tables<WI
   }
 }
 
+// Aligned over-fetch load of one input row (see permute_desc.h): 16-byte copies from the
+// aligned range that encloses the row; at the ends of the buffer element copies of the row's
+// own elements only.
+template <int ELT>
+CUTT_HD void aof_row(sptr_t srow, const unsigned char* grow, uint32_t valid, uint32_t tq, uint32_t Tq,
+                     const unsigned char* lo, const unsigned char* hi) {
+  constexpr uint32_t VE = 16 / ELT;
+  const uint32_t sh = (uint32_t)(((uintptr_t)grow / ELT) & (VE - 1));
+  const unsigned char* gal = grow - sh * ELT;
+  const uint32_t nvec = (sh + valid + VE - 1) / VE;
+  for (uint32_t v = tq; v < nvec; v += Tq) {
+    const unsigned char* src = gal + 16u * v;
+    if (src >= lo && src + 16 <= hi) {
+      copy_g2s<16>(srow + 16u * v, src);
+    } else {
+      for (uint32_t e = 0; e < VE; e++) {
+        const uint32_t pos = v * VE + e;  // position relative to the aligned start
+        if (pos >= sh && pos < sh + valid) copy_g2s<ELT>(srow + pos * ELT, gal + (size_t)pos * ELT);
+      }
+    }
+  }
+}
+
+template <int ELT, bool WIDE, bool PARTIAL>
+CUTT_HD void tile_load_aof(const TileDesc& D, const TileCtx& c, const Tables<WIDE>& T,
+                           sptr_t sbuf, const unsigned char* gin, uint32_t tid) {
+  typedef typename RowEntSel<WIDE>::type Ent;
+  const Side& S = D.in;
+  const uint32_t tq = tid & (S.tq - 1);
+  const uint32_t tr = tid >> S.tqShift;
+  const uint32_t Tr = D.nthreads >> S.tqShift;
+  const uint32_t valid = PARTIAL ? run_valid(S, c) : S.run;
+  const unsigned char* lo = gin;
+  const unsigned char* hi = gin + D.inElems * ELT;
+  const unsigned char* gbase = gin + c.inOff * ELT;
+  if (S.nRowDims <= 1) {
+    const RowDim& R = S.rowDim[0];
+    const uint32_t nr = PARTIAL ? single_dim_rows(S, c) : S.nrows;
+    const int64_t gstepB = S.nRowDims ? R.gstride * (int64_t)(Tr * ELT) : 0;
+    const unsigned char* g0 = gbase + (S.nRowDims ? R.gstride * (int64_t)(tr * ELT) : 0);
+    const bool skewed = S.nRowDims && R.skew.mask != 0;
+    for (uint32_t row = tr; row < nr; row += Tr) {
+      sptr_t s = sbuf + row * R.sstrideB;
+      if (skewed) s += skew_bytes(R.skew, row);
+      aof_row<ELT>(s, g0, valid, tq, S.tq, lo, hi);
+      g0 += gstepB;
+    }
+    return;
+  }
+  for (uint32_t row = tr; row < S.nrows; row += Tr) {
+    if (PARTIAL) {
+      const RowCoord rc = T.coIn[row];
+      if (!(rc.c0 < c.rem0 && rc.c1 < c.rem1)) continue;
+    }
+    const Ent e = T.tabIn[row];
+    const unsigned char* g = gbase + (WIDE ? (int64_t)e.goff * ELT : (int64_t)((uint64_t)(uint32_t)e.goff * ELT));
+    aof_row<ELT>(sbuf + e.soffB, g, valid, tq, S.tq, lo, hi);
+  }
+}
+
+// Store side of the aligned over-fetch mode: scalar shared loads at
+// base + row offset + position offset + ((A + row residue + position residue) mod VE) * ELT,
+// where A is the misalignment of the tile origin and the residues travel in the low two bits
+// of the offsets.
+template <int ELT, int W, bool WIDE, bool PARTIAL>
+CUTT_HD void tile_store_aof(const TileDesc& D, const TileCtx& c, const Tables<WIDE>& T,
+                            sptr_t sbuf, const unsigned char* gin, unsigned char* gout, uint32_t tid) {
+  typedef typename RowEntSel<WIDE>::type Ent;
+  constexpr int EW = ELT / 4;
+  constexpr uint32_t VE = 16 / ELT;
+  const Side& S = D.out;
+  const uint32_t tq = tid & (S.tq - 1);
+  const uint32_t tr = tid >> S.tqShift;
+  const uint32_t Tr = D.nthreads >> S.tqShift;
+  const uint32_t valid = PARTIAL ? run_valid(S, c) : S.run;
+  const uint32_t qstep = S.tq * W;
+  const uint32_t A = (uint32_t)((((uintptr_t)gin / ELT) + (uint64_t)c.inOff) & (VE - 1));
+  unsigned char* gbase = gout + c.outOff * ELT;
+  const bool single = S.nRowDims <= 1;
+  const RowDim& R = S.rowDim[0];
+  const uint32_t nr = single ? (PARTIAL ? single_dim_rows(S, c) : S.nrows) : S.nrows;
+  const int64_t gstepB = (single && S.nRowDims) ? R.gstride * (int64_t)(Tr * ELT) : 0;
+  const int64_t g0off = (single && S.nRowDims) ? R.gstride * (int64_t)(tr * ELT) : 0;
+  const bool skewed = single && S.nRowDims && R.skew.mask != 0;
+  for (uint32_t q = tq * W; q < valid; q += qstep) {
+    uint32_t so[W], qr[W];
+#pragma unroll
+    for (int i = 0; i < W; i++) {
+      const uint32_t v = T.qtab[q + i];
+      so[i] = v & ~3u;
+      qr[i] = A + (v & 3u);
+    }
+    unsigned char* gq = gbase + (size_t)q * ELT;
+    unsigned char* g = gq + g0off;
+#pragma unroll 2
+    for (uint32_t row = tr; row < nr; row += Tr) {
+      uint32_t soff, rres;
+      if (single) {
+        soff = row * R.sstrideB;
+        if (skewed) soff += skew_bytes(R.skew, row);
+        rres = row * R.ishift;
+      } else {
+        if (PARTIAL) {
+          const RowCoord rc = T.coOut[row];
+          if (!(rc.c0 < c.rem0 && rc.c1 < c.rem1)) continue;
+        }
+        const Ent e = T.tabOut[row];
+        soff = e.soffB & ~3u;
+        rres = e.soffB & 3u;
+        g = gq + (WIDE ? (int64_t)e.goff * ELT : (int64_t)((uint64_t)(uint32_t)e.goff * ELT));
+      }
+      uint32_t y[W * EW];
+#pragma unroll
+      for (int i = 0; i < W; i++)
+        lds<ELT>(&y[i * EW], sbuf + soff + so[i] + ((qr[i] + rres) & (VE - 1)) * ELT);
+      stg<ELT * W>(g, y);
+      if (single) g += gstepB;
+    }
+  }
+}
+
 // One (row group, run position) item of the store side: W shared-memory vectors of V
 // elements in, V global vectors of W elements out.
 template <int ELT, int W, int V>
@@ -251,18 +372,28 @@ CUTT_HD void tile_store_impl(const TileDesc& D, const TileCtx& c, const Tables<W
   }
 }
 
-template <int ELT, int W, bool WIDE>
+template <int ELT, int W, bool WIDE, bool AOF>
 CUTT_HD void tile_load(const TileDesc& D, const TileCtx& c, const Tables<WIDE>& T,
                        sptr_t sbuf, const unsigned char* gin, uint32_t tid) {
-  if (c.partial) tile_load_impl<ELT, W, WIDE, true>(D, c, T, sbuf, gin, tid);
-  else tile_load_impl<ELT, W, WIDE, false>(D, c, T, sbuf, gin, tid);
+  if (AOF) {
+    if (c.partial) tile_load_aof<ELT, WIDE, true>(D, c, T, sbuf, gin, tid);
+    else tile_load_aof<ELT, WIDE, false>(D, c, T, sbuf, gin, tid);
+  } else {
+    if (c.partial) tile_load_impl<ELT, W, WIDE, true>(D, c, T, sbuf, gin, tid);
+    else tile_load_impl<ELT, W, WIDE, false>(D, c, T, sbuf, gin, tid);
+  }
 }
 
-template <int ELT, int W, int V, bool WIDE>
+template <int ELT, int W, int V, bool WIDE, bool AOF>
 CUTT_HD void tile_store(const TileDesc& D, const TileCtx& c, const Tables<WIDE>& T,
-                        sptr_t sbuf, unsigned char* gout, uint32_t tid) {
-  if (c.partial) tile_store_impl<ELT, W, V, WIDE, true>(D, c, T, sbuf, gout, tid);
-  else tile_store_impl<ELT, W, V, WIDE, false>(D, c, T, sbuf, gout, tid);
+                        sptr_t sbuf, const unsigned char* gin, unsigned char* gout, uint32_t tid) {
+  if (AOF) {
+    if (c.partial) tile_store_aof<ELT, W, WIDE, true>(D, c, T, sbuf, gin, gout, tid);
+    else tile_store_aof<ELT, W, WIDE, false>(D, c, T, sbuf, gin, gout, tid);
+  } else {
+    if (c.partial) tile_store_impl<ELT, W, V, WIDE, true>(D, c, T, sbuf, gout, tid);
+    else tile_store_impl<ELT, W, V, WIDE, false>(D, c, T, sbuf, gout, tid);
+  }
 }
 
 }  // namespace cuttb

@@ -1,5 +1,6 @@
 // Plan builder (host only).  See planner.h.
 #include "planner.h"
+#include "cost_model_data.h"
 #include <algorithm>
 #include <cmath>
 #include <cstdio>
@@ -40,6 +41,7 @@ bool canonicalize(int rank, const int64_t* d, const int64_t* is, const int64_t* 
   P.rank = (int)f.size();
   P.elt = elt;
   P.volume = vol;
+  P.inElems = vol;
   P.peerDim = -1;
   for (int i = 0; i < P.rank; i++) {
     P.d[i] = f[i].d;
@@ -287,7 +289,7 @@ bool build_tile(const Problem& P, const TileParams& tp, const DeviceInfo& dev, C
     }
     return 1;
   };
-  const uint32_t win = side_vec(true);
+  uint32_t win = side_vec(true);
   const uint32_t wout = side_vec(false);
 
   // 64-bit row offsets are needed when a tile spans 2^32 elements or more on either side
@@ -305,6 +307,16 @@ bool build_tile(const Problem& P, const TileParams& tp, const DeviceInfo& dev, C
       if (t[0] % v == 0 && P.d[0] % v == 0) { V = (uint32_t)v; break; }
     }
   }
+  // aligned over-fetch: misaligned input rows are still fetched with 16-byte copies
+  const uint32_t VE = 16u / elt;
+  bool aof = false;
+  if (tp.allowAof && !wide && win < VE && inRunLast >= 0 && P.is[0] == 1 && tp.maxVecBytes >= 16) {
+    int64_t run = 1;
+    for (int j = 0; j < r; j++) if (inRun[j]) run *= t[j];
+    if (run >= 2 * (int64_t)VE) { aof = true; win = VE; V = 1; }
+  }
+  D.aof = aof ? 1 : 0;
+  D.inElems = P.inElems;
   D.vblk = V;
   D.vstep = P.os[0];
 
@@ -317,9 +329,11 @@ bool build_tile(const Problem& P, const TileParams& tp, const DeviceInfo& dev, C
   {
     int p0 = nOutRun > 0 ? outRunOrder[0] : -1;
     int64_t s = 1;
+    bool slackDone = false;
     for (int j = 0; j < r; j++) {
       if (t[j] == 1) { ss[j] = 0; continue; }
       if (!inRun[j]) {
+        if (aof && !slackDone) { s += VE - 1; slackDone = true; }  // room for the row's displacement
         if (j == p0) {
           // lanes per shared-memory wavefront for one output-side access
           uint32_t G = 128u / (V * elt);
@@ -338,7 +352,7 @@ bool build_tile(const Problem& P, const TileParams& tp, const DeviceInfo& dev, C
       ss[j] = s;
       s = s * t[j];
     }
-    int64_t elems = 1;
+    int64_t elems = 1 + (aof ? 2 * (int64_t)VE : 0);
     for (int j = 0; j < r; j++)
       if (t[j] > 1) elems += (t[j] - 1) * ss[j] + (skewOf[j].mask ? (int64_t)skewOf[j].mask * A : 0);
     if (elems > (int64_t)dev.maxSmemPerBlock / elt) return false;
@@ -369,6 +383,7 @@ bool build_tile(const Problem& P, const TileParams& tp, const DeviceInfo& dev, C
       R.slot = slotOf[j];
       R.cmul = (uint32_t)blk;
       R.skew = skewOf[j];
+      R.ishift = (aof && !input && !inRun[j]) ? (uint32_t)(P.is[j] % VE) : 0;
       nrows *= R.ext;
     }
     if (nrows > 8192) return false;
@@ -388,16 +403,18 @@ bool build_tile(const Problem& P, const TileParams& tp, const DeviceInfo& dev, C
     R.div = make_fastdiv((uint32_t)t[j]);
     R.sstrideB = (uint32_t)(ss[j] * elt);
     R.skew = skewOf[j];
+    R.ishift = (aof && !inRun[j]) ? (uint32_t)(P.is[j] % VE) : 0;
   }
   if (D.nOutRunDims == 0) {
     D.outRunDim[0].div = make_fastdiv(1);
     D.outRunDim[0].sstrideB = 0;
     D.outRunDim[0].skew = skewOf[0];
     D.outRunDim[0].skew.mask = 0;
+    D.outRunDim[0].ishift = 0;
     D.nOutRunDims = 1;
   }
   D.smemGatherContig = 0;
-  if (wout > 1 && nOutRun > 0 && V == 1) {
+  if (wout > 1 && nOutRun > 0 && V == 1 && !aof) {
     int j0 = outRunOrder[0];
     bool ok = ss[j0] == 1 && t[j0] % wout == 0 && skewOf[j0].mask == 0;
     for (int j = 0; j < r && ok; j++)
@@ -476,8 +493,8 @@ bool build_tile(const Problem& P, const TileParams& tp, const DeviceInfo& dev, C
   char buf[512];
   std::string ts;
   for (int j = 0; j < r; j++) { snprintf(buf, sizeof buf, "%s%lld", j ? "," : "", (long long)t[j]); ts += buf; }
-  snprintf(buf, sizeof buf, "tiles t=[%s] in=%ux%u/w%u out=%ux%u/w%u V%u%s smem=%d st=%d lo=%d nt=%d",
-           ts.c_str(), D.in.nrows, D.in.run, D.in.vec, D.out.nrows, D.out.run, D.out.vec, D.vblk,
+  snprintf(buf, sizeof buf, "tiles t=[%s] in=%ux%u/w%u%s out=%ux%u/w%u V%u%s smem=%d st=%d lo=%d nt=%d",
+           ts.c_str(), D.in.nrows, D.in.run, D.in.vec, D.aof ? "a" : "", D.out.nrows, D.out.run, D.out.vec, D.vblk,
            D.wide ? " wide" : "", out.smemBytes, D.stages, tp.loopOrder, tp.nthreads);
   if (D.split[0].used || D.split[1].used) {
     snprintf(buf + strlen(buf), sizeof buf - strlen(buf), " g=%d/%d", D.split[0].used ? tp.groupIn : 1,
@@ -534,13 +551,15 @@ bool build_tile(const Problem& P, const TileParams& tp, const DeviceInfo& dev, C
     f[28] = lg(inRowStride);
     f[29] = lg(outRowStride);
     f[30] = (float)D.wide;
-    f[31] = (float)P.rank;
+    f[31] = (float)D.aof;
   }
   out.cost = model_cost(P, out, dev);
   return true;
 }
 
-double model_cost(const Problem& P, const Candidate& c, const DeviceInfo& dev) {
+// Closed-form estimate (no measurements behind it); kept as a cross-check and for devices the
+// fitted model was not trained on.
+double analytic_cost(const Problem& P, const Candidate& c, const DeviceInfo& dev) {
   const TileDesc& D = c.desc;
   const double bytes = 2.0 * (double)P.volume * P.elt;
   const double rin = (double)D.in.run * P.elt, rout = (double)D.out.run * P.elt;
@@ -561,6 +580,31 @@ double model_cost(const Problem& P, const Candidate& c, const DeviceInfo& dev) {
   fwave = 0.5 + 0.5 * fwave;
   double eff = fin * fout * finstr * ftile * (0.5 + 0.5 * focc) * fwave;
   return bytes / (dev.hbmGBs * 1e9 * eff) + 4e-6;
+}
+
+// Fitted model: gradient-boosted regression trees over the candidate's feature vector, trained
+// on B200 timings of every candidate of the benchmark shapes (cutt_b200/cost_model/).  Predicts
+// the fraction of the copy bandwidth the candidate reaches.
+static double predicted_efficiency(const float* f) {
+  using namespace cost_model;
+  double s = kInit;
+  for (int t = 0; t < kTrees; t++) {
+    int n = kRoot[t];
+    while (kFeat[n] >= 0) n = f[kFeat[n]] <= kThr[n] ? kLeft[n] : kRight[n];
+    s += kVal[n];
+  }
+  return s;
+}
+
+double model_cost(const Problem& P, const Candidate& c, const DeviceInfo& dev) {
+  static_assert(cost_model::kFeatures == kNumFeatures, "regenerate cost_model_data.h");
+  const double bytes = 2.0 * (double)P.volume * P.elt;
+  // tensors far smaller than the training shapes are launch/latency bound: the fitted model
+  // has not seen them, use the closed form there
+  if (bytes < 64e6) return analytic_cost(P, c, dev);
+  double eff = predicted_efficiency(c.feat);
+  if (eff < 0.02) eff = 0.02;
+  return bytes / (cost_model::kRefGBs * 1e9 * eff) + 4e-6;
 }
 
 std::vector<Candidate> enumerate_candidates(const Problem& P, const DeviceInfo& dev) {

@@ -30,6 +30,7 @@ struct Problem {
   int64_t inBase = 0, outBase = 0;
   int peerDim = -1;   // canonical dimension whose coordinate selects the destination GPU
   int64_t volume = 0;
+  int64_t inElems = 0;  // elements of the input buffer this problem reads from
   bool identity = false;  // one contiguous run on both sides: a plain copy
 };
 
@@ -73,6 +74,7 @@ struct TileParams {
   int stages = 2;
   int maxVecBytes = 16;        // widest global access
   int maxVBytes = 16;          // widest shared-memory vector of the register-blocked store side
+  int allowAof = 1;            // aligned over-fetch loads when input rows are not 16-byte aligned
   int loopOrder = 0;           // tile index runs fastest along 0: input order, 1: output order
   int groupIn = 1;             // neighbouring tiles along the input run's chunked dimension taken first
   int groupOut = 1;            // then this many along the output run's chunked dimension
@@ -99,7 +101,8 @@ bool build_tile(const Problem& P, const TileParams& tp, const DeviceInfo& dev, C
 // All distinct candidates for a problem, cheapest model cost first.
 std::vector<Candidate> enumerate_candidates(const Problem& P, const DeviceInfo& dev);
 
-// Model estimate (seconds) for a tiles candidate.
+// Model estimate (seconds) for a tiles candidate (fitted model; closed form for small tensors).
+double analytic_cost(const Problem& P, const Candidate& c, const DeviceInfo& dev);
 double model_cost(const Problem& P, const Candidate& c, const DeviceInfo& dev);
 
 // One-line JSON description (used by tests and by CUTT_VERBOSE).
