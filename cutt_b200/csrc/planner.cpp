@@ -632,18 +632,22 @@ std::vector<Candidate> enumerate_candidates(const Problem& P, const DeviceInfo& 
         for (int ext = 0; ext < 2; ext++)
           for (int lo = 0; lo < 2; lo++)
             for (const auto& g : groups)
-              for (int nt = 256; nt <= 512; nt *= 2) {
-                TileParams tp;
-                tp.tinBytes = tinB; tp.toutBytes = toutB; tp.vtargetBytes = vB;
-                tp.extend = ext; tp.loopOrder = lo;
-                tp.groupIn = g[0]; tp.groupOut = g[1];
-                tp.nthreads = nt;
-                Candidate c;
-                if (!build_tile(P, tp, dev, c)) continue;
-                if (nt == 512 && c.smemBytes < 40 * 1024) continue;  // small tiles: more blocks instead
-                if (!seen.insert(c.label).second) continue;
-                res.push_back(c);
-              }
+              for (int nt = 256; nt <= 512; nt *= 2)
+                for (int aof = 1; aof >= 0; aof--) {
+                  TileParams tp;
+                  tp.tinBytes = tinB; tp.toutBytes = toutB; tp.vtargetBytes = vB;
+                  tp.extend = ext; tp.loopOrder = lo;
+                  tp.groupIn = g[0]; tp.groupOut = g[1];
+                  tp.nthreads = nt;
+                  tp.allowAof = aof;
+                  Candidate c;
+                  if (!build_tile(P, tp, dev, c)) continue;
+                  if (nt == 512 && c.smemBytes < 40 * 1024) continue;  // small tiles: more blocks instead
+                  // 4-byte element-wise loads never beat the aligned over-fetch of the same tile
+                  if (!aof && P.elt == 4 && c.desc.in.vec == 1 && c.desc.in.run >= 8) continue;
+                  if (!seen.insert(c.label).second) continue;
+                  res.push_back(c);
+                }
   std::stable_sort(res.begin(), res.end(), [](const Candidate& a, const Candidate& b) { return a.cost < b.cost; });
   return res;
 }

@@ -16,7 +16,7 @@ def _build(native, tmpdir):
     exe = os.path.join(str(tmpdir), "dropin_example")
     libdir = os.path.dirname(native.lib_path())
     cmd = ["g++", "-std=c++11", "-O1", SRC, "-I", os.path.join(ROOT, "include"), "-I", os.path.join(CUDA, "include"),
-           "-L", libdir, "-lcutt", "-L", os.path.join(CUDA, "lib64"), "-lcudart", "-lstdc++", "-lpthread", "-ldl",
+           "-L", libdir, "-l:libcutt.a", "-L", os.path.join(CUDA, "lib64"), "-lcudart", "-lstdc++", "-lpthread", "-ldl",
            "-o", exe]
     res = subprocess.run(cmd, stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True)
     assert res.returncode == 0, res.stdout
