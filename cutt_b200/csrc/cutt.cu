@@ -237,6 +237,18 @@ bool adopt_candidate(Plan& p, const DeviceInfo& dev, const Candidate& c) {
   return true;
 }
 
+// The candidate list of the last problem enumerated (sweeps ask for candidate 0, 1, 2, ... of the
+// same problem in a row).
+std::string g_enumKey;
+std::vector<Candidate> g_enumList;
+const std::vector<Candidate>& enumerate_cached(const std::string& key, const Problem& P, const DeviceInfo& dev) {
+  if (key != g_enumKey || g_enumList.empty()) {
+    g_enumList = enumerate_candidates(P, dev);
+    g_enumKey = key;
+  }
+  return g_enumList;
+}
+
 enum PlanMode { kByModel, kByMeasure, kByIndex, kByParams };
 
 struct PlanRequest {
@@ -320,7 +332,8 @@ cuttResult make_plan(cuttHandle* handle, int rank, const int* dim, const int* pe
       ok = adopt_candidate(*p, dev, c);
     }
   } else {
-    std::vector<Candidate> cands = enumerate_candidates(p->prob, dev);
+    // (a copy: the cached list may be replaced by another thread while this one measures)
+    const std::vector<Candidate> cands = enumerate_cached(key, p->prob, dev);
     if (cands.empty()) {
       if (p->mgMode == 1) return CUTT_INTERNAL_ERROR;  // no local fallback can write peer slabs
       p->method = kMethodNaive;
@@ -500,7 +513,7 @@ int cutt_c_num_candidates(int rank, const int* dim, const int* permutation, size
   if (!device_info(devId, dev)) return 0;
   Problem P;
   if (!problem_from_cutt(rank, dim, permutation, (int)sizeofType, P)) return 0;
-  return (int)enumerate_candidates(P, dev).size();
+  return (int)enumerate_cached(problem_key(devId, rank, dim, permutation, sizeofType), P, dev).size();
 }
 
 int cutt_c_plan_candidate(unsigned int* handle, int rank, const int* dim, const int* permutation,
@@ -734,12 +747,12 @@ int cutt_c_plan_cache_save(const char* path) {
   std::lock_guard<std::mutex> lk(g_mutex);
   FILE* f = fopen(path, "w");
   if (!f) return CUTT_INTERNAL_ERROR;
-  fprintf(f, "# cutt-b200 plan cache v1\n");
+  fprintf(f, "# cutt-b200 plan cache v2\n");
   plan_cache().for_each_oldest_first([&](const std::string& k, const CachedChoice& c) {
     const TileParams& t = c.params;
-    fprintf(f, "%s %d %u %u %u %d %d %d %d %d %d %d %d\n", k.c_str(), (int)c.method, t.tinBytes, t.toutBytes,
+    fprintf(f, "%s %d %u %u %u %d %d %d %d %d %d %d %d %d %d\n", k.c_str(), (int)c.method, t.tinBytes, t.toutBytes,
             t.vtargetBytes, t.extend, t.nthreads, t.stages, t.maxVecBytes, t.maxVBytes, t.loopOrder,
-            t.groupIn, t.groupOut);
+            t.groupIn, t.groupOut, t.cutInRun, t.allowAof);
   });
   fclose(f);
   return CUTT_SUCCESS;
@@ -758,9 +771,9 @@ int cutt_c_plan_cache_load(const char* path) {
     int method;
     CachedChoice c;
     TileParams& t = c.params;
-    if (sscanf(line, "%511s %d %u %u %u %d %d %d %d %d %d %d %d", key, &method, &t.tinBytes, &t.toutBytes,
+    if (sscanf(line, "%511s %d %u %u %u %d %d %d %d %d %d %d %d %d %d", key, &method, &t.tinBytes, &t.toutBytes,
                &t.vtargetBytes, &t.extend, &t.nthreads, &t.stages, &t.maxVecBytes, &t.maxVBytes,
-               &t.loopOrder, &t.groupIn, &t.groupOut) != 13)
+               &t.loopOrder, &t.groupIn, &t.groupOut, &t.cutInRun, &t.allowAof) != 15)
       continue;
     if (method < 0 || method > (int)kMethodNaive) continue;
     c.method = (Method)method;

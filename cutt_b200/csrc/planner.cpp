@@ -135,7 +135,8 @@ static void choose_thread_split(Side& S, uint32_t nthreads) {
   S.tqShift = ilog2_exact(bestTq);
 }
 
-bool build_tile(const Problem& P, const TileParams& tp, const DeviceInfo& dev, Candidate& out) {
+bool build_tile(const Problem& P, const TileParams& tp, const DeviceInfo& dev, Candidate& out,
+                std::set<std::string>* seenExtents) {
   const int r = P.rank;
   const int elt = P.elt;
   if (r < 1 || r > kMaxDims) return false;
@@ -213,6 +214,16 @@ bool build_tile(const Problem& P, const TileParams& tp, const DeviceInfo& dev, C
     if (nt < P.d[pick]) break;  // chunked: the target is met (or the chunk limit was hit)
   }
   if (num_chunked() > 2) return false;
+  if (seenExtents) {
+    // everything below depends only on the extents and these options
+    std::string key;
+    char kb[64];
+    for (int j = 0; j < r; j++) { snprintf(kb, sizeof kb, "%lld,", (long long)t[j]); key += kb; }
+    snprintf(kb, sizeof kb, "|%d%d%d%d%d%d%d%d", tp.nthreads, tp.stages, tp.maxVecBytes, tp.maxVBytes, tp.loopOrder,
+             tp.cutInRun, tp.allowAof, tp.groupIn * 16 + tp.groupOut);
+    key += kb;
+    if (!seenExtents->insert(key).second) return false;
+  }
 
   // 4. derive descriptor
   TileDesc& D = out.desc;
@@ -242,6 +253,7 @@ bool build_tile(const Problem& P, const TileParams& tp, const DeviceInfo& dev, C
     int64_t expect = 1;
     for (int j = 0; j < r; j++) {
       if (P.is[j] != expect || t[j] == 1 || j == P.peerDim) break;
+      if (tp.cutInRun && j > 0 && j == oo[0]) break;
       inRun[j] = true; inRunLast = j;
       if (t[j] < P.d[j]) break;
       expect *= P.d[j];
@@ -622,9 +634,16 @@ std::vector<Candidate> enumerate_candidates(const Problem& P, const DeviceInfo& 
     res.push_back(m);
     return res;
   }
-  std::set<std::string> seen;
+  std::set<std::string> seen, seenExt;
+  // first dimension of the output order (the peer dimension has no output stride)
+  int oo0 = -1;
+  for (int j = 0; j < P.rank; j++)
+    if (j != P.peerDim && (oo0 < 0 || P.os[j] < P.os[oo0])) oo0 = j;
   const uint32_t runs[] = {128, 256, 512, 1024, 2048};
-  const uint32_t vols[] = {8192, 16384, 32768, 65536};
+  // small tensors need small tiles to give every SM something to do
+  const bool small = (double)P.volume * P.elt < 64e6;
+  std::vector<uint32_t> vols = {8192, 16384, 32768, 65536};
+  if (small) { vols.insert(vols.begin(), 4096); vols.insert(vols.begin(), 2048); }
   const int groups[][2] = {{1, 1}, {2, 1}, {4, 1}, {1, 4}, {2, 4}};
   for (uint32_t tinB : runs)
     for (uint32_t toutB : runs)
@@ -641,7 +660,16 @@ std::vector<Candidate> enumerate_candidates(const Problem& P, const DeviceInfo& 
                   tp.nthreads = nt;
                   tp.allowAof = aof;
                   Candidate c;
-                  if (!build_tile(P, tp, dev, c)) continue;
+                  if (!build_tile(P, tp, dev, c, &seenExt)) continue;
+                  // same tile with the input run cut in front of the output's first dimension
+                  if (P.rank > 1 && oo0 > 0 && c.desc.in.nrows * (uint64_t)c.desc.in.run > 0) {
+                    TileParams tc = tp;
+                    tc.cutInRun = 1;
+                    Candidate cc;
+                    if (build_tile(P, tc, dev, cc, &seenExt) && cc.label != c.label &&
+                        !(nt == 512 && cc.smemBytes < 40 * 1024) && seen.insert(cc.label).second)
+                      res.push_back(cc);
+                  }
                   if (nt == 512 && c.smemBytes < 40 * 1024) continue;  // small tiles: more blocks instead
                   // 4-byte element-wise loads never beat the aligned over-fetch of the same tile
                   if (!aof && P.elt == 4 && c.desc.in.vec == 1 && c.desc.in.run >= 8) continue;

@@ -6,6 +6,7 @@
 // (src/cuttGpuModel.cpp) of the reference.
 #pragma once
 #include <stdint.h>
+#include <set>
 #include <string>
 #include <vector>
 #include "permute_desc.h"
@@ -74,6 +75,8 @@ struct TileParams {
   int stages = 2;
   int maxVecBytes = 16;        // widest global access
   int maxVBytes = 16;          // widest shared-memory vector of the register-blocked store side
+  int cutInRun = 0;            // end the input run before the dimension that starts the output run, so that
+                               // dimension gets a padded (bank-conflict-free) shared-memory stride
   int allowAof = 1;            // aligned over-fetch loads when input rows are not 16-byte aligned
   int loopOrder = 0;           // tile index runs fastest along 0: input order, 1: output order
   int groupIn = 1;             // neighbouring tiles along the input run's chunked dimension taken first
@@ -95,8 +98,10 @@ struct Candidate {
 };
 
 // Builds the descriptor for one parameter choice; false if it is illegal
-// (too much shared memory, more than two partial dimensions, ...).
-bool build_tile(const Problem& P, const TileParams& tp, const DeviceInfo& dev, Candidate& out);
+// (too much shared memory, more than two partial dimensions, ...).  With `seenExtents`, also
+// false when the same tile extents and launch options were already built (enumeration dedup).
+bool build_tile(const Problem& P, const TileParams& tp, const DeviceInfo& dev, Candidate& out,
+                std::set<std::string>* seenExtents = nullptr);
 
 // All distinct candidates for a problem, cheapest model cost first.
 std::vector<Candidate> enumerate_candidates(const Problem& P, const DeviceInfo& dev);
