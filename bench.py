@@ -360,6 +360,8 @@ def run_ours(args):
                                   "min_gbs": min(r["gbs"] for r in res), "max_gbs": max(r["gbs"] for r in res)}
         except Exception as e:  # extras never fail the headline
             extras["c3_suite"] = {"error": repr(e)}
+    if rank == 0 and not args.no_extras and world == 1:
+        extras["reference_cutt_gpu"] = reference_gpu_baseline(cases)
     if extras:
         line["extras"] = extras
     for p in plans:
@@ -480,6 +482,37 @@ def run_suite(C, cases, stream, reps=5):
             out.append({"case": ci, "dims": dims, "perm": perm, "elt": elt, "ms": ms,
                         "gbs": 2 * vol * elt / (ms * 1e-3) / 1e9, "plan": label})
     return out
+
+
+def reference_gpu_baseline(cases):
+    """The original cuTT on this GPU (PTX-JIT build, see oracle/build_ref.py), same shapes,
+    both planning modes; runs in a child process because the original exits on CUDA errors."""
+    try:
+        from oracle import ref_runner
+        if not ref_runner.available():
+            return {"unavailable": "oracle/_ref/libcutt_ref.so not built (original sources not on this machine)"}
+        import tempfile
+        spec = [{"dims": list(d), "perm": list(p), "elt": e} for _, d, p, e in cases]
+        out = {}
+        with tempfile.NamedTemporaryFile("w", suffix=".json", delete=False) as f:
+            json.dump(spec, f)
+            path = f.name
+        for mode, flag in (("cuttPlan", []), ("cuttPlanMeasure", ["--measure"])):
+            res = subprocess.run([sys.executable, "-m", "oracle.ref_runner", path, "--reps", "5", "--no-hash"] + flag,
+                                 cwd=ROOT, stdout=subprocess.PIPE, stderr=subprocess.PIPE, text=True, timeout=600)
+            recs = [json.loads(ln) for ln in res.stdout.splitlines() if ln.startswith("{")]
+            if res.returncode != 0 or len(recs) != len(spec):
+                out[mode] = {"error": (res.stderr or "no output")[-300:]}
+                continue
+            tot_bytes = sum(2 * _vol(r["dims"]) * r["elt"] for r in recs)
+            tot_ms = sum(r["ms"] for r in recs)
+            out[mode] = {"gbs": tot_bytes / (tot_ms * 1e-3) / 1e9,
+                         "per_case_gbs": [round(r["gbs"], 1) for r in recs]}
+        os.remove(path)
+        out["build"] = "unmodified sources, nvcc -gencode arch=compute_60,code=compute_60 (PTX only), driver JIT"
+        return out
+    except Exception as e:
+        return {"error": repr(e)}
 
 
 def cpu_baseline(cases):
