@@ -357,11 +357,28 @@ def run_ours(args):
             med = statistics.median(r["gbs"] for r in res)
             extras["c3_suite"] = {"cases": len(res), "median_gbs": med, "frac_of_peak": med / peak,
                                   "frac_of_8000": med / 8000.0,
-                                  "min_gbs": min(r["gbs"] for r in res), "max_gbs": max(r["gbs"] for r in res)}
+                                  "min_gbs": min(r["gbs"] for r in res), "max_gbs": max(r["gbs"] for r in res),
+                                  "_per_case": [r["gbs"] for r in res]}
         except Exception as e:  # extras never fail the headline
             extras["c3_suite"] = {"error": repr(e)}
     if rank == 0 and not args.no_extras and world == 1:
         extras["reference_cutt_gpu"] = reference_gpu_baseline(cases)
+        if "c3_suite" in extras and "error" not in extras["c3_suite"]:
+            suite_cases = [("c3", d, p, e) for d, p in W.c3_cases(args.suite_cases) for e in (8, 4)]
+            ref = reference_gpu_baseline(suite_cases, modes=(("cuttPlanMeasure", ["--measure"]),), reps=3)
+            r = ref.get("cuttPlanMeasure", {})
+            if "per_case_gbs" in r:
+                ours = extras["c3_suite"].pop("_per_case")
+                ratios = sorted(o / max(x, 1e-9) for o, x in zip(ours, r["per_case_gbs"]))
+                extras["reference_cutt_gpu"]["c3_suite_cuttPlanMeasure"] = {
+                    "median_gbs": statistics.median(r["per_case_gbs"]), "min_gbs": min(r["per_case_gbs"]),
+                    "max_gbs": max(r["per_case_gbs"]),
+                    "ours_over_reference": {"median": statistics.median(ratios), "min": ratios[0], "max": ratios[-1],
+                                            "cases_where_reference_is_faster": sum(1 for x in ratios if x < 1.0)}}
+            else:
+                extras["reference_cutt_gpu"]["c3_suite_cuttPlanMeasure"] = r
+        if "c3_suite" in extras:
+            extras["c3_suite"].pop("_per_case", None)
     if extras:
         line["extras"] = extras
     for p in plans:
@@ -484,7 +501,7 @@ def run_suite(C, cases, stream, reps=5):
     return out
 
 
-def reference_gpu_baseline(cases):
+def reference_gpu_baseline(cases, modes=(("cuttPlan", []), ("cuttPlanMeasure", ["--measure"])), reps=5):
     """The original cuTT on this GPU (PTX-JIT build, see oracle/build_ref.py), same shapes,
     both planning modes; runs in a child process because the original exits on CUDA errors."""
     try:
@@ -497,9 +514,9 @@ def reference_gpu_baseline(cases):
         with tempfile.NamedTemporaryFile("w", suffix=".json", delete=False) as f:
             json.dump(spec, f)
             path = f.name
-        for mode, flag in (("cuttPlan", []), ("cuttPlanMeasure", ["--measure"])):
-            res = subprocess.run([sys.executable, "-m", "oracle.ref_runner", path, "--reps", "5", "--no-hash"] + flag,
-                                 cwd=ROOT, stdout=subprocess.PIPE, stderr=subprocess.PIPE, text=True, timeout=600)
+        for mode, flag in modes:
+            res = subprocess.run([sys.executable, "-m", "oracle.ref_runner", path, "--reps", str(reps), "--device-input"] + flag,
+                                 cwd=ROOT, stdout=subprocess.PIPE, stderr=subprocess.PIPE, text=True, timeout=900)
             recs = [json.loads(ln) for ln in res.stdout.splitlines() if ln.startswith("{")]
             if res.returncode != 0 or len(recs) != len(spec):
                 out[mode] = {"error": (res.stderr or "no output")[-300:]}

@@ -55,9 +55,11 @@ def main():
     from sklearn.ensemble import GradientBoostingRegressor
     ap = argparse.ArgumentParser()
     ap.add_argument("data", nargs="+")
-    ap.add_argument("--trees", type=int, default=250)
-    ap.add_argument("--depth", type=int, default=4)
-    ap.add_argument("--lr", type=float, default=0.06)
+    ap.add_argument("--trees", type=int, default=300)
+    ap.add_argument("--depth", type=int, default=5)
+    ap.add_argument("--lr", type=float, default=0.05)
+    ap.add_argument("--wpow", type=float, default=6.0,
+                    help="sample weight = (achieved / best of its case)^wpow: accuracy matters near the top")
     ap.add_argument("--no-write", action="store_true")
     ap.add_argument("--mask", default="", help="comma-separated feature indices to zero (features whose meaning changed)")
     args = ap.parse_args()
@@ -70,9 +72,14 @@ def main():
     cases = sorted(set(r["case"] for r in rows))
     print("records %d, cases %d, features %d" % (len(rows), len(cases), X.shape[1]))
 
+    best = collections.defaultdict(float)
+    for g, v in zip(groups, y):
+        best[g] = max(best[g], v)
+    weight = np.array([(v / best[g]) ** args.wpow for g, v in zip(groups, y)])
+
     def fit(mask):
         return GradientBoostingRegressor(n_estimators=args.trees, max_depth=args.depth, learning_rate=args.lr,
-                                         subsample=0.8, random_state=0).fit(X[mask], y[mask])
+                                         subsample=0.8, random_state=0).fit(X[mask], y[mask], sample_weight=weight[mask])
 
     # leave-cases-out cross validation (both element sizes of a case are held out together)
     rng = np.random.default_rng(0)

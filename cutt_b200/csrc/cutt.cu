@@ -363,7 +363,7 @@ cuttResult make_plan(cuttHandle* handle, int rank, const int* dim, const int* pe
         // candidate once, cold, on stream 0; here: one warm-up and the best of three runs on
         // the plan's stream, after the same memset + device synchronisation).
         lk.unlock();
-        const size_t topk = env_size("CUTT_MEASURE_TOPK", 24);
+        const size_t topk = env_size("CUTT_MEASURE_TOPK", 48);
         cudaEvent_t e0, e1;
         if (cudaEventCreate(&e0) != cudaSuccess || cudaEventCreate(&e1) != cudaSuccess)
           return CUTT_INTERNAL_ERROR;
@@ -377,8 +377,9 @@ cuttResult make_plan(cuttHandle* handle, int rank, const int* dim, const int* pe
         Plan trial = *p;
         for (size_t i = 0; i < cands.size() && i < topk; i++) {
           if (!adopt_candidate(trial, dev, cands[i])) continue;
-          bool fail = run_plan(trial, req.idata, measureOut, stream, peers) != cudaSuccess;
+          bool fail = false;
           double tmin = 1e30;
+          // first run (doubles as warm-up); clearly slower candidates are dropped after it
           for (int rep = 0; rep < 3 && !fail; rep++) {
             cudaEventRecord(e0, stream);
             fail = run_plan(trial, req.idata, measureOut, stream, peers) != cudaSuccess;
@@ -386,6 +387,7 @@ cuttResult make_plan(cuttHandle* handle, int rank, const int* dim, const int* pe
             if (cudaEventSynchronize(e1) != cudaSuccess) fail = true;
             float ms = 0.f;
             if (!fail && cudaEventElapsedTime(&ms, e0, e1) == cudaSuccess && ms < tmin) tmin = ms;
+            if (rep == 0 && tmin > 1.2 * best) break;
           }
           if (fail) { cudaGetLastError(); continue; }
           if (verbose) fprintf(stderr, "[cutt] measure %2zu %8.4f ms  %s\n", i, tmin, cands[i].label.c_str());

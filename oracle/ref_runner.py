@@ -54,6 +54,8 @@ def main():
     ap.add_argument("--check", action="store_true", help="also compare with the CPU oracle")
     ap.add_argument("--seed", type=int, default=1234)
     ap.add_argument("--no-hash", action="store_true")
+    ap.add_argument("--device-input", action="store_true",
+                    help="timing only: random input generated on the device, output not read back")
     args = ap.parse_args()
     with open(args.cases) as f:
         cases = json.load(f)
@@ -67,8 +69,12 @@ def main():
         if vol >= 2**31:
             print(json.dumps({"dims": dims, "perm": perm, "elt": elt, "skipped": "volume >= 2^31: outside the original's int range"}))
             continue
-        a = input_bits(vol, elt, args.seed)
-        tin = torch.from_numpy(a.view(np.int32)).cuda()
+        if args.device_input:
+            a = None
+            tin = torch.randint(-2**31, 2**31 - 1, (vol * (elt // 4),), dtype=torch.int32, device="cuda")
+        else:
+            a = input_bits(vol, elt, args.seed)
+            tin = torch.from_numpy(a.view(np.int32)).cuda()
         tout = torch.zeros_like(tin)
         torch.cuda.synchronize()
         h = ctypes.c_uint(0)
@@ -97,6 +103,11 @@ def main():
         ms = min(ts) if ts else None
         rec = {"dims": dims, "perm": perm, "elt": elt, "ms": ms,
                "gbs": (2 * vol * elt / (ms * 1e-3) / 1e9) if ms else None}
+        if args.device_input:
+            print(json.dumps(rec))
+            sys.stdout.flush()
+            del tin, tout
+            continue
         out = tout.cpu().numpy()
         if not args.no_hash:
             rec["sha256"] = hashlib.sha256(out.tobytes()).hexdigest()
