@@ -370,11 +370,15 @@ def run_ours(args):
             if "per_case_gbs" in r:
                 ours = extras["c3_suite"].pop("_per_case")
                 ratios = sorted(o / max(x, 1e-9) for o, x in zip(ours, r["per_case_gbs"]))
+                behind = sorted(((o / max(x, 1e-9), i) for i, (o, x) in enumerate(zip(ours, r["per_case_gbs"]))))[:10]
+                behind = [{"case": i // 2, "elt": 8 if i % 2 == 0 else 4, "ours_gbs": round(ours[i], 1),
+                           "reference_gbs": r["per_case_gbs"][i]} for q, i in behind if q < 1.0]
                 extras["reference_cutt_gpu"]["c3_suite_cuttPlanMeasure"] = {
                     "median_gbs": statistics.median(r["per_case_gbs"]), "min_gbs": min(r["per_case_gbs"]),
                     "max_gbs": max(r["per_case_gbs"]),
                     "ours_over_reference": {"median": statistics.median(ratios), "min": ratios[0], "max": ratios[-1],
-                                            "cases_where_reference_is_faster": sum(1 for x in ratios if x < 1.0)}}
+                                            "cases_where_reference_is_faster": sum(1 for x in ratios if x < 1.0),
+                                            "slowest_relative_cases": behind}}
             else:
                 extras["reference_cutt_gpu"]["c3_suite_cuttPlanMeasure"] = r
         if "c3_suite" in extras:
