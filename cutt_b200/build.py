@@ -26,7 +26,7 @@ CXX_FLAGS = ["-O2", "-std=c++17", "-fPIC", "-Wall", "-Wno-unknown-pragmas"]
 
 CU_SOURCES = ["kernels.cu", "cutt.cu"]
 CXX_SOURCES = ["planner.cpp"]
-HEADERS = ["permute_desc.h", "permute_tile_impl.h", "planner.h", "kernels.h", "cost_model_data.h",
+HEADERS = ["permute_desc.h", "permute_tile_impl.h", "planner.h", "kernels.h", "cost_model_data.h", "rowcopy_impl.h",
            os.path.join("..", "..", "include", "cutt.h"), os.path.join("..", "..", "include", "cutt_c.h"),
            os.path.join("..", "..", "include", "cutt_mg.h")]
 

@@ -205,6 +205,9 @@ cudaError_t run_plan(const Plan& p, const void* in, void* out, cudaStream_t stre
       return launch_copy(in, out, p.bytes, p.numSM, stream);
     case kMethodNaive:
       return launch_naive(p.naive, in, out, stream);
+    case kMethodRowCopy:
+      if ((uintptr_t)in % p.elt || (uintptr_t)out % p.elt) return cudaErrorInvalidValue;
+      return launch_rowcopy(p.cand.rc, p.numSM, in, out, stream);
     case kMethodTiles: {
       PeerPtrs pp;
       for (int i = 0; i < kMaxPeers; i++) pp.p[i] = (unsigned char*)out;
@@ -322,6 +325,11 @@ cuttResult make_plan(cuttHandle* handle, int rank, const int* dim, const int* pe
     return CUTT_INVALID_PARAMETER;
   } else if (req.mode == kByParams) {
     if (req.method == kMethodNaive) { p->method = kMethodNaive; ok = true; }
+    else if (req.method == kMethodRowCopy) {
+      Candidate c;
+      if (!build_rowcopy(p->prob, dev, c)) return CUTT_INVALID_PARAMETER;
+      ok = adopt_candidate(*p, dev, c);
+    }
     else if (req.method == kMethodCopy || req.method == kMethodMemcpy) {
       if (!p->prob.identity) return CUTT_INVALID_PARAMETER;
       p->method = (Method)req.method; ok = true;
@@ -348,6 +356,9 @@ cuttResult make_plan(cuttHandle* handle, int rank, const int* dim, const int* pe
         if (cc.method == kMethodTiles) {
           Candidate c;
           ok = build_tile(p->prob, cc.params, dev, c) && adopt_candidate(*p, dev, c);
+        } else if (cc.method == kMethodRowCopy) {
+          Candidate c;
+          ok = build_rowcopy(p->prob, dev, c) && adopt_candidate(*p, dev, c);
         } else {
           p->method = cc.method;
           ok = true;
@@ -375,7 +386,9 @@ cuttResult make_plan(cuttHandle* handle, int rank, const int* dim, const int* pe
         double best = 1e30;
         int bestIdx = -1;
         Plan trial = *p;
-        for (size_t i = 0; i < cands.size() && i < topk; i++) {
+        for (size_t i = 0; i < cands.size(); i++) {
+          // beyond the model's best `topk`, only methods of another kind still get their turn
+          if (i >= topk && cands[i].method == kMethodTiles) continue;
           if (!adopt_candidate(trial, dev, cands[i])) continue;
           bool fail = false;
           double tmin = 1e30;
@@ -413,7 +426,8 @@ cuttResult make_plan(cuttHandle* handle, int rank, const int* dim, const int* pe
   if (verbose) {
     Candidate shown = p->cand;
     shown.method = p->method;
-    if (p->method != kMethodTiles) shown.label = p->method == kMethodNaive ? "naive" : (p->method == kMethodCopy ? "copy" : "memcpy");
+    if (p->method != kMethodTiles && p->method != kMethodRowCopy)
+      shown.label = p->method == kMethodNaive ? "naive" : (p->method == kMethodCopy ? "copy" : "memcpy");
     fprintf(stderr, "[cutt] plan %u (%s): %s\n", *handle, p->note.c_str(),
             canon ? describe(p->prob, shown).c_str() : "naive (rank too high after fusion)");
   }
@@ -777,7 +791,7 @@ int cutt_c_plan_cache_load(const char* path) {
                &t.vtargetBytes, &t.extend, &t.nthreads, &t.stages, &t.maxVecBytes, &t.maxVBytes,
                &t.loopOrder, &t.groupIn, &t.groupOut, &t.cutInRun, &t.allowAof) != 15)
       continue;
-    if (method < 0 || method > (int)kMethodNaive) continue;
+    if (method < 0 || method > (int)kMethodRowCopy) continue;
     c.method = (Method)method;
     plan_cache().put(key, c);
     n++;

@@ -103,6 +103,20 @@ static int dispatch(const TileDesc& D, const unsigned char* in, unsigned char* o
   return 4;
 }
 
+// Row-copy method: every work item, every lane, with all accesses range- and alignment-checked.
+static int run_rowcopy(const RowCopyDesc& R, const unsigned char* in, unsigned char* out, size_t bytes) {
+  rowcopy_bounds().in0 = in; rowcopy_bounds().in1 = in + bytes;
+  rowcopy_bounds().out0 = out; rowcopy_bounds().out1 = out + bytes;
+  rowcopy_violations() = 0;
+  for (uint32_t item = 0; item < R.numItems; item++)
+    for (uint32_t lane = 0; lane < 32; lane++) {
+      if (R.elt == 4) rowcopy_item<4>(R, in, out, item, lane);
+      else rowcopy_item<8>(R, in, out, item, lane);
+    }
+  if (rowcopy_violations()) { fprintf(stderr, "hostcheck: %lld bad row-copy accesses\n", rowcopy_violations()); return 9; }
+  return 0;
+}
+
 static DeviceInfo g_dev;
 
 extern "C" {
@@ -128,6 +142,7 @@ int cutt_hostcheck_run(int rank, const int* dim, const int* perm, int elt, int i
     memcpy(out, in, (size_t)P.volume * elt);
     return 0;
   }
+  if (c.method == kMethodRowCopy) return run_rowcopy(c.rc, (const unsigned char*)in, (unsigned char*)out, (size_t)P.volume * elt);
   return dispatch_checked(c.desc, (const unsigned char*)in, (unsigned char*)out, (size_t)P.volume * elt);
 }
 

@@ -214,6 +214,34 @@ cudaError_t launch_copy(const void* in, void* out, size_t bytes, int numSM, cuda
 }
 
 // ---------------------------------------------------------------------------------------
+// strided row copy (rowcopy_impl.h): one warp per work item, grid-stride
+template <int ELT>
+__global__ void __launch_bounds__(256)
+rowcopy_kernel(const __grid_constant__ RowCopyDesc D, const unsigned char* __restrict__ in,
+               unsigned char* __restrict__ out) {
+  const uint32_t lane = threadIdx.x & 31u;
+  const uint32_t wpb = blockDim.x >> 5;
+  const uint32_t stride = gridDim.x * wpb;
+  for (uint32_t item = blockIdx.x * wpb + (threadIdx.x >> 5); item < D.numItems; item += stride)
+    rowcopy_item<ELT>(D, in, out, item, lane);
+}
+
+cudaError_t launch_rowcopy(const RowCopyDesc& d, int numSM, const void* in, void* out, cudaStream_t stream) {
+  const int threads = 256;
+  int nb = 0;
+  const void* k = d.elt == 4 ? (const void*)rowcopy_kernel<4> : (const void*)rowcopy_kernel<8>;
+  if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&nb, k, threads, 0) != cudaSuccess || nb < 1) nb = 4;
+  long long want = ((long long)d.numItems + (threads / 32) - 1) / (threads / 32);
+  long long grid = (long long)numSM * nb;
+  if (grid > want) grid = want;
+  if (grid < 1) grid = 1;
+  if (d.elt == 4) rowcopy_kernel<4><<<(int)grid, threads, 0, stream>>>(d, (const unsigned char*)in, (unsigned char*)out);
+  else rowcopy_kernel<8><<<(int)grid, threads, 0, stream>>>(d, (const unsigned char*)in, (unsigned char*)out);
+  g_launches++;
+  return cudaGetLastError();
+}
+
+// ---------------------------------------------------------------------------------------
 // one thread per output element
 template <typename T>
 __global__ void __launch_bounds__(256)

@@ -30,6 +30,7 @@ cudaError_t launch_tiles(const Candidate& c, int gridBlocks, const void* in, con
                          cudaStream_t stream);
 cudaError_t launch_copy(const void* in, void* out, size_t bytes, int numSM, cudaStream_t stream);
 cudaError_t launch_naive(const NaiveDesc& d, const void* in, void* out, cudaStream_t stream);
+cudaError_t launch_rowcopy(const RowCopyDesc& d, int numSM, const void* in, void* out, cudaStream_t stream);
 
 // Number of kernel launches issued by this library since load (for benchmarks' accounting).
 unsigned long long launch_count();

@@ -10,6 +10,7 @@
 #include <string>
 #include <vector>
 #include "permute_desc.h"
+#include "rowcopy_impl.h"
 
 namespace cuttb {
 
@@ -64,6 +65,7 @@ enum Method : int {
   kMethodMemcpy = 1,   // identity: cudaMemcpyAsync device-to-device
   kMethodTiles = 2,    // tiled permutation kernel (cp.async staged)
   kMethodNaive = 3,    // one thread per output element (fallback for rank > kMaxDims, debug)
+  kMethodRowCopy = 4,  // strided copy of contiguous rows with register shifting (rowcopy_impl.h)
 };
 
 struct TileParams {
@@ -90,6 +92,7 @@ struct Candidate {
   float feat[kNumFeatures] = {0};  // inputs of the cost model (see candidate_features in planner.cpp)
   TileParams params;
   TileDesc desc;
+  RowCopyDesc rc;              // kMethodRowCopy only
   int smemBytes = 0;
   int blocksPerSM = 1;
   int gridBlocks = 0;
@@ -102,6 +105,9 @@ struct Candidate {
 // false when the same tile extents and launch options were already built (enumeration dedup).
 bool build_tile(const Problem& P, const TileParams& tp, const DeviceInfo& dev, Candidate& out,
                 std::set<std::string>* seenExtents = nullptr);
+
+// Row-copy candidate for problems whose fastest dimension is kept; false if not applicable.
+bool build_rowcopy(const Problem& P, const DeviceInfo& dev, Candidate& out);
 
 // All distinct candidates for a problem, cheapest model cost first.
 std::vector<Candidate> enumerate_candidates(const Problem& P, const DeviceInfo& dev);

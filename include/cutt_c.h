@@ -46,8 +46,8 @@ int cutt_c_plan_candidate(unsigned int* handle, int rank, const int* dim, const 
                           size_t sizeofType, void* stream, int index);
 
 /* Plan with an explicit tile parameter choice (tests; see TileParams in planner.h).
- * method: 2 = tiled kernel, 3 = one-thread-per-element kernel, 0 = copy kernel (identity only),
- * 1 = cudaMemcpyAsync (identity only). */
+ * method: 2 = tiled kernel, 3 = one-thread-per-element kernel, 4 = strided row copy (fastest
+ * dimension kept), 0 = copy kernel (identity only), 1 = cudaMemcpyAsync (identity only). */
 int cutt_c_plan_params(unsigned int* handle, int rank, const int* dim, const int* permutation,
                        size_t sizeofType, void* stream, int method, unsigned tinBytes,
                        unsigned toutBytes, unsigned vtargetBytes, int extend, int loopOrder,

@@ -92,6 +92,39 @@ def test_forced_parameters(native, oracle_mod, kw):
             assert_bit_exact(out, oracle_mod.transpose_blocked(dims, perm, a), "%s %s %s" % (dims, perm, desc))
 
 
+@pytest.mark.parametrize("dims,perm", [
+    ([317, 107, 6], [0, 2, 1]), ([1305, 59, 8], [0, 2, 1]), ([31, 7, 5, 3], [0, 3, 1, 2]), ([64, 10, 6], [0, 2, 1]),
+    ([4099, 5, 3], [0, 2, 1]), ([17, 5, 4], [0, 2, 1]), ([31713, 75, 6], [0, 2, 1]), ([2, 50, 9, 12], [0, 1, 3, 2]),
+])
+def test_row_copy_method(native, oracle_mod, dims, perm):
+    """Forced strided row copy (method 4): misaligned rows, heads and tails, both element sizes."""
+    for elt in (4, 8):
+        a = raw_bits(volume(dims), elt, 21)
+        out, desc = gpu_transpose(native, dims, perm, elt, a, planner="params", method=4)
+        assert "rowcopy" in desc
+        assert_bit_exact(out, oracle_mod.transpose_blocked(dims, perm, a), desc)
+    # not applicable when the fastest dimension moves
+    rc, _ = native.plan_params([64, 48], [1, 0], 4, method=4)
+    assert rc == native.CUTT_INVALID_PARAMETER
+
+
+def test_row_copy_unaligned_buffers(native, oracle_mod):
+    import torch
+    dims, perm = [317, 107, 6], [0, 2, 1]
+    vol = volume(dims)
+    a = raw_bits(vol, 4, 5)
+    big_in = torch.zeros(vol + 3, dtype=torch.int32, device="cuda")
+    big_out = torch.full((vol + 3,), -1, dtype=torch.int32, device="cuda")
+    big_in[1:vol + 1] = torch.from_numpy(a.view(np.int32)).cuda()
+    rc, h = native.plan_params(dims, perm, 4, method=4)
+    assert rc == 0
+    assert native.cuttExecute(h, big_in.data_ptr() + 4, big_out.data_ptr() + 8) == 0
+    torch.cuda.synchronize()
+    native.cuttDestroy(h)
+    assert_bit_exact(big_out[2:vol + 2].cpu().numpy().view(np.uint32), oracle_mod.transpose_blocked(dims, perm, a))
+    assert int(big_out[0].item()) == -1 and int(big_out[1].item()) == -1 and int(big_out[vol + 2].item()) == -1
+
+
 def test_streams(native, oracle_mod):
     """Ten plans on ten streams, all writing the same output (src/cutt_test.cpp:371-404)."""
     import torch
