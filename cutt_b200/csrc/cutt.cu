@@ -176,7 +176,7 @@ bool finalize_tiles(const DeviceInfo& dev, Candidate& c, int& grid) {
   if (nb <= 0) return false;
   c.blocksPerSM = nb;
   long long g = (long long)dev.numSM * nb;
-  if (g > (long long)c.desc.numTiles) g = c.desc.numTiles;
+  if (g > (long long)c.desc.numTiles || c.params.oneTilePerBlock) g = c.desc.numTiles;
   grid = (int)g;
   c.gridBlocks = grid;
   return true;
@@ -763,12 +763,12 @@ int cutt_c_plan_cache_save(const char* path) {
   std::lock_guard<std::mutex> lk(g_mutex);
   FILE* f = fopen(path, "w");
   if (!f) return CUTT_INTERNAL_ERROR;
-  fprintf(f, "# cutt-b200 plan cache v2\n");
+  fprintf(f, "# cutt-b200 plan cache v3\n");
   plan_cache().for_each_oldest_first([&](const std::string& k, const CachedChoice& c) {
     const TileParams& t = c.params;
-    fprintf(f, "%s %d %u %u %u %d %d %d %d %d %d %d %d %d %d\n", k.c_str(), (int)c.method, t.tinBytes, t.toutBytes,
+    fprintf(f, "%s %d %u %u %u %d %d %d %d %d %d %d %d %d %d %d\n", k.c_str(), (int)c.method, t.tinBytes, t.toutBytes,
             t.vtargetBytes, t.extend, t.nthreads, t.stages, t.maxVecBytes, t.maxVBytes, t.loopOrder,
-            t.groupIn, t.groupOut, t.cutInRun, t.allowAof);
+            t.groupIn, t.groupOut, t.cutInRun, t.allowAof, t.oneTilePerBlock);
   });
   fclose(f);
   return CUTT_SUCCESS;
@@ -787,9 +787,9 @@ int cutt_c_plan_cache_load(const char* path) {
     int method;
     CachedChoice c;
     TileParams& t = c.params;
-    if (sscanf(line, "%511s %d %u %u %u %d %d %d %d %d %d %d %d %d %d", key, &method, &t.tinBytes, &t.toutBytes,
+    if (sscanf(line, "%511s %d %u %u %u %d %d %d %d %d %d %d %d %d %d %d", key, &method, &t.tinBytes, &t.toutBytes,
                &t.vtargetBytes, &t.extend, &t.nthreads, &t.stages, &t.maxVecBytes, &t.maxVBytes,
-               &t.loopOrder, &t.groupIn, &t.groupOut, &t.cutInRun, &t.allowAof) != 15)
+               &t.loopOrder, &t.groupIn, &t.groupOut, &t.cutInRun, &t.allowAof, &t.oneTilePerBlock) != 16)
       continue;
     if (method < 0 || method > (int)kMethodRowCopy) continue;
     c.method = (Method)method;

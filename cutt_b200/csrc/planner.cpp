@@ -219,8 +219,8 @@ bool build_tile(const Problem& P, const TileParams& tp, const DeviceInfo& dev, C
     std::string key;
     char kb[64];
     for (int j = 0; j < r; j++) { snprintf(kb, sizeof kb, "%lld,", (long long)t[j]); key += kb; }
-    snprintf(kb, sizeof kb, "|%d%d%d%d%d%d%d%d", tp.nthreads, tp.stages, tp.maxVecBytes, tp.maxVBytes, tp.loopOrder,
-             tp.cutInRun, tp.allowAof, tp.groupIn * 16 + tp.groupOut);
+    snprintf(kb, sizeof kb, "|%d%d%d%d%d%d%d%d%d", tp.nthreads, tp.stages, tp.maxVecBytes, tp.maxVBytes, tp.loopOrder,
+             tp.cutInRun, tp.allowAof, tp.groupIn * 16 + tp.groupOut, tp.oneTilePerBlock);
     key += kb;
     if (!seenExtents->insert(key).second) return false;
   }
@@ -500,7 +500,8 @@ bool build_tile(const Problem& P, const TileParams& tp, const DeviceInfo& dev, C
   int bps = std::min(dev.smemPerSM / (out.smemBytes + 1024), dev.maxThreadsPerSM / tp.nthreads);
   bps = std::max(1, std::min(bps, 32));
   out.blocksPerSM = bps;
-  out.gridBlocks = (int)std::min<int64_t>(D.numTiles, (int64_t)dev.numSM * bps);
+  out.gridBlocks = tp.oneTilePerBlock ? (int)D.numTiles
+                                      : (int)std::min<int64_t>(D.numTiles, (int64_t)dev.numSM * bps);
 
   char buf[512];
   std::string ts;
@@ -512,6 +513,7 @@ bool build_tile(const Problem& P, const TileParams& tp, const DeviceInfo& dev, C
     snprintf(buf + strlen(buf), sizeof buf - strlen(buf), " g=%d/%d", D.split[0].used ? tp.groupIn : 1,
              D.split[1].used ? tp.groupOut : 1);
   }
+  if (tp.oneTilePerBlock) snprintf(buf + strlen(buf), sizeof buf - strlen(buf), " 1tpb");
   out.label = buf;
 
   // features of the cost model
@@ -562,7 +564,7 @@ bool build_tile(const Problem& P, const TileParams& tp, const DeviceInfo& dev, C
     f[27] = (float)D.nLoopDims;
     f[28] = lg(inRowStride);
     f[29] = lg(outRowStride);
-    f[30] = (float)D.wide;
+    f[30] = (float)D.wide + 2.f * (float)tp.oneTilePerBlock;
     f[31] = (float)D.aof;
   }
   out.cost = model_cost(P, out, dev);
@@ -721,6 +723,28 @@ std::vector<Candidate> enumerate_candidates(const Problem& P, const DeviceInfo& 
                   if (!seen.insert(c.label).second) continue;
                   res.push_back(c);
                 }
+  // small tiles, one per thread block, single stage: the hardware block scheduler replaces the
+  // persistent loop and many blocks per SM hide each other's phases
+  {
+    const uint32_t sruns[] = {128, 256, 512};
+    const uint32_t svols[] = {4096, 8192, 16384};
+    for (uint32_t tinB : sruns)
+      for (uint32_t toutB : sruns)
+        for (uint32_t vB : svols)
+          for (int lo = 0; lo < 2; lo++)
+            for (int nt = 128; nt <= 256; nt *= 2)
+              for (int aof = 1; aof >= 0; aof--) {
+                TileParams tp;
+                tp.tinBytes = tinB; tp.toutBytes = toutB; tp.vtargetBytes = vB;
+                tp.loopOrder = lo; tp.nthreads = nt; tp.stages = 1; tp.oneTilePerBlock = 1; tp.allowAof = aof;
+                Candidate c;
+                if (!build_tile(P, tp, dev, c, &seenExt)) continue;
+                if (c.smemBytes > 24 * 1024) continue;
+                if (!aof && P.elt == 4 && c.desc.in.vec == 1 && c.desc.in.run >= 8) continue;
+                if (!seen.insert(c.label).second) continue;
+                res.push_back(c);
+              }
+  }
   {
     Candidate rc;
     if (build_rowcopy(P, dev, rc)) res.push_back(rc);

@@ -79,6 +79,7 @@ struct TileParams {
   int maxVBytes = 16;          // widest shared-memory vector of the register-blocked store side
   int cutInRun = 0;            // end the input run before the dimension that starts the output run, so that
                                // dimension gets a padded (bank-conflict-free) shared-memory stride
+  int oneTilePerBlock = 0;     // launch one block per tile (no persistent loop); for small tiles
   int allowAof = 1;            // aligned over-fetch loads when input rows are not 16-byte aligned
   int loopOrder = 0;           // tile index runs fastest along 0: input order, 1: output order
   int groupIn = 1;             // neighbouring tiles along the input run's chunked dimension taken first

@@ -94,13 +94,13 @@ def test_missing_library_fails_loudly(monkeypatch, native):
 def test_plan_cache_file_roundtrip(native, tmp_path):
     path = str(tmp_path / "plans.txt")
     with open(path, "w") as f:
-        f.write("# cutt-b200 plan cache v2\n0/4/64,48,/1,0, 2 128 512 65536 1 512 2 16 16 1 2 4 0 1\n")
+        f.write("# cutt-b200 plan cache v3\n0/4/64,48,/1,0, 2 128 512 65536 1 512 2 16 16 1 2 4 0 1 0\n")
     native.clear_plan_cache()
     assert native.plan_cache_load(path) == 0
     assert native.plan_cache_size() == 1
     out = str(tmp_path / "out.txt")
     assert native.plan_cache_save(out) == 0
-    assert "0/4/64,48,/1,0, 2 128 512 65536 1 512 2 16 16 1 2 4 0 1" in open(out).read()
+    assert "0/4/64,48,/1,0, 2 128 512 65536 1 512 2 16 16 1 2 4 0 1 0" in open(out).read()
     native.clear_plan_cache()
     assert native.plan_cache_size() == 0
 
