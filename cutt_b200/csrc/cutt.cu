@@ -213,6 +213,7 @@ cudaError_t run_plan(const Plan& p, const void* in, void* out, cudaStream_t stre
       for (int i = 0; i < kMaxPeers; i++) pp.p[i] = (unsigned char*)out;
       if (tiles_pointers_aligned(p.cand, in, out)) return launch_tiles(p.cand, p.grid, in, pp, stream);
       if (p.haveFallback) return launch_tiles(p.fallback, p.fallbackGrid, in, pp, stream);
+      if (p.mgMode >= 1) return cudaErrorInvalidValue;
       return launch_naive(p.naive, in, out, stream);
     }
   }
@@ -258,6 +259,8 @@ struct PlanRequest {
   PlanMode mode = kByModel;
   void* idata = nullptr;
   void* odata = nullptr;
+  int chunkLast = 0;           // > 0: plan for a slab of this extent along the last dimension,
+                               // written into the full output tensor (host pipeline)
   int world = 0;               // > 0: multi-GPU plan for rank `me`
   int me = 0;
   void* const* peers = nullptr;  // output slabs per rank (measure mode)
@@ -303,6 +306,12 @@ cuttResult make_plan(cuttHandle* handle, int rank, const int* dim, const int* pe
     p->bytes = (size_t)info.localVolume * elt;
     if (info.mode == 0) fill_naive(*p, rank, info.localDim, perm);
     key += "/mg" + std::to_string(req.world) + "." + std::to_string(req.me);
+  } else if (req.chunkLast > 0) {
+    if (!problem_from_cutt_chunk(rank, dim, perm, (int)elt, req.chunkLast, p->prob)) return CUTT_INVALID_PARAMETER;
+    canon = true;
+    p->bytes = (size_t)p->prob.volume * elt;
+    p->mgMode = 2;  // no element-wise fallback: the output is a strided part of a larger tensor
+    key += "/chunk" + std::to_string(req.chunkLast);
   } else {
     size_t vol = 1;
     for (int i = 0; i < rank; i++) vol *= (size_t)dim[i];
@@ -343,7 +352,7 @@ cuttResult make_plan(cuttHandle* handle, int rank, const int* dim, const int* pe
     // (a copy: the cached list may be replaced by another thread while this one measures)
     const std::vector<Candidate> cands = enumerate_cached(key, p->prob, dev);
     if (cands.empty()) {
-      if (p->mgMode == 1) return CUTT_INTERNAL_ERROR;  // no local fallback can write peer slabs
+      if (p->mgMode >= 1) return CUTT_INTERNAL_ERROR;  // no element-wise fallback for these
       p->method = kMethodNaive;
       ok = true;
     } else if (req.mode == kByIndex) {
@@ -563,12 +572,18 @@ int cutt_c_plan_params(unsigned int* handle, int rank, const int* dim, const int
 
 int cutt_c_transpose_host(int rank, const int* dim, const int* permutation, size_t sizeofType,
                           const void* hin, void* hout) {
-  // device scratch, grown on demand and kept (one pair per process; serialised)
+  // Device scratch (one pair of buffers per process, grown on demand, kept), three streams and a
+  // few events; calls are serialised.  Large tensors are cut into slabs along the slowest input
+  // dimension so that the upload of slab k+1, the kernel of slab k and the download of slab k-1
+  // overlap (PCIe is full duplex); each slab is permuted straight into its strided place in the
+  // device output, which is downloaded with a 2-D copy.
   static std::mutex hostMutex;
   static void* dIn = nullptr;
   static void* dOut = nullptr;
   static size_t cap = 0;
   static int capDev = -1;
+  static cudaStream_t sUp = nullptr, sRun = nullptr, sDown = nullptr;
+  static std::vector<cudaEvent_t> evUp, evRun;
   static std::unordered_map<std::string, cuttHandle> plans;
   if (check_input(rank, dim, permutation, sizeofType) != CUTT_SUCCESS) return CUTT_INVALID_PARAMETER;
   if (!hin || !hout) return CUTT_INVALID_PARAMETER;
@@ -577,7 +592,8 @@ int cutt_c_transpose_host(int rank, const int* dim, const int* permutation, size
   if (cudaGetDevice(&dev) != cudaSuccess) return CUTT_INTERNAL_ERROR;
   size_t bytes = sizeofType;
   for (int i = 0; i < rank; i++) bytes *= (size_t)dim[i];
-  if (bytes > cap || dev != capDev) {
+  if (dev != capDev && capDev >= 0) return CUTT_INVALID_DEVICE;  // the scratch belongs to the first device used
+  if (bytes > cap) {
     if (dIn) cudaFree(dIn);
     if (dOut) cudaFree(dOut);
     dIn = dOut = nullptr;
@@ -591,22 +607,75 @@ int cutt_c_transpose_host(int rank, const int* dim, const int* permutation, size
     cap = bytes;
     capDev = dev;
   }
-  std::string key = problem_key(dev, rank, dim, permutation, sizeofType);
-  cuttHandle h;
-  auto it = plans.find(key);
-  if (it == plans.end()) {
-    PlanRequest req;
-    cuttResult r = make_plan(&h, rank, dim, permutation, sizeofType, 0, req);
-    if (r != CUTT_SUCCESS) return r;
-    plans[key] = h;
-  } else {
-    h = it->second;
+  if (!sUp) {
+    if (cudaStreamCreateWithFlags(&sUp, cudaStreamNonBlocking) != cudaSuccess ||
+        cudaStreamCreateWithFlags(&sRun, cudaStreamNonBlocking) != cudaSuccess ||
+        cudaStreamCreateWithFlags(&sDown, cudaStreamNonBlocking) != cudaSuccess)
+      return CUTT_INTERNAL_ERROR;
   }
-  if (cudaMemcpyAsync(dIn, hin, bytes, cudaMemcpyHostToDevice, 0) != cudaSuccess) return CUTT_INTERNAL_ERROR;
-  cuttResult r = cuttExecute(h, dIn, dOut);
-  if (r != CUTT_SUCCESS) return r;
-  if (cudaMemcpyAsync(hout, dOut, bytes, cudaMemcpyDeviceToHost, 0) != cudaSuccess) return CUTT_INTERNAL_ERROR;
-  if (cudaStreamSynchronize(0) != cudaSuccess) return CUTT_INTERNAL_ERROR;
+  const int last = rank - 1;
+  const int dlast = dim[last];
+  int nslab = 1;
+  if (bytes >= (size_t)64 << 20) nslab = dlast < 8 ? dlast : 8;
+  // strides of the slowest input dimension on both sides (elements)
+  size_t isLast = 1, osLast = 1;
+  for (int i = 0; i < last; i++) isLast *= (size_t)dim[i];
+  for (int k = 0; k < rank && permutation[k] != last; k++) osLast *= (size_t)dim[permutation[k]];
+  const size_t pitch = osLast * (size_t)dlast * sizeofType;   // distance between the pieces of a slab's output
+  const size_t height = bytes / pitch;
+  if (nslab > 1 && height > 1 && pitch >= ((size_t)1 << 31)) nslab = 1;  // beyond what a 2-D copy can describe
+  int chunk = (dlast + nslab - 1) / nslab;
+  if (nslab > 1 && chunk >= 32) chunk = (chunk + 15) / 16 * 16;  // keeps slab offsets 16-byte aligned
+  nslab = (dlast + chunk - 1) / chunk;
+  while ((int)evUp.size() < nslab) {
+    cudaEvent_t a, b;
+    if (cudaEventCreateWithFlags(&a, cudaEventDisableTiming) != cudaSuccess ||
+        cudaEventCreateWithFlags(&b, cudaEventDisableTiming) != cudaSuccess)
+      return CUTT_INTERNAL_ERROR;
+    evUp.push_back(a);
+    evRun.push_back(b);
+  }
+  auto plan_for = [&](int extent, cuttHandle& h) -> cuttResult {
+    std::string key = problem_key(dev, rank, dim, permutation, sizeofType) + "/host" + std::to_string(extent);
+    auto it = plans.find(key);
+    if (it != plans.end()) { h = it->second; return CUTT_SUCCESS; }
+    PlanRequest req;
+    if (extent != dlast) req.chunkLast = extent;
+    cuttResult r = make_plan(&h, rank, dim, permutation, sizeofType, sRun, req);
+    if (r == CUTT_SUCCESS) plans[key] = h;
+    return r;
+  };
+  for (int k = 0; k < nslab; k++) {
+    const int c0 = k * chunk;
+    const int ext = (c0 + chunk <= dlast) ? chunk : dlast - c0;
+    cuttHandle h;
+    cuttResult r = plan_for(ext, h);
+    if (r != CUTT_SUCCESS) return r;
+    const size_t inOff = (size_t)c0 * isLast * sizeofType;
+    const size_t inBytes = (size_t)ext * isLast * sizeofType;
+    const size_t outOff = (size_t)c0 * osLast * sizeofType;
+    const size_t width = (size_t)ext * osLast * sizeofType;
+    if (cudaMemcpyAsync((char*)dIn + inOff, (const char*)hin + inOff, inBytes, cudaMemcpyHostToDevice, sUp) != cudaSuccess ||
+        cudaEventRecord(evUp[k], sUp) != cudaSuccess || cudaStreamWaitEvent(sRun, evUp[k], 0) != cudaSuccess)
+      return CUTT_INTERNAL_ERROR;
+    const Plan* p = nullptr;
+    {
+      std::lock_guard<std::mutex> lk2(g_mutex);
+      auto it = g_plans.find(h);
+      if (it == g_plans.end()) return CUTT_INTERNAL_ERROR;
+      p = it->second.get();
+    }
+    if (run_plan(*p, (char*)dIn + inOff, (char*)dOut + outOff, sRun) != cudaSuccess) return CUTT_INTERNAL_ERROR;
+    if (cudaEventRecord(evRun[k], sRun) != cudaSuccess || cudaStreamWaitEvent(sDown, evRun[k], 0) != cudaSuccess)
+      return CUTT_INTERNAL_ERROR;
+    cudaError_t e;
+    if (nslab == 1) e = cudaMemcpyAsync(hout, dOut, bytes, cudaMemcpyDeviceToHost, sDown);
+    else if (height == 1) e = cudaMemcpyAsync((char*)hout + outOff, (char*)dOut + outOff, width, cudaMemcpyDeviceToHost, sDown);
+    else e = cudaMemcpy2DAsync((char*)hout + outOff, pitch, (char*)dOut + outOff, pitch, width, height,
+                               cudaMemcpyDeviceToHost, sDown);
+    if (e != cudaSuccess) return CUTT_INTERNAL_ERROR;
+  }
+  if (cudaStreamSynchronize(sDown) != cudaSuccess) return CUTT_INTERNAL_ERROR;
   return CUTT_SUCCESS;
 }
 

@@ -204,6 +204,67 @@ int cutt_hostcheck_run_sharded(int rank, const int* dim, const int* perm, int el
   return info.mode;
 }
 
+// The host-buffer pipeline cuts the input into slabs along its slowest dimension and permutes
+// each slab straight into the full output (strided).  This runs that decomposition on the host:
+// `nslab` slabs, candidate `index` of each slab's enumeration.
+int cutt_hostcheck_run_chunked(int rank, const int* dim, const int* perm, int elt, int nslab, int index,
+                               const void* in, void* out) {
+  const int last = rank - 1;
+  const int dlast = dim[last];
+  if (nslab < 1) return 2;
+  const int chunk = (dlast + nslab - 1) / nslab;
+  size_t isLast = 1, osLast = 1;
+  for (int i = 0; i < last; i++) isLast *= (size_t)dim[i];
+  for (int k = 0; k < rank && perm[k] != last; k++) osLast *= (size_t)dim[perm[k]];
+  size_t total = (size_t)elt;
+  for (int i = 0; i < rank; i++) total *= (size_t)dim[i];
+  for (int c0 = 0; c0 < dlast; c0 += chunk) {
+    const int ext = c0 + chunk <= dlast ? chunk : dlast - c0;
+    Problem P;
+    if (!problem_from_cutt_chunk(rank, dim, perm, elt, ext, P)) return 2;
+    const unsigned char* pin = (const unsigned char*)in + (size_t)c0 * isLast * elt;
+    unsigned char* pout = (unsigned char*)out + (size_t)c0 * osLast * elt;
+    std::vector<Candidate> cands = enumerate_candidates(P, g_dev);
+    if (cands.empty()) return 3;
+    Candidate c = cands[(size_t)index % cands.size()];
+    if (c.method == kMethodTiles) {
+      // what the library does at execute time: pointers that are not aligned for the plan's
+      // vector widths take the element-wise variant of the same tile
+      const TileDesc& D = c.desc;
+      const bool inOk = D.aof ? true : ((uintptr_t)pin % (D.in.vec * D.elt) == 0);
+      const bool outOk = (uintptr_t)pout % (D.out.vec * D.elt) == 0;
+      if (!inOk || !outOk) {
+        TileParams tp = c.params;
+        tp.maxVecBytes = elt; tp.maxVBytes = elt; tp.allowAof = 0;
+        Candidate f;
+        if (!build_tile(P, tp, g_dev, f)) return 6;
+        c = f;
+      }
+    }
+    if (c.method == kMethodCopy || c.method == kMethodMemcpy) {
+      memcpy(pout, pin, (size_t)P.volume * elt);
+    } else if (c.method == kMethodRowCopy) {
+      rowcopy_bounds().in0 = pin; rowcopy_bounds().in1 = pin + (size_t)P.volume * elt;
+      rowcopy_bounds().out0 = (unsigned char*)out; rowcopy_bounds().out1 = (unsigned char*)out + total;
+      rowcopy_violations() = 0;
+      for (uint32_t item = 0; item < c.rc.numItems; item++)
+        for (uint32_t lane = 0; lane < 32; lane++) {
+          if (elt == 4) rowcopy_item<4>(c.rc, pin, pout, item, lane);
+          else rowcopy_item<8>(c.rc, pin, pout, item, lane);
+        }
+      if (rowcopy_violations()) return 9;
+    } else {
+      HostBounds& b = host_bounds();
+      b.gin0 = pin; b.gin1 = pin + (size_t)P.volume * elt;
+      b.gout0 = (unsigned char*)out; b.gout1 = (unsigned char*)out + total;
+      b.violations = 0;
+      if (dispatch(c.desc, pin, pout)) return 4;
+      if (b.violations) return 9;
+    }
+  }
+  return 0;
+}
+
 // Exhaustive-ish self check of the division helper: returns the number of mismatches.
 long long cutt_hostcheck_fastdiv(unsigned d, unsigned long long nmax, unsigned long long step) {
   FastDiv f = make_fastdiv(d);

@@ -62,6 +62,18 @@ bool problem_from_cutt(int rank, const int* dim, const int* perm, int elt, Probl
   return canonicalize(rank, d.data(), is.data(), os.data(), elt, -1, P);
 }
 
+bool problem_from_cutt_chunk(int rank, const int* dim, const int* perm, int elt, int chunk, Problem& P) {
+  if (rank < 1 || chunk < 1 || chunk > dim[rank - 1]) return false;
+  std::vector<int64_t> d(rank), is(rank), os(rank);
+  int64_t acc = 1;
+  for (int i = 0; i < rank; i++) { d[i] = i == rank - 1 ? chunk : dim[i]; is[i] = acc; acc *= d[i]; }
+  acc = 1;
+  for (int k = 0; k < rank; k++) { os[perm[k]] = acc; acc *= dim[perm[k]]; }
+  if (!canonicalize(rank, d.data(), is.data(), os.data(), elt, -1, P)) return false;
+  // one contiguous block on both sides only if the slab is also contiguous in the output
+  return true;
+}
+
 bool problem_from_cutt_sharded(int rank, const int* dim, const int* perm, int elt, int world, int me,
                                Problem& P, ShardInfo& info) {
   info = ShardInfo();

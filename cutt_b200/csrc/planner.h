@@ -60,6 +60,11 @@ struct ShardInfo {
 bool problem_from_cutt_sharded(int rank, const int* dim, const int* perm, int elt, int world, int me,
                                Problem& P, ShardInfo& info);
 
+// A slab of the input along its slowest dimension (extent `chunk` instead of dim[rank-1]) permuted
+// INTO the full output tensor: input strides of the slab, output strides of the whole tensor.
+// Used to pipeline host transfers with the kernel.
+bool problem_from_cutt_chunk(int rank, const int* dim, const int* perm, int elt, int chunk, Problem& P);
+
 enum Method : int {
   kMethodCopy = 0,     // identity after fusion: contiguous copy kernel
   kMethodMemcpy = 1,   // identity: cudaMemcpyAsync device-to-device

@@ -120,6 +120,26 @@ def test_forced_parameters(hc, oracle_mod, kw):
             assert np.array_equal(out, oracle_mod.transpose_blocked(dims, perm, a)), (dims, perm, elt, lab.value.decode())
 
 
+@pytest.mark.parametrize("dims,perm", [
+    ([130, 257], [1, 0]), ([64, 48, 20], [2, 1, 0]), ([64, 48, 20], [1, 0, 2]), ([31, 54, 2, 9], [3, 0, 2, 1]),
+    ([317, 17, 6], [0, 2, 1]), ([8, 6, 30, 50], [3, 0, 2, 1]), ([12, 10, 7], [0, 1, 2]),
+])
+def test_host_pipeline_slabs(hc, oracle_mod, dims, perm):
+    """Slabs of the input permuted into the strided full output (the host-buffer pipeline)."""
+    hc.cutt_hostcheck_run_chunked.argtypes = [ctypes.c_int, ctypes.POINTER(ctypes.c_int), ctypes.POINTER(ctypes.c_int),
+                                              ctypes.c_int, ctypes.c_int, ctypes.c_int, ctypes.c_void_p, ctypes.c_void_p]
+    for elt in (4, 8):
+        a = raw_bits(volume(dims), elt, 2)
+        want = oracle_mod.transpose_blocked(dims, perm, a)
+        for nslab in (1, 2, 3, 8):
+            for index in (0, 2):
+                out = np.full_like(a, 0x5A)
+                rc = hc.cutt_hostcheck_run_chunked(len(dims), _iarr(dims), _iarr(perm), elt, nslab, index,
+                                                   a.ctypes.data, out.ctypes.data)
+                assert rc == 0, (rc, dims, perm, elt, nslab, index)
+                assert np.array_equal(out, want), (dims, perm, elt, nslab, index)
+
+
 def test_candidate_descriptions_are_json(hc):
     dims, perm = [64, 48, 20], [2, 1, 0]
     a = raw_bits(volume(dims), 4, 1)
