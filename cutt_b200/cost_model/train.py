@@ -28,7 +28,8 @@ def load(paths):
             for line in f:
                 if '"feat"' in line:
                     r = json.loads(line)
-                    if len(r["feat"]) and r["gbs"] > 0:
+                    # only tile candidates carry features; other methods have closed-form costs
+                    if len(r["feat"]) and r["gbs"] > 0 and r["label"].startswith("tiles"):
                         rows.append(r)
     return rows
 

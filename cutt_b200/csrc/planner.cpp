@@ -663,12 +663,11 @@ bool build_rowcopy(const Problem& P, const DeviceInfo& dev, Candidate& out) {
     R.os[j - 1] = P.os[j];
     if (P.is[j] % VE || P.os[j] % VE) aligned = false;
   }
-  // measured on B200 (row lengths 0.5-120 KB): 0.75-0.9 of the copy bandwidth; rows that are
-  // 16-byte aligned on both sides are served at least as well by the tiled kernel
-  const double rb = (double)L * elt;
-  double eff = (aligned ? 0.70 : 0.82) * rb / (rb + 192.0);
-  // lanes idle in the last segment of short rows
-  eff *= (double)slots / (double)(segs * 32 * kRowCopyUnroll) * 0.5 + 0.5;
+  // measured on B200: 0.85-0.89 of the copy bandwidth when the lanes of a work item are all
+  // busy (rows of 0.5 K elements and more), proportionally less for rows that leave lanes idle
+  (void)aligned;
+  if (L * elt < 512) return false;
+  double eff = 0.86 * (double)slots / (double)(segs * 32 * kRowCopyUnroll);
   out.cost = 2.0 * (double)P.volume * elt / (dev.hbmGBs * 1e9 * eff) + 4e-6;
   char buf[128];
   snprintf(buf, sizeof buf, "rowcopy rows=%lldx%lld %s", (long long)nrows, (long long)L, aligned ? "aligned" : "misaligned");

@@ -93,8 +93,8 @@ def test_forced_parameters(native, oracle_mod, kw):
 
 
 @pytest.mark.parametrize("dims,perm", [
-    ([317, 107, 6], [0, 2, 1]), ([1305, 59, 8], [0, 2, 1]), ([31, 7, 5, 3], [0, 3, 1, 2]), ([64, 10, 6], [0, 2, 1]),
-    ([4099, 5, 3], [0, 2, 1]), ([17, 5, 4], [0, 2, 1]), ([31713, 75, 6], [0, 2, 1]), ([2, 50, 9, 12], [0, 1, 3, 2]),
+    ([317, 107, 6], [0, 2, 1]), ([1305, 59, 8], [0, 2, 1]), ([131, 7, 5, 3], [0, 3, 1, 2]), ([128, 10, 6], [0, 2, 1]),
+    ([4099, 5, 3], [0, 2, 1]), ([1031, 5, 4], [0, 2, 1]), ([31713, 75, 6], [0, 2, 1]), ([2, 150, 9, 12], [0, 1, 3, 2]),
 ])
 def test_row_copy_method(native, oracle_mod, dims, perm):
     """Forced strided row copy (method 4): misaligned rows, heads and tails, both element sizes."""
@@ -103,8 +103,10 @@ def test_row_copy_method(native, oracle_mod, dims, perm):
         out, desc = gpu_transpose(native, dims, perm, elt, a, planner="params", method=4)
         assert "rowcopy" in desc
         assert_bit_exact(out, oracle_mod.transpose_blocked(dims, perm, a), desc)
-    # not applicable when the fastest dimension moves
+    # not applicable when the fastest dimension moves, nor for rows shorter than 512 bytes
     rc, _ = native.plan_params([64, 48], [1, 0], 4, method=4)
+    assert rc == native.CUTT_INVALID_PARAMETER
+    rc, _ = native.plan_params([31, 7, 5], [0, 2, 1], 4, method=4)
     assert rc == native.CUTT_INVALID_PARAMETER
 
 
