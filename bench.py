@@ -374,6 +374,19 @@ def run_ours(args):
         except Exception as e:  # extras never fail the headline
             extras["c3_suite"] = {"error": repr(e)}
     if rank == 0 and not args.no_extras and world == 1:
+        # the 0.8 MB README tensor (configs[0]): launch/latency-bound, reported beside the suites
+        try:
+            d1, p1 = W.C1
+            res1 = run_suite(C, [(d1, p1)], stream, reps=20)
+            extras["c1_readme_example"] = {"dims": d1, "perm": p1,
+                                           "fp64_us": res1[0]["ms"] * 1e3, "fp64_gbs": res1[0]["gbs"],
+                                           "fp32_us": res1[1]["ms"] * 1e3, "fp32_gbs": res1[1]["gbs"],
+                                           "plan_fp64": res1[0]["plan"]}
+            ref1 = reference_gpu_baseline([("c1", d1, p1, 8), ("c1", d1, p1, 4)],
+                                          modes=(("cuttPlanMeasure", ["--measure"]),), reps=20)
+            extras["c1_readme_example"]["reference_cutt_gpu_gbs"] = ref1.get("cuttPlanMeasure", {}).get("per_case_gbs")
+        except Exception as e:
+            extras["c1_readme_example"] = {"error": repr(e)}
         extras["reference_cutt_gpu"] = reference_gpu_baseline(cases)
         if "c3_suite" in extras and "error" not in extras["c3_suite"]:
             suite_cases = [("c3", d, p, e) for d, p in W.c3_cases(args.suite_cases) for e in (8, 4)]

@@ -617,6 +617,7 @@ int cutt_c_transpose_host(int rank, const int* dim, const int* permutation, size
   const int dlast = dim[last];
   int nslab = 1;
   if (bytes >= (size_t)64 << 20) nslab = dlast < 8 ? dlast : 8;
+  if (bytes >= (size_t)512 << 20 && dlast >= 256) nslab = 16;  // shorter unoverlapped head and tail
   // strides of the slowest input dimension on both sides (elements)
   size_t isLast = 1, osLast = 1;
   for (int i = 0; i < last; i++) isLast *= (size_t)dim[i];
