@@ -1,0 +1,195 @@
+// Contiguous copy through the bulk asynchronous copy engine (TMA without a tensor map):
+// global -> shared with cp.async.bulk + mbarrier transaction counts, shared -> global with
+// cp.async.bulk bulk groups.  One thread per block drives a ring of 32 KB stages; no thread
+// touches the data.  Used for identity permutations (the reference's Trivial method,
+// src/cuttkernel.cu:846-851, calls cudaMemcpyAsync) when both buffers are 16-byte aligned.
+//
+// Every wait on an mbarrier is bounded: after kBulkSpinLimit failed polls the block counts a
+// timeout in a status word in global memory, drains what it has in flight (bounded again) and
+// returns, so a lost completion can never hang the device.  The status word is the only global
+// memory the kernel uses besides its input and output.
+#include "kernels.h"
+#include <map>
+#include <mutex>
+
+namespace cuttb {
+
+constexpr uint32_t kBulkChunk = 32u * 1024u;   // bytes per stage
+constexpr int kBulkStages = 4;                 // 128 KB of shared memory per block
+constexpr uint32_t kBulkSpinLimit = 1u << 22;  // polls of a barrier before giving up
+
+__device__ __forceinline__ uint32_t shared_addr(const void* p) {
+  return (uint32_t)__cvta_generic_to_shared(p);
+}
+
+__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;\n" ::"r"(bar), "r"(count) : "memory");
+}
+
+__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;\n" ::"r"(bar), "r"(bytes) : "memory");
+}
+
+__device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{\n"
+      "  .reg .pred p;\n"
+      "  mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n"
+      "  selp.u32 %0, 1, 0, p;\n"
+      "}\n"
+      : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
+  return ok != 0;
+}
+
+// false if the barrier did not complete the awaited phase within the poll limit
+__device__ __forceinline__ bool mbar_wait_bounded(uint32_t bar, uint32_t parity) {
+  for (uint32_t spin = 0; spin < kBulkSpinLimit; spin++)
+    if (mbar_try_wait(bar, parity)) return true;
+  return false;
+}
+
+__device__ __forceinline__ void bulk_g2s(uint32_t dst, const void* src, uint32_t bytes, uint32_t bar) {
+  asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];\n"
+               ::"r"(dst), "l"(src), "r"(bytes), "r"(bar) : "memory");
+}
+
+__device__ __forceinline__ void bulk_s2g(void* dst, uint32_t src, uint32_t bytes) {
+  asm volatile("cp.async.bulk.global.shared::cta.bulk_group [%0], [%1], %2;\n"
+               ::"l"(dst), "r"(src), "r"(bytes) : "memory");
+}
+
+__device__ __forceinline__ void bulk_commit() { asm volatile("cp.async.bulk.commit_group;\n" ::: "memory"); }
+// all committed stores have finished READING shared memory
+__device__ __forceinline__ void bulk_wait_read_all() { asm volatile("cp.async.bulk.wait_group.read 0;\n" ::: "memory"); }
+// all committed stores are complete
+__device__ __forceinline__ void bulk_wait_all() { asm volatile("cp.async.bulk.wait_group 0;\n" ::: "memory"); }
+
+// nbytes: multiple of 16; in/out: 16-byte aligned.
+__global__ void __launch_bounds__(32, 1)
+bulk_copy_kernel(const unsigned char* __restrict__ in, unsigned char* __restrict__ out,
+                 unsigned long long nbytes, unsigned int* __restrict__ status) {
+  extern __shared__ __align__(128) unsigned char stages[];
+  __shared__ __align__(8) unsigned long long full[kBulkStages];
+  if (threadIdx.x != 0) return;  // the copy engine does the work; one thread issues and waits
+
+  const uint32_t bar0 = shared_addr(full);
+  const uint32_t st0 = shared_addr(stages);
+  for (int s = 0; s < kBulkStages; s++) mbar_init(bar0 + 8u * s, 1);
+  // make the initialised barriers visible to the asynchronous proxy before it signals them
+  asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
+  asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");
+
+  const unsigned long long nchunks = (nbytes + kBulkChunk - 1) / kBulkChunk;
+  const unsigned long long first = blockIdx.x, stride = gridDim.x;
+  if (first >= nchunks) return;
+  const unsigned long long nlocal = (nchunks - first + stride - 1) / stride;
+
+  auto load = [&](unsigned long long i) {
+    const unsigned long long off = (first + i * stride) * kBulkChunk;
+    const unsigned long long rem = nbytes - off;
+    const uint32_t bytes = rem < kBulkChunk ? (uint32_t)rem : kBulkChunk;
+    const uint32_t s = (uint32_t)(i % kBulkStages);
+    mbar_expect_tx(bar0 + 8u * s, bytes);
+    bulk_g2s(st0 + s * kBulkChunk, in + off, bytes, bar0 + 8u * s);
+  };
+
+  unsigned long long issued = 0;
+  for (; issued < nlocal && issued < (unsigned long long)kBulkStages; issued++) load(issued);
+
+  bool failed = false;
+  unsigned long long i = 0;
+  for (; i < nlocal; i++) {
+    const uint32_t s = (uint32_t)(i % kBulkStages);
+    const uint32_t parity = (uint32_t)((i / kBulkStages) & 1ull);
+    if (!mbar_wait_bounded(bar0 + 8u * s, parity)) { failed = true; break; }
+    const unsigned long long off = (first + i * stride) * kBulkChunk;
+    const unsigned long long rem = nbytes - off;
+    const uint32_t bytes = rem < kBulkChunk ? (uint32_t)rem : kBulkChunk;
+    bulk_s2g(out + off, st0 + s * kBulkChunk, bytes);
+    bulk_commit();
+    if (issued < nlocal) {
+      bulk_wait_read_all();  // the stage may be overwritten once the store has read it
+      load(issued);
+      issued++;
+    }
+  }
+  if (failed) {
+    atomicAdd(status, 1u);
+    // loads i .. issued-1 may still be in flight: give each its (bounded) chance to land so that
+    // nothing is written into this block's shared memory after it has exited
+    for (unsigned long long j = i; j < issued; j++)
+      mbar_wait_bounded(bar0 + 8u * (uint32_t)(j % kBulkStages), (uint32_t)((j / kBulkStages) & 1ull));
+  }
+  bulk_wait_all();
+}
+
+// Per-device status word (timeouts observed by bulk_copy_kernel), allocated on first use.
+static std::mutex g_statusMutex;
+static std::map<int, unsigned int*> g_statusWord;
+
+static unsigned int* status_word(int dev) {
+  std::lock_guard<std::mutex> lk(g_statusMutex);
+  auto it = g_statusWord.find(dev);
+  if (it != g_statusWord.end()) return it->second;
+  unsigned int* p = nullptr;
+  if (cudaMalloc(&p, 256) != cudaSuccess) { cudaGetLastError(); return nullptr; }
+  if (cudaMemset(p, 0, 256) != cudaSuccess) { cudaGetLastError(); cudaFree(p); return nullptr; }
+  g_statusWord[dev] = p;
+  return p;
+}
+
+bool bulk_copy_usable(const void* in, const void* out, size_t bytes) {
+  return ((uintptr_t)in % 16 == 0) && ((uintptr_t)out % 16 == 0) && bytes >= (size_t)kBulkChunk;
+}
+
+cudaError_t launch_bulk_copy_with_status(const void* in, void* out, size_t bytes16, int numSM,
+                                         unsigned int* status, cudaStream_t stream) {
+  static std::mutex attrMutex;
+  static std::map<int, bool> attrSet;
+  int dev = 0;
+  cudaError_t e = cudaGetDevice(&dev);
+  if (e != cudaSuccess) return e;
+  const int smem = kBulkStages * (int)kBulkChunk;
+  {
+    std::lock_guard<std::mutex> lk(attrMutex);
+    if (!attrSet[dev]) {
+      e = cudaFuncSetAttribute((const void*)bulk_copy_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+      if (e != cudaSuccess) return e;
+      attrSet[dev] = true;
+    }
+  }
+  const unsigned long long nchunks = (bytes16 + kBulkChunk - 1) / kBulkChunk;
+  int grid = (int)(nchunks < (unsigned long long)numSM ? nchunks : (unsigned long long)numSM);
+  if (grid < 1) return cudaSuccess;
+  bulk_copy_kernel<<<grid, 32, smem, stream>>>((const unsigned char*)in, (unsigned char*)out,
+                                               (unsigned long long)bytes16, status);
+  return cudaGetLastError();
+}
+
+cudaError_t launch_bulk_copy(const void* in, void* out, size_t bytes16, int numSM, cudaStream_t stream) {
+  int dev = 0;
+  cudaError_t e = cudaGetDevice(&dev);
+  if (e != cudaSuccess) return e;
+  unsigned int* st = status_word(dev);
+  if (!st) return cudaErrorMemoryAllocation;
+  return launch_bulk_copy_with_status(in, out, bytes16, numSM, st, stream);
+}
+
+// Timeouts counted on the current device since the library was loaded (synchronises the device).
+int bulk_copy_timeouts() {
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess) return -1;
+  unsigned int* st = nullptr;
+  {
+    std::lock_guard<std::mutex> lk(g_statusMutex);
+    auto it = g_statusWord.find(dev);
+    if (it == g_statusWord.end()) return 0;
+    st = it->second;
+  }
+  unsigned int v = 0;
+  if (cudaMemcpy(&v, st, sizeof v, cudaMemcpyDeviceToHost) != cudaSuccess) return -1;
+  return (int)v;
+}
+
+}  // namespace cuttb

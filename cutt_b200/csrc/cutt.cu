@@ -822,6 +822,8 @@ int cutt_mg_enable_peer_access(int world) {
 
 unsigned long long cutt_c_launch_count(void) { return launch_count(); }
 
+int cutt_c_copy_timeouts(void) { return bulk_copy_timeouts(); }
+
 void cutt_c_clear_plan_cache(void) {
   std::lock_guard<std::mutex> lk(g_mutex);
   plan_cache().clear();

@@ -194,7 +194,12 @@ cudaError_t launch_copy(const void* in, void* out, size_t bytes, int numSM, cuda
   const int threads = 256;
   const bool al16 = ((uintptr_t)in % 16 == 0) && ((uintptr_t)out % 16 == 0);
   size_t body = al16 ? bytes / 16 : 0;  // 16-byte words
-  if (body) {
+  if (body && bulk_copy_usable(in, out, bytes)) {
+    // large aligned copies go through the bulk copy engine
+    cudaError_t e = launch_bulk_copy(in, out, body * 16, numSM, stream);
+    if (e != cudaSuccess) return e;
+    g_launches++;
+  } else if (body) {
     size_t want = (body + threads * 4 - 1) / (threads * 4);
     int grid = (int)(want < (size_t)numSM * 8 ? want : (size_t)numSM * 8);
     copy_kernel<uint4, 4><<<grid, threads, 0, stream>>>((const uint4*)in, (uint4*)out, body);

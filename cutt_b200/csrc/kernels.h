@@ -30,6 +30,13 @@ cudaError_t launch_tiles(const Candidate& c, int gridBlocks, const void* in, con
                          cudaStream_t stream);
 cudaError_t launch_copy(const void* in, void* out, size_t bytes, int numSM, cudaStream_t stream);
 cudaError_t launch_naive(const NaiveDesc& d, const void* in, void* out, cudaStream_t stream);
+
+// Bulk-copy-engine copy (bulk_copy.cu): both pointers 16-byte aligned, bytes16 a multiple of 16.
+bool bulk_copy_usable(const void* in, const void* out, size_t bytes);
+cudaError_t launch_bulk_copy(const void* in, void* out, size_t bytes16, int numSM, cudaStream_t stream);
+cudaError_t launch_bulk_copy_with_status(const void* in, void* out, size_t bytes16, int numSM,
+                                         unsigned int* status, cudaStream_t stream);
+int bulk_copy_timeouts();
 cudaError_t launch_rowcopy(const RowCopyDesc& d, int numSM, const void* in, void* out, cudaStream_t stream);
 
 // Number of kernel launches issued by this library since load (for benchmarks' accounting).

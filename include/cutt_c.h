@@ -62,6 +62,11 @@ int cutt_c_transpose_host(int rank, const int* dim, const int* permutation, size
 /* Kernel launches issued by the library since it was loaded. */
 unsigned long long cutt_c_launch_count(void);
 
+/* The copy kernel used for identity permutations waits on hardware barriers with a poll limit;
+ * this returns how many such waits have run out on the current device since the library was
+ * loaded (0 in a healthy run; synchronises the device; -1 on error). */
+int cutt_c_copy_timeouts(void);
+
 /* Empties the plan cache (the cuttPlanMeasure winners). */
 void cutt_c_clear_plan_cache(void);
 

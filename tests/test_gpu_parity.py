@@ -127,6 +127,37 @@ def test_row_copy_unaligned_buffers(native, oracle_mod):
     assert int(big_out[0].item()) == -1 and int(big_out[1].item()) == -1 and int(big_out[vol + 2].item()) == -1
 
 
+@pytest.mark.parametrize("dims", [[2, 5, 9, 12], [1000, 1000, 6], [4099, 33, 77], [65536, 64], [8191, 3, 5]])
+def test_identity_copy_methods(native, oracle_mod, dims):
+    """Identity permutations: the library's copy kernels (bulk-copy-engine path for large aligned
+    buffers, vector/word kernels otherwise) and the driver copy, all bit-exact."""
+    perm = list(range(len(dims)))
+    for elt in (4, 8):
+        a = raw_bits(volume(dims), elt, 13)
+        for method in (0, 1):
+            out, desc = gpu_transpose(native, dims, perm, elt, a, planner="params", method=method)
+            assert_bit_exact(out, a, desc)
+        out, desc = gpu_transpose(native, dims, perm, elt, a)
+        assert_bit_exact(out, a, desc)
+    assert native.copy_timeouts() == 0
+
+
+def test_identity_copy_unaligned(native):
+    import torch
+    n = 3_000_001
+    src = torch.arange(n + 4, dtype=torch.int32, device="cuda")
+    dst = torch.full((n + 4,), -1, dtype=torch.int32, device="cuda")
+    rc, h = native.plan_params([n // 7, 7], [0, 1], 4, method=0)
+    assert rc == 0
+    m = (n // 7) * 7
+    assert native.cuttExecute(h, src.data_ptr() + 4, dst.data_ptr() + 12) == 0
+    torch.cuda.synchronize()
+    native.cuttDestroy(h)
+    assert torch.equal(dst[3:3 + m], src[1:1 + m])
+    assert int(dst[2].item()) == -1 and int(dst[3 + m].item()) == -1
+    assert native.copy_timeouts() == 0
+
+
 def test_streams(native, oracle_mod):
     """Ten plans on ten streams, all writing the same output (src/cutt_test.cpp:371-404)."""
     import torch
