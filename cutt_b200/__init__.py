@@ -19,7 +19,7 @@ __all__ = [
     "CUTT_SUCCESS", "CUTT_INVALID_PLAN", "CUTT_INVALID_PARAMETER", "CUTT_INVALID_DEVICE",
     "CUTT_INTERNAL_ERROR", "CUTT_UNDEFINED_ERROR", "CuttError", "lib", "lib_path",
     "cuttPlan", "cuttPlanMeasure", "cuttExecute", "cuttDestroy", "plan_describe",
-    "num_candidates", "plan_candidate", "plan_params", "transpose_host", "launch_count", "copy_timeouts",
+    "num_candidates", "plan_candidate", "plan_params", "transpose_host", "launch_count", "copy_timeouts", "copy_noalloc", "copy_noalloc_timeouts",
     "clear_plan_cache", "plan_cache_save", "plan_cache_load", "plan_cache_size", "Plan",
 ]
 
@@ -84,6 +84,9 @@ def lib() -> ctypes.CDLL:
     L.cutt_c_plan_cache_load.restype = ctypes.c_int
     L.cutt_c_plan_cache_size.restype = ctypes.c_int
     L.cutt_c_copy_timeouts.restype = ctypes.c_int
+    L.cutt_c_copy_noalloc.argtypes = [vp, vp, ctypes.c_size_t, vp]
+    L.cutt_c_copy_noalloc.restype = ctypes.c_int
+    L.cutt_c_copy_noalloc_timeouts.restype = ctypes.c_int
     vpp = ctypes.POINTER(ctypes.c_void_p)
     L.cutt_mg_plan.argtypes = [up, ctypes.c_int, ip, ip, ctypes.c_size_t, vp, ctypes.c_int, ctypes.c_int]
     L.cutt_mg_plan_measure.argtypes = [up, ctypes.c_int, ip, ip, ctypes.c_size_t, vp, ctypes.c_int, ctypes.c_int, vp, vpp]
@@ -179,6 +182,15 @@ def launch_count() -> int:
 
 def copy_timeouts() -> int:
     return int(lib().cutt_c_copy_timeouts())
+
+
+def copy_noalloc(src: int, dst: int, nbytes: int, stream: int = 0) -> int:
+    """Device-to-device copy that allocates nothing (see cutt_c_copy_noalloc in include/cutt_c.h)."""
+    return lib().cutt_c_copy_noalloc(src, dst, nbytes, stream)
+
+
+def copy_noalloc_timeouts() -> int:
+    return int(lib().cutt_c_copy_noalloc_timeouts())
 
 
 def clear_plan_cache() -> None:

@@ -9,6 +9,7 @@
 // returns, so a lost completion can never hang the device.  The status word is the only global
 // memory the kernel uses besides its input and output.
 #include "kernels.h"
+#include <cstdio>
 #include <map>
 #include <mutex>
 
@@ -192,4 +193,157 @@ int bulk_copy_timeouts() {
   return (int)v;
 }
 
+// ---------------------------------------------------------------------------------------
+// Copy entry point for callers that must not allocate device memory.
+//
+// Some hosts cannot call cudaMalloc when they need a copy: they have handed the whole device
+// to a memory manager of their own, or they sit in a latency-critical loop where the
+// device-wide synchronisation an allocation implies is not acceptable.  For them the status
+// words of the copy kernel live in a fixed array inside the library image instead of an
+// allocation: kNoAllocMaxBlocks words (1 KB), present on every GPU that loads the library
+// until the process exits.
+//
+// The array below is a device symbol.  Its name is only a stand-in on the host side - handing
+// it to a kernel as if it were a pointer would make the kernel use the wrong memory - so the
+// device address is looked up once per device with cudaGetSymbolAddress (device current, return
+// code checked) and that address is what the kernel receives.
+constexpr int kNoAllocMaxBlocks = 256;                       // thread blocks one launch may use
+constexpr unsigned long long kNoAllocMaxBytes = 1ull << 40;  // largest copy accepted (1 TiB)
+
+static __device__ __align__(256) unsigned int g_noalloc_status[kNoAllocMaxBlocks];
+
+// Same pipeline as bulk_copy_kernel; block b reports in status[b] (1 = a barrier wait ran out).
+__global__ void __launch_bounds__(32, 1)
+bulk_copy_noalloc_kernel(const unsigned char* __restrict__ in, unsigned char* __restrict__ out,
+                         unsigned long long nbytes, unsigned int* __restrict__ status) {
+  extern __shared__ __align__(128) unsigned char stages[];
+  __shared__ __align__(8) unsigned long long full[kBulkStages];
+  if (threadIdx.x != 0) return;
+  const uint32_t bar0 = shared_addr(full);
+  const uint32_t st0 = shared_addr(stages);
+  for (int s = 0; s < kBulkStages; s++) mbar_init(bar0 + 8u * s, 1);
+  asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
+  asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");
+
+  const unsigned long long nchunks = (nbytes + kBulkChunk - 1) / kBulkChunk;
+  const unsigned long long first = blockIdx.x, stride = gridDim.x;
+  if (first >= nchunks) return;
+  const unsigned long long nlocal = (nchunks - first + stride - 1) / stride;
+  unsigned long long issued = 0, i = 0;
+  bool failed = false;
+  while (issued < nlocal && issued < (unsigned long long)kBulkStages) {
+    const unsigned long long off = (first + issued * stride) * kBulkChunk;
+    const uint32_t bytes = nbytes - off < kBulkChunk ? (uint32_t)(nbytes - off) : kBulkChunk;
+    const uint32_t s = (uint32_t)(issued % kBulkStages);
+    mbar_expect_tx(bar0 + 8u * s, bytes);
+    bulk_g2s(st0 + s * kBulkChunk, in + off, bytes, bar0 + 8u * s);
+    issued++;
+  }
+  for (; i < nlocal; i++) {
+    const uint32_t s = (uint32_t)(i % kBulkStages);
+    if (!mbar_wait_bounded(bar0 + 8u * s, (uint32_t)((i / kBulkStages) & 1ull))) { failed = true; break; }
+    const unsigned long long off = (first + i * stride) * kBulkChunk;
+    const uint32_t bytes = nbytes - off < kBulkChunk ? (uint32_t)(nbytes - off) : kBulkChunk;
+    bulk_s2g(out + off, st0 + s * kBulkChunk, bytes);
+    bulk_commit();
+    if (issued < nlocal) {
+      bulk_wait_read_all();
+      const unsigned long long noff = (first + issued * stride) * kBulkChunk;
+      const uint32_t nb = nbytes - noff < kBulkChunk ? (uint32_t)(nbytes - noff) : kBulkChunk;
+      mbar_expect_tx(bar0 + 8u * s, nb);
+      bulk_g2s(st0 + s * kBulkChunk, in + noff, nb, bar0 + 8u * s);
+      issued++;
+    }
+  }
+  if (failed) {
+    status[blockIdx.x] = 1u;
+    for (unsigned long long j = i; j < issued; j++)
+      mbar_wait_bounded(bar0 + 8u * (uint32_t)(j % kBulkStages), (uint32_t)((j / kBulkStages) & 1ull));
+  }
+  bulk_wait_all();
+}
+
+struct NoAllocDevice {
+  unsigned int* status = nullptr;  // device address of g_noalloc_status on this device
+  int numSM = 0;
+};
+static std::mutex g_noallocMutex;
+static std::map<int, NoAllocDevice> g_noallocDevices;
+
+// One-time set-up for the current device: symbol address, SM count, shared-memory limit of the
+// kernel.  None of these allocate.
+static cudaError_t noalloc_setup(int dev, NoAllocDevice& out) {
+  std::lock_guard<std::mutex> lk(g_noallocMutex);
+  auto it = g_noallocDevices.find(dev);
+  if (it != g_noallocDevices.end()) { out = it->second; return cudaSuccess; }
+  NoAllocDevice d;
+  void* p = nullptr;
+  cudaError_t e = cudaGetSymbolAddress(&p, g_noalloc_status);
+  if (e != cudaSuccess) return e;
+  d.status = static_cast<unsigned int*>(p);
+  e = cudaDeviceGetAttribute(&d.numSM, cudaDevAttrMultiProcessorCount, dev);
+  if (e != cudaSuccess) return e;
+  e = cudaFuncSetAttribute((const void*)bulk_copy_noalloc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                           kBulkStages * (int)kBulkChunk);
+  if (e != cudaSuccess) return e;
+  g_noallocDevices[dev] = d;
+  out = d;
+  return cudaSuccess;
+}
+
 }  // namespace cuttb
+
+extern "C" {
+
+// Declared in include/cutt_c.h.  0 success, 2 invalid parameter (null or misaligned pointers, size
+// not a multiple of 16, size over the limit, more thread blocks needed than status words exist),
+// 4 a CUDA call failed.
+int cutt_c_copy_noalloc(const void* src, void* dst, size_t bytes, void* stream) {
+  using namespace cuttb;
+  if (!src || !dst || src == dst) return 2;
+  if ((uintptr_t)src % 16 || (uintptr_t)dst % 16 || bytes % 16) return 2;
+  if (bytes == 0) return 0;
+  if ((unsigned long long)bytes > kNoAllocMaxBytes) {
+    fprintf(stderr, "cutt_c_copy_noalloc: %zu bytes exceed the limit of %llu bytes per call\n", bytes, kNoAllocMaxBytes);
+    return 2;
+  }
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess) return 4;
+  NoAllocDevice d;
+  if (noalloc_setup(dev, d) != cudaSuccess) { cudaGetLastError(); return 4; }
+  const unsigned long long nchunks = ((unsigned long long)bytes + kBulkChunk - 1) / kBulkChunk;
+  const unsigned long long want = nchunks < (unsigned long long)d.numSM ? nchunks : (unsigned long long)d.numSM;
+  if (want > (unsigned long long)kNoAllocMaxBlocks) {
+    fprintf(stderr, "cutt_c_copy_noalloc: the launch needs %llu status words, the fixed array holds %d\n", want, kNoAllocMaxBlocks);
+    return 2;
+  }
+  const int grid = (int)want;
+  cudaStream_t st = (cudaStream_t)stream;
+  // the array keeps what the previous call left: this call's words start at zero
+  if (cudaMemsetAsync(d.status, 0, sizeof(unsigned int) * grid, st) != cudaSuccess) { cudaGetLastError(); return 4; }
+  bulk_copy_noalloc_kernel<<<grid, 32, kBulkStages * (int)kBulkChunk, st>>>(
+      (const unsigned char*)src, (unsigned char*)dst, (unsigned long long)bytes, d.status);
+  return cudaGetLastError() == cudaSuccess ? 0 : 4;
+}
+
+// Barrier waits that ran out during the most recent cutt_c_copy_noalloc on the current device
+// (0 in a healthy run).  Synchronises the device; -1 on error or before the first call.
+int cutt_c_copy_noalloc_timeouts(void) {
+  using namespace cuttb;
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess) return -1;
+  NoAllocDevice d;
+  {
+    std::lock_guard<std::mutex> lk(g_noallocMutex);
+    auto it = g_noallocDevices.find(dev);
+    if (it == g_noallocDevices.end()) return -1;
+    d = it->second;
+  }
+  unsigned int host[kNoAllocMaxBlocks];
+  if (cudaMemcpy(host, d.status, sizeof host, cudaMemcpyDeviceToHost) != cudaSuccess) { cudaGetLastError(); return -1; }
+  int n = 0;
+  for (int b = 0; b < kNoAllocMaxBlocks; b++) n += host[b] ? 1 : 0;
+  return n;
+}
+
+}  // extern "C"

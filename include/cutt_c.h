@@ -67,6 +67,31 @@ unsigned long long cutt_c_launch_count(void);
  * loaded (0 in a healthy run; synchronises the device; -1 on error). */
 int cutt_c_copy_timeouts(void);
 
+/*
+ * Device-to-device copy of `bytes` bytes that allocates nothing (no counterpart in the original
+ * library, whose identity case calls cudaMemcpyAsync).
+ *
+ * Meant for hosts that cannot allocate device memory at the moment they need the copy - the
+ * device's memory belongs to their own memory manager, or they run in a loop where the
+ * device-wide synchronisation of an allocation is not tolerable.  The kernel is the bulk-copy
+ * kernel used for identity permutations; the status words it needs are a fixed 1 KB array inside
+ * the library image (256 words: one per thread block, so launches of up to 256 blocks), which
+ * every GPU that loads the library holds until the process exits.
+ *
+ * Rules: src and dst are device pointers aligned to 16 bytes, bytes is a multiple of 16 and at
+ * most 2^40; anything else returns CUTT_INVALID_PARAMETER (2) with a message on stderr for the
+ * two size limits.  The first call on a device looks up the array's device address and sets the
+ * kernel's shared-memory limit; make that first call before any stream capture begins.  All
+ * calls share the one array and each call clears the words it uses, so two calls whose kernels
+ * overlap on the GPU (different streams) race on it: issue them on one stream or order them
+ * with events.  The copy is asynchronous on `stream`.
+ */
+int cutt_c_copy_noalloc(const void* src, void* dst, size_t bytes, void* stream);
+
+/* Hardware-barrier waits that ran out during the most recent cutt_c_copy_noalloc on the current
+ * device (0 in a healthy run; synchronises the device; -1 before the first call or on error). */
+int cutt_c_copy_noalloc_timeouts(void);
+
 /* Empties the plan cache (the cuttPlanMeasure winners). */
 void cutt_c_clear_plan_cache(void);
 
