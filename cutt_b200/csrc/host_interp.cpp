@@ -82,9 +82,10 @@ static int dispatch_checked(const TileDesc& D, const unsigned char* in, unsigned
 
 static int dispatch(const TileDesc& D, const unsigned char* in, unsigned char* out) {
   if (D.aof) {
-    if (D.wide || D.vblk != 1) return 4;
-#define ACASE(E, A, B) if (D.elt == E && D.in.vec == A && D.out.vec == B) { run_desc<E, A, B, 1, false, true>(D, in, out); return 0; }
-    ACASE(4, 4, 1) ACASE(4, 4, 2) ACASE(4, 4, 4) ACASE(8, 2, 1) ACASE(8, 2, 2)
+    if (D.wide || D.vblk > 2) return 4;
+#define ACASE(E, A, B, V) if (D.elt == E && D.in.vec == A && D.out.vec == B && D.vblk == V) { run_desc<E, A, B, V, false, true>(D, in, out); return 0; }
+    ACASE(4, 4, 1, 1) ACASE(4, 4, 2, 1) ACASE(4, 4, 4, 1) ACASE(8, 2, 1, 1) ACASE(8, 2, 2, 1)
+    ACASE(4, 4, 1, 2) ACASE(4, 4, 2, 2) ACASE(4, 4, 4, 2)
 #undef ACASE
     return 4;
   }

@@ -91,7 +91,13 @@ typedef void (*TilesKernel)(const TileDesc, const unsigned char*, const PeerPtrs
 static TilesKernel pick_tiles_kernel(const TileDesc& D) {
   const int elt = D.elt, win = D.in.vec, wout = D.out.vec, v = D.vblk;
   if (D.aof) {  // aligned over-fetch: 16-byte loads, no register blocking, 32-bit offsets
-    if (D.wide || v != 1) return nullptr;
+    if (D.wide || v > 2) return nullptr;
+    if (elt == 4 && win == 4 && v == 2) {  // rows 8-byte aligned: 8-byte register blocking still works
+      if (wout == 1) return permute_tiles_kernel<4, 4, 1, 2, false, true>;
+      if (wout == 2) return permute_tiles_kernel<4, 4, 2, 2, false, true>;
+      if (wout == 4) return permute_tiles_kernel<4, 4, 4, 2, false, true>;
+    }
+    if (v != 1) return nullptr;
     if (elt == 4 && win == 4) {
       if (wout == 1) return permute_tiles_kernel<4, 4, 1, 1, false, true>;
       if (wout == 2) return permute_tiles_kernel<4, 4, 2, 1, false, true>;

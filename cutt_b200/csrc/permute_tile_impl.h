@@ -240,7 +240,7 @@ CUTT_HD void tile_load_aof(const TileDesc& D, const TileCtx& c, const Tables<WID
 // base + row offset + position offset + ((A + row residue + position residue) mod VE) * ELT,
 // where A is the misalignment of the tile origin and the residues travel in the low two bits
 // of the offsets.
-template <int ELT, int W, bool WIDE, bool PARTIAL>
+template <int ELT, int W, int V, bool WIDE, bool PARTIAL>
 CUTT_HD void tile_store_aof(const TileDesc& D, const TileCtx& c, const Tables<WIDE>& T,
                             sptr_t sbuf, const unsigned char* gin, unsigned char* gout, uint32_t tid) {
   typedef typename RowEntSel<WIDE>::type Ent;
@@ -253,6 +253,7 @@ CUTT_HD void tile_store_aof(const TileDesc& D, const TileCtx& c, const Tables<WI
   const uint32_t valid = PARTIAL ? run_valid(S, c) : S.run;
   const uint32_t qstep = S.tq * W;
   const uint32_t A = (uint32_t)((((uintptr_t)gin / ELT) + (uint64_t)c.inOff) & (VE - 1));
+  const int64_t vstepB = D.vstep * ELT;
   unsigned char* gbase = gout + c.outOff * ELT;
   const bool single = S.nRowDims <= 1;
   const RowDim& R = S.rowDim[0];
@@ -287,11 +288,24 @@ CUTT_HD void tile_store_aof(const TileDesc& D, const TileCtx& c, const Tables<WI
         rres = e.soffB & 3u;
         g = gq + (WIDE ? (int64_t)e.goff * ELT : (int64_t)((uint64_t)(uint32_t)e.goff * ELT));
       }
-      uint32_t y[W * EW];
+      // V consecutive elements along dimension 0 stay one aligned shared vector because every
+      // displacement is a multiple of V in this mode (the planner guarantees it)
+      uint32_t x[W][V * EW];
 #pragma unroll
       for (int i = 0; i < W; i++)
-        lds<ELT>(&y[i * EW], sbuf + soff + so[i] + ((qr[i] + rres) & (VE - 1)) * ELT);
-      stg<ELT * W>(g, y);
+        lds<ELT * V>(x[i], sbuf + soff + so[i] + ((qr[i] + rres) & (VE - 1)) * ELT);
+      unsigned char* gg = g;
+#pragma unroll
+      for (int j = 0; j < V; j++) {
+        uint32_t y[W * EW];
+#pragma unroll
+        for (int i = 0; i < W; i++) {
+#pragma unroll
+          for (int w = 0; w < EW; w++) y[i * EW + w] = x[i][j * EW + w];
+        }
+        stg<ELT * W>(gg, y);
+        gg += vstepB;
+      }
       if (single) g += gstepB;
     }
   }
@@ -388,8 +402,8 @@ template <int ELT, int W, int V, bool WIDE, bool AOF>
 CUTT_HD void tile_store(const TileDesc& D, const TileCtx& c, const Tables<WIDE>& T,
                         sptr_t sbuf, const unsigned char* gin, unsigned char* gout, uint32_t tid) {
   if (AOF) {
-    if (c.partial) tile_store_aof<ELT, W, WIDE, true>(D, c, T, sbuf, gin, gout, tid);
-    else tile_store_aof<ELT, W, WIDE, false>(D, c, T, sbuf, gin, gout, tid);
+    if (c.partial) tile_store_aof<ELT, W, V, WIDE, true>(D, c, T, sbuf, gin, gout, tid);
+    else tile_store_aof<ELT, W, V, WIDE, false>(D, c, T, sbuf, gin, gout, tid);
   } else {
     if (c.partial) tile_store_impl<ELT, W, V, WIDE, true>(D, c, T, sbuf, gout, tid);
     else tile_store_impl<ELT, W, V, WIDE, false>(D, c, T, sbuf, gout, tid);

@@ -337,7 +337,15 @@ bool build_tile(const Problem& P, const TileParams& tp, const DeviceInfo& dev, C
   if (tp.allowAof && !wide && win < VE && inRunLast >= 0 && P.is[0] == 1 && tp.maxVecBytes >= 16) {
     int64_t run = 1;
     for (int j = 0; j < r; j++) if (inRun[j]) run *= t[j];
-    if (run >= 2 * (int64_t)VE) { aof = true; win = VE; V = 1; }
+    if (run >= 2 * (int64_t)VE) {
+      // rows keep their alignment to the widest legal plain vector (winOrig elements), so every
+      // displacement is a multiple of it and register blocking up to that width stays possible
+      const uint32_t winOrig = win;
+      aof = true;
+      win = VE;
+      while (V > winOrig) V /= 2;
+      if (V < 1) V = 1;
+    }
   }
   D.aof = aof ? 1 : 0;
   D.inElems = P.inElems;
