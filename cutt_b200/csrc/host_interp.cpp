@@ -232,7 +232,7 @@ int cutt_hostcheck_run_chunked(int rank, const int* dim, const int* perm, int el
       // what the library does at execute time: pointers that are not aligned for the plan's
       // vector widths take the element-wise variant of the same tile
       const TileDesc& D = c.desc;
-      const bool inOk = D.aof ? true : ((uintptr_t)pin % (D.in.vec * D.elt) == 0);
+      const bool inOk = D.aof ? ((uintptr_t)pin % (D.vblk * D.elt) == 0) : ((uintptr_t)pin % (D.in.vec * D.elt) == 0);
       const bool outOk = (uintptr_t)pout % (D.out.vec * D.elt) == 0;
       if (!inOk || !outOk) {
         TileParams tp = c.params;

@@ -160,8 +160,9 @@ int tiles_blocks_per_sm(const Candidate& c) {
 
 bool tiles_pointers_aligned(const Candidate& c, const void* in, const void* out) {
   const TileDesc& D = c.desc;
-  // aligned over-fetch reads whatever alignment the input has
-  const bool inOk = D.aof ? ((uintptr_t)in % D.elt == 0) : ((uintptr_t)in % (D.in.vec * D.elt) == 0);
+  // aligned over-fetch reads whatever alignment the input has, but register blocking of width V on
+  // the store side relies on every row displacement being a multiple of V elements
+  const bool inOk = D.aof ? ((uintptr_t)in % (D.vblk * D.elt) == 0) : ((uintptr_t)in % (D.in.vec * D.elt) == 0);
   return inOk && ((uintptr_t)out % (D.out.vec * D.elt) == 0);
 }
 
