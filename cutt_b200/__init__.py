@@ -66,6 +66,8 @@ def lib() -> ctypes.CDLL:
     vp = ctypes.c_void_p
     L.cutt_c_plan.argtypes = [up, ctypes.c_int, ip, ip, ctypes.c_size_t, vp]
     L.cutt_c_plan_measure.argtypes = [up, ctypes.c_int, ip, ip, ctypes.c_size_t, vp, vp, vp]
+    L.cutt_c_plan_ext.argtypes = [up, ctypes.c_int, ip, ip, ctypes.c_size_t, vp]
+    L.cutt_c_plan_measure_ext.argtypes = [up, ctypes.c_int, ip, ip, ctypes.c_size_t, vp, vp, vp]
     L.cutt_c_execute.argtypes = [ctypes.c_uint, vp, vp]
     L.cutt_c_destroy.argtypes = [ctypes.c_uint]
     L.cutt_c_plan_describe.argtypes = [ctypes.c_uint, ctypes.c_char_p, ctypes.c_size_t]
@@ -102,6 +104,7 @@ def lib() -> ctypes.CDLL:
                  "cutt_mg_ipc_open", "cutt_mg_ipc_close", "cutt_mg_enable_peer_access"):
         getattr(L, name).restype = ctypes.c_int
     for name in ("cutt_c_plan", "cutt_c_plan_measure", "cutt_c_execute", "cutt_c_destroy",
+                 "cutt_c_plan_ext", "cutt_c_plan_measure_ext",
                  "cutt_c_plan_describe", "cutt_c_num_candidates", "cutt_c_plan_candidate",
                  "cutt_c_plan_params", "cutt_c_transpose_host"):
         getattr(L, name).restype = ctypes.c_int
@@ -142,6 +145,22 @@ def cuttDestroy(handle: int) -> int:
 
 
 # --- additions without a counterpart in the original library ---
+
+def plan_ext(dim: Sequence[int], permutation: Sequence[int], sizeofType: int, stream: int = 0):
+    """cuttPlan for element sizes 1, 2, 4, 8 or 16 bytes. Returns (result, handle)."""
+    h = ctypes.c_uint(0)
+    rc = lib().cutt_c_plan_ext(ctypes.byref(h), len(dim), _iarr(dim), _iarr(permutation), sizeofType, stream)
+    return rc, h.value
+
+
+def plan_measure_ext(dim: Sequence[int], permutation: Sequence[int], sizeofType: int, stream: int,
+                     idata: int, odata: int):
+    """cuttPlanMeasure for element sizes 1, 2, 4, 8 or 16 bytes. Overwrites odata."""
+    h = ctypes.c_uint(0)
+    rc = lib().cutt_c_plan_measure_ext(ctypes.byref(h), len(dim), _iarr(dim), _iarr(permutation), sizeofType,
+                                       stream, idata, odata)
+    return rc, h.value
+
 
 def plan_describe(handle: int) -> str:
     buf = ctypes.create_string_buffer(4096)

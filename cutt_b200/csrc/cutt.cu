@@ -26,6 +26,7 @@
 
 #include "kernels.h"
 #include "planner.h"
+#include "small_elt_impl.h"
 
 using namespace cuttb;
 
@@ -51,6 +52,9 @@ struct Plan {
   int mgMe = 0;
   int mgMode = -1;
   long long mgLocalVolume = 0;
+  // plans of the extension entry points (element sizes 1, 2, 16)
+  int extBytes = 0;        // the caller's element size; 0 for ordinary plans
+  SmallDesc small;         // kMethodSmall
 };
 
 struct CachedChoice {
@@ -137,8 +141,8 @@ bool device_info(int& dev, DeviceInfo& info) {
 }
 
 // src/cutt.cpp:59-82
-cuttResult check_input(int rank, const int* dim, const int* perm, size_t elt) {
-  if (elt != 4 && elt != 8) return CUTT_INVALID_PARAMETER;
+cuttResult check_input(int rank, const int* dim, const int* perm, size_t elt, bool ext = false) {
+  if (elt != 4 && elt != 8 && !(ext && (elt == 1 || elt == 2 || elt == 16))) return CUTT_INVALID_PARAMETER;
   if (rank <= 1) return CUTT_INVALID_PARAMETER;
   if (!dim || !perm) return CUTT_INVALID_PARAMETER;
   for (int i = 0; i < rank; i++)
@@ -198,7 +202,15 @@ cudaError_t run_plan(const Plan& p, const void* in, void* out, cudaStream_t stre
     if (p.haveFallback) return launch_tiles(p.fallback, p.fallbackGrid, in, pp, stream);
     return cudaErrorInvalidValue;
   }
+  if (p.extBytes && p.method != kMethodMemcpy && p.method != kMethodSmall &&
+      ((uintptr_t)in % p.elt || (uintptr_t)out % p.elt)) {
+    // a re-stated problem moves 4- or 8-byte units; buffers aligned for the caller's smaller
+    // type only are permuted element by element
+    return launch_naive(p.naive, in, out, stream);
+  }
   switch (p.method) {
+    case kMethodSmall:
+      return launch_small(p.small, in, out, stream);
     case kMethodMemcpy:
       return cudaMemcpyAsync(out, in, p.bytes, cudaMemcpyDeviceToDevice, stream);
     case kMethodCopy:
@@ -218,6 +230,20 @@ cudaError_t run_plan(const Plan& p, const void* in, void* out, cudaStream_t stre
     }
   }
   return cudaErrorInvalidValue;
+}
+
+// Label of a plan that is not described by a tiled candidate.
+std::string plain_label(const Plan& p) {
+  if (p.method == kMethodNaive) return "naive";
+  if (p.method == kMethodCopy) return "copy";
+  if (p.method == kMethodMemcpy) return "memcpy";
+  if (p.method == kMethodSmall) {
+    char buf[96];
+    snprintf(buf, sizeof buf, "small t=%ux%u%s tiles=%u", 1u << p.small.logTA, 1u << p.small.logTB,
+             p.small.storeAlongB ? "" : " rows", p.small.numTiles);
+    return buf;
+  }
+  return "?";
 }
 
 // Completes a plan around a chosen candidate (grid sizes, unaligned-pointer fallback).
@@ -267,13 +293,18 @@ struct PlanRequest {
   int index = 0;
   int method = kMethodTiles;
   TileParams params;
+  bool ext = false;            // extension entry point: element sizes 1, 2 and 16 as well
 };
 
 cuttResult make_plan(cuttHandle* handle, int rank, const int* dim, const int* perm, size_t elt,
                      cudaStream_t stream, const PlanRequest& req) {
-  cuttResult chk = check_input(rank, dim, perm, elt);
+  cuttResult chk = check_input(rank, dim, perm, elt, req.ext);
   if (chk != CUTT_SUCCESS) return chk;
   if (!handle) return CUTT_INVALID_PARAMETER;
+  const bool extSize = req.ext && elt != 4 && elt != 8;
+  if (extSize && (rank > 31 || req.world > 0 || req.chunkLast > 0 ||
+                  (req.mode != kByModel && req.mode != kByMeasure)))
+    return CUTT_INVALID_PARAMETER;
   if (req.mode == kByMeasure && req.idata == req.odata) return CUTT_INVALID_PARAMETER;
 
   std::unique_lock<std::mutex> lk(g_mutex);
@@ -312,6 +343,25 @@ cuttResult make_plan(cuttHandle* handle, int rank, const int* dim, const int* pe
     p->bytes = (size_t)p->prob.volume * elt;
     p->mgMode = 2;  // no element-wise fallback: the output is a strided part of a larger tensor
     key += "/chunk" + std::to_string(req.chunkLast);
+  } else if (extSize) {
+    size_t vol = 1;
+    for (int i = 0; i < rank; i++) vol *= (size_t)dim[i];
+    p->bytes = vol * elt;
+    p->extBytes = (int)elt;
+    // the element-wise kernel works on the caller's element type (16 bytes: two 8-byte words)
+    if (elt == 16) {
+      int d2[32], p2[32];
+      d2[0] = 2; p2[0] = 0;
+      for (int i = 0; i < rank; i++) { d2[i + 1] = dim[i]; p2[i + 1] = perm[i] + 1; }
+      p->elt = 8;
+      fill_naive(*p, rank + 1, d2, p2);
+    } else {
+      p->elt = (int)elt;
+      fill_naive(*p, rank, dim, perm);
+    }
+    canon = problem_from_cutt_ext(rank, dim, perm, (int)elt, p->prob);
+    if (canon) p->elt = p->prob.elt;
+    key += "/ext";
   } else {
     size_t vol = 1;
     for (int i = 0; i < rank; i++) vol *= (size_t)dim[i];
@@ -329,6 +379,12 @@ cuttResult make_plan(cuttHandle* handle, int rank, const int* dim, const int* pe
 
   if (!canon) {
     p->method = kMethodNaive;  // fused rank beyond the tiled kernel's limit
+    ok = true;
+  } else if (extSize && p->prob.identity) {
+    p->method = kMethodMemcpy;
+    ok = true;
+  } else if (extSize && p->prob.elt < 4) {
+    p->method = build_small(p->prob, p->small) ? kMethodSmall : kMethodNaive;
     ok = true;
   } else if (p->mgMode == 1 && req.mode != kByModel && req.mode != kByMeasure && req.mode != kByIndex) {
     return CUTT_INVALID_PARAMETER;
@@ -436,7 +492,7 @@ cuttResult make_plan(cuttHandle* handle, int rank, const int* dim, const int* pe
     Candidate shown = p->cand;
     shown.method = p->method;
     if (p->method != kMethodTiles && p->method != kMethodRowCopy)
-      shown.label = p->method == kMethodNaive ? "naive" : (p->method == kMethodCopy ? "copy" : "memcpy");
+      shown.label = plain_label(*p);
     fprintf(stderr, "[cutt] plan %u (%s): %s\n", *handle, p->note.c_str(),
             canon ? describe(p->prob, shown).c_str() : "naive (rank too high after fusion)");
   }
@@ -483,6 +539,10 @@ cuttResult cuttExecute(cuttHandle handle, void* idata, void* odata) {
   }
   if (idata == odata) return CUTT_INVALID_PARAMETER;
   if (p->mgMode == 1) return CUTT_INVALID_PARAMETER;  // needs the peers' slabs: cutt_mg_execute
+  if (p->extBytes) {  // buffers must be aligned for the caller's element type (at most 8 bytes)
+    const uintptr_t need = p->extBytes > 8 ? 8 : p->extBytes;
+    if ((uintptr_t)idata % need || (uintptr_t)odata % need) return CUTT_INVALID_PARAMETER;
+  }
   int dev = 0;
   if (cudaGetDevice(&dev) != cudaSuccess) return CUTT_INTERNAL_ERROR;
   if (dev != p->device) return CUTT_INVALID_DEVICE;
@@ -509,6 +569,23 @@ int cutt_c_plan_measure(unsigned int* handle, int rank, const int* dim, const in
   return (int)make_plan(handle, rank, dim, permutation, sizeofType, (cudaStream_t)stream, req);
 }
 
+int cutt_c_plan_ext(unsigned int* handle, int rank, const int* dim, const int* permutation,
+                    size_t sizeofType, void* stream) {
+  PlanRequest req;
+  req.ext = true;
+  return (int)make_plan(handle, rank, dim, permutation, sizeofType, (cudaStream_t)stream, req);
+}
+
+int cutt_c_plan_measure_ext(unsigned int* handle, int rank, const int* dim, const int* permutation,
+                            size_t sizeofType, void* stream, void* idata, void* odata) {
+  PlanRequest req;
+  req.ext = true;
+  req.mode = kByMeasure;
+  req.idata = idata;
+  req.odata = odata;
+  return (int)make_plan(handle, rank, dim, permutation, sizeofType, (cudaStream_t)stream, req);
+}
+
 int cutt_c_execute(unsigned int handle, void* idata, void* odata) {
   return (int)cuttExecute(handle, idata, odata);
 }
@@ -523,9 +600,7 @@ int cutt_c_plan_describe(unsigned int handle, char* buf, size_t len) {
   const Plan& p = *it->second;
   Candidate shown = p.cand;
   shown.method = p.method;
-  if (p.method == kMethodNaive) shown.label = "naive";
-  else if (p.method == kMethodCopy) shown.label = "copy";
-  else if (p.method == kMethodMemcpy) shown.label = "memcpy";
+  if (p.method != kMethodTiles && p.method != kMethodRowCopy) shown.label = plain_label(p);
   snprintf(buf, len, "%s", describe(p.prob, shown).c_str());
   return CUTT_SUCCESS;
 }

@@ -9,6 +9,7 @@
 #define CUTT_HOSTCHECK_BOUNDS 1
 #include "permute_tile_impl.h"
 #include "planner.h"
+#include "small_elt_impl.h"
 
 using namespace cuttb;
 
@@ -118,6 +119,25 @@ static int run_rowcopy(const RowCopyDesc& R, const unsigned char* in, unsigned c
   return 0;
 }
 
+// Small-element method: every tile, every thread, both phases, all accesses range-checked.
+static int run_small(const SmallDesc& S, const unsigned char* in, unsigned char* out) {
+  std::vector<unsigned char> smem(S.smemBytes);
+  small_violations() = 0;
+  for (uint32_t tile = 0; tile < S.numTiles; tile++) {
+    const SmallOrigin o = small_origin(S, tile);
+    for (uint32_t tid = 0; tid < (uint32_t)kSmallThreads; tid++) {
+      if (S.elt == 1) small_load<1>(S, o, in, smem.data(), tid, kSmallThreads);
+      else small_load<2>(S, o, in, smem.data(), tid, kSmallThreads);
+    }
+    for (uint32_t tid = 0; tid < (uint32_t)kSmallThreads; tid++) {
+      if (S.elt == 1) small_store<1>(S, o, out, smem.data(), tid, kSmallThreads);
+      else small_store<2>(S, o, out, smem.data(), tid, kSmallThreads);
+    }
+  }
+  if (small_violations()) { fprintf(stderr, "hostcheck: %lld bad small-element accesses\n", small_violations()); return 9; }
+  return 0;
+}
+
 static DeviceInfo g_dev;
 
 extern "C" {
@@ -145,6 +165,41 @@ int cutt_hostcheck_run(int rank, const int* dim, const int* perm, int elt, int i
   }
   if (c.method == kMethodRowCopy) return run_rowcopy(c.rc, (const unsigned char*)in, (unsigned char*)out, (size_t)P.volume * elt);
   return dispatch_checked(c.desc, (const unsigned char*)in, (unsigned char*)out, (size_t)P.volume * elt);
+}
+
+// Extension element sizes (1, 2, 16 bytes besides 4 and 8): the problem as the library re-states
+// it, then candidate `index` of the planner or the small-element method.  `label` receives
+// "memcpy", "small ..." or the candidate's description.  Returns 0 on success, 3 when `index`
+// is past the end of the candidate list.
+int cutt_hostcheck_run_ext(int rank, const int* dim, const int* perm, int eltBytes, int index,
+                           const void* in, void* out, char* label, int labelLen) {
+  Problem P;
+  if (!problem_from_cutt_ext(rank, dim, perm, eltBytes, P)) return 2;
+  size_t bytes = (size_t)eltBytes;
+  for (int i = 0; i < rank; i++) bytes *= (size_t)dim[i];
+  if ((size_t)P.volume * P.elt != bytes) return 6;
+  if (P.identity) {
+    if (index > 0) return 3;
+    if (label && labelLen > 0) snprintf(label, labelLen, "memcpy");
+    memcpy(out, in, bytes);
+    return 0;
+  }
+  if (P.elt < 4) {
+    if (index > 0) return 3;
+    SmallDesc S;
+    if (!build_small(P, S)) return 5;
+    if (label && labelLen > 0)
+      snprintf(label, labelLen, "small t=%ux%u%s tiles=%u", 1u << S.logTA, 1u << S.logTB,
+               S.storeAlongB ? "" : " rows", S.numTiles);
+    return run_small(S, (const unsigned char*)in, (unsigned char*)out);
+  }
+  std::vector<Candidate> cands = enumerate_candidates(P, g_dev);
+  if (index < 0 || index >= (int)cands.size()) return 3;
+  const Candidate& c = cands[index];
+  if (label && labelLen > 0) snprintf(label, labelLen, "%s", describe(P, c).c_str());
+  if (c.method == kMethodCopy || c.method == kMethodMemcpy) { memcpy(out, in, bytes); return 0; }
+  if (c.method == kMethodRowCopy) return run_rowcopy(c.rc, (const unsigned char*)in, (unsigned char*)out, bytes);
+  return dispatch_checked(c.desc, (const unsigned char*)in, (unsigned char*)out, bytes);
 }
 
 // Same, for an explicit parameter choice (used to force odd tile shapes in tests).

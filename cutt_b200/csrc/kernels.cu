@@ -20,6 +20,7 @@ namespace cuttb {
 
 static std::atomic<unsigned long long> g_launches{0};
 unsigned long long launch_count() { return g_launches.load(); }
+void count_launch() { g_launches++; }
 
 __device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;\n" ::: "memory"); }
 template <int N>
@@ -277,6 +278,8 @@ cudaError_t launch_naive(const NaiveDesc& d, const void* in, void* out, cudaStre
   int grid = (int)(want < 148ull * 16 ? want : 148ull * 16);
   if (grid < 1) grid = 1;
   if (d.elt == 4) naive_kernel<uint32_t><<<grid, threads, 0, stream>>>(d, (const uint32_t*)in, (uint32_t*)out);
+  else if (d.elt == 2) naive_kernel<uint16_t><<<grid, threads, 0, stream>>>(d, (const uint16_t*)in, (uint16_t*)out);
+  else if (d.elt == 1) naive_kernel<uint8_t><<<grid, threads, 0, stream>>>(d, (const uint8_t*)in, (uint8_t*)out);
   else naive_kernel<unsigned long long><<<grid, threads, 0, stream>>>(d, (const unsigned long long*)in, (unsigned long long*)out);
   g_launches++;
   return cudaGetLastError();

@@ -39,7 +39,12 @@ cudaError_t launch_bulk_copy_with_status(const void* in, void* out, size_t bytes
 int bulk_copy_timeouts();
 cudaError_t launch_rowcopy(const RowCopyDesc& d, int numSM, const void* in, void* out, cudaStream_t stream);
 
+// Permutation of 1- or 2-byte elements, one tile per block (small_elt.cu).
+struct SmallDesc;
+cudaError_t launch_small(const SmallDesc& d, const void* in, void* out, cudaStream_t stream);
+
 // Number of kernel launches issued by this library since load (for benchmarks' accounting).
 unsigned long long launch_count();
+void count_launch();
 
 }  // namespace cuttb

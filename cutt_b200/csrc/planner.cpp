@@ -62,6 +62,34 @@ bool problem_from_cutt(int rank, const int* dim, const int* perm, int elt, Probl
   return canonicalize(rank, d.data(), is.data(), os.data(), elt, -1, P);
 }
 
+bool problem_from_cutt_ext(int rank, const int* dim, const int* perm, int eltBytes, Problem& P) {
+  if (eltBytes == 4 || eltBytes == 8) return problem_from_cutt(rank, dim, perm, eltBytes, P);
+  if (eltBytes != 1 && eltBytes != 2 && eltBytes != 16) return false;
+  std::vector<int64_t> d(rank + 1), is(rank + 1), os(rank + 1);
+  int64_t acc = 1;
+  for (int i = 0; i < rank; i++) { d[i + 1] = dim[i]; is[i + 1] = acc; acc *= dim[i]; }
+  acc = 1;
+  for (int k = 0; k < rank; k++) { os[perm[k] + 1] = acc; acc *= dim[perm[k]]; }
+  if (eltBytes == 16) {
+    // an unpermuted innermost dimension of two 8-byte words
+    d[0] = 2; is[0] = 1; os[0] = 1;
+    for (int i = 1; i <= rank; i++) { is[i] *= 2; os[i] *= 2; }
+    return canonicalize(rank + 1, d.data(), is.data(), os.data(), 8, -1, P);
+  }
+  if (!canonicalize(rank, d.data() + 1, is.data() + 1, os.data() + 1, eltBytes, -1, P)) return false;
+  if (P.identity || P.is[0] != 1 || P.os[0] != 1) return true;
+  for (int unit = 8; unit >= 4; unit /= 2) {
+    const int f = unit / eltBytes;  // elements per unit
+    if (P.d[0] % f) continue;
+    // every other stride is a multiple of the leading extent, hence of f
+    Problem Q = P;
+    Q.d[0] /= f;
+    for (int j = 1; j < Q.rank; j++) { Q.is[j] /= f; Q.os[j] /= f; }
+    return canonicalize(Q.rank, Q.d, Q.is, Q.os, unit, -1, P);
+  }
+  return true;
+}
+
 bool problem_from_cutt_chunk(int rank, const int* dim, const int* perm, int elt, int chunk, Problem& P) {
   if (rank < 1 || chunk < 1 || chunk > dim[rank - 1]) return false;
   std::vector<int64_t> d(rank), is(rank), os(rank);

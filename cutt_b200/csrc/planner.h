@@ -45,6 +45,11 @@ bool canonicalize(int rank, const int64_t* d, const int64_t* is, const int64_t* 
 // cuTT convention (dim[0] fastest, outDim[i] = dim[perm[i]]) -> Problem.
 bool problem_from_cutt(int rank, const int* dim, const int* perm, int elt, Problem& P);
 
+// The same for element sizes 1, 2, 4, 8 and 16 bytes (extension entry points).  16-byte elements
+// become pairs of 8-byte words.  1- and 2-byte elements are re-stated in 8- or 4-byte units when
+// the fastest dimension stays fastest and its byte length allows; otherwise P.elt stays 1 or 2.
+bool problem_from_cutt_ext(int rank, const int* dim, const int* perm, int eltBytes, Problem& P);
+
 // A tensor sharded over `world` GPUs of one box: the input along its slowest dimension, the
 // output along ITS slowest dimension (= input dimension perm[rank-1]), both in equal parts.
 struct ShardInfo {
@@ -71,6 +76,7 @@ enum Method : int {
   kMethodTiles = 2,    // tiled permutation kernel (cp.async staged)
   kMethodNaive = 3,    // one thread per output element (fallback for rank > kMaxDims, debug)
   kMethodRowCopy = 4,  // strided copy of contiguous rows with register shifting (rowcopy_impl.h)
+  kMethodSmall = 5,    // 1- and 2-byte elements moved one by one (small_elt_impl.h)
 };
 
 struct TileParams {

@@ -1,0 +1,34 @@
+// Kernel and launcher for permutations of 1- and 2-byte elements (small_elt_impl.h).
+#include "kernels.h"
+#include "small_elt_impl.h"
+
+namespace cuttb {
+
+template <int ELT>
+__global__ void __launch_bounds__(kSmallThreads)
+small_elt_kernel(const __grid_constant__ SmallDesc D, const unsigned char* __restrict__ in,
+                 unsigned char* __restrict__ out) {
+  extern __shared__ __align__(16) unsigned char smem[];
+  const uint32_t tile = blockIdx.x;
+  if (tile >= D.numTiles) return;
+  const SmallOrigin o = small_origin(D, tile);
+  small_load<ELT>(D, o, in, smem, threadIdx.x, blockDim.x);
+  __syncthreads();
+  small_store<ELT>(D, o, out, smem, threadIdx.x, blockDim.x);
+}
+
+cudaError_t launch_small(const SmallDesc& d, const void* in, void* out, cudaStream_t stream) {
+  if (d.numTiles == 0 || d.smemBytes > 48 * 1024) return cudaErrorInvalidValue;
+  if (d.elt == 1)
+    small_elt_kernel<1><<<d.numTiles, kSmallThreads, d.smemBytes, stream>>>(
+        d, (const unsigned char*)in, (unsigned char*)out);
+  else if (d.elt == 2)
+    small_elt_kernel<2><<<d.numTiles, kSmallThreads, d.smemBytes, stream>>>(
+        d, (const unsigned char*)in, (unsigned char*)out);
+  else
+    return cudaErrorInvalidValue;
+  count_launch();
+  return cudaGetLastError();
+}
+
+}  // namespace cuttb

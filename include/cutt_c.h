@@ -24,6 +24,19 @@ int cutt_c_plan(unsigned int* handle, int rank, const int* dim, const int* permu
 int cutt_c_plan_measure(unsigned int* handle, int rank, const int* dim, const int* permutation,
                         size_t sizeofType, void* stream, void* idata, void* odata);
 
+/* Element sizes 1, 2 and 16 bytes besides 4 and 8.  No counterpart in the original library, which
+ * rejects them (src/cutt.cpp:62); every other rule of cuttPlan / cuttPlanMeasure applies
+ * unchanged.  The handles are executed and destroyed with cutt_c_execute / cutt_c_destroy (or
+ * cuttExecute / cuttDestroy).  Buffers must be aligned for the element type (16-byte elements:
+ * 8 bytes suffice); otherwise execution returns CUTT_INVALID_PARAMETER.
+ * 16-byte elements move as pairs of 8-byte words through the ordinary plans.  1- and 2-byte
+ * elements do so in 4- or 8-byte units when the fastest dimension stays fastest and its byte
+ * length is a multiple of 4; all other cases use a separate element-wise tiled kernel. */
+int cutt_c_plan_ext(unsigned int* handle, int rank, const int* dim, const int* permutation,
+                    size_t sizeofType, void* stream);
+int cutt_c_plan_measure_ext(unsigned int* handle, int rank, const int* dim, const int* permutation,
+                            size_t sizeofType, void* stream, void* idata, void* odata);
+
 /* cuttExecute (src/cutt.h:101, src/cutt.cpp:296-310). */
 int cutt_c_execute(unsigned int handle, void* idata, void* odata);
 

@@ -83,6 +83,17 @@ def test_validation_codes_without_device(native):
     assert native.lib().cutt_c_version().startswith(b"cutt-b200")
 
 
+def test_extension_entry_validation_without_device(native):
+    """cutt_c_plan_ext accepts 1, 2, 4, 8, 16 bytes and applies the original's other rules."""
+    bad = native.CUTT_INVALID_PARAMETER
+    for elt in (0, 3, 5, 12, 32):
+        assert native.plan_ext([4, 4], [1, 0], elt, 0)[0] == bad
+    for elt in (1, 2, 4, 8, 16):
+        assert native.plan_ext([4], [0], elt, 0)[0] == bad
+        assert native.plan_ext([4, 1], [1, 0], elt, 0)[0] == bad
+        assert native.plan_ext([4, 4, 4], [0, 1, 1], elt, 0)[0] == bad
+
+
 def test_missing_library_fails_loudly(monkeypatch, native):
     import cutt_b200
     monkeypatch.setattr(cutt_b200, "_lib", None)

@@ -35,6 +35,46 @@ def _iarr(v):
     return (ctypes.c_int * len(v))(*v)
 
 
+def _ext_expected(oracle_mod, dims, perm, elt, raw):
+    """Permuted bytes of a tensor of 1-, 2- or 16-byte elements (the oracle handles 16 bytes as two
+    8-byte words under an unpermuted innermost dimension of extent 2)."""
+    if elt == 16:
+        return oracle_mod.transpose_blocked([2] + list(dims), [0] + [p + 1 for p in perm],
+                                            raw.view(np.uint64)).view(np.uint8)
+    return oracle_mod.transpose_numpy(dims, perm, raw.view(np.uint8 if elt == 1 else np.uint16)).view(np.uint8)
+
+
+@pytest.mark.parametrize("elt", [1, 2, 16])
+def test_extension_element_sizes(hc, oracle_mod, elt):
+    """The problems as the extension entry points re-state them, and the element-wise kernel's
+    index arithmetic, on host memory with every access range-checked."""
+    hc.cutt_hostcheck_run_ext.argtypes = [ctypes.c_int, ctypes.POINTER(ctypes.c_int), ctypes.POINTER(ctypes.c_int),
+                                          ctypes.c_int, ctypes.c_int, ctypes.c_void_p, ctypes.c_void_p,
+                                          ctypes.c_char_p, ctypes.c_int]
+    rng = random.Random(31 + elt)
+    cases = []
+    for dims in ([3, 5], [4, 6], [8, 3, 5], [2, 3, 4, 5], [7, 66, 5], [130, 70], [258, 3, 9], [5, 300, 2, 3]):
+        cases += [(dims, list(p)) for p in itertools.permutations(range(len(dims)))]
+    for rank in range(2, 10):
+        cases += [random_case(rng, rank, 60_000) for _ in range(3)]
+    labels = set()
+    for dims, perm in cases:
+        raw = np.random.default_rng(volume(dims)).integers(0, 256, volume(dims) * elt, dtype=np.uint8)
+        want = _ext_expected(oracle_mod, dims, perm, elt, raw)
+        for idx in range(2):
+            out = np.full_like(raw, 0xEE)
+            lab = ctypes.create_string_buffer(4096)
+            rc = hc.cutt_hostcheck_run_ext(len(dims), _iarr(dims), _iarr(perm), elt, idx, raw.ctypes.data,
+                                           out.ctypes.data, lab, 4096)
+            if rc == 3:
+                break
+            assert rc == 0, (rc, dims, perm, elt, idx)
+            assert np.array_equal(out, want), (dims, perm, elt, idx, lab.value.decode())
+            labels.add(lab.value.decode()[:5])
+    if elt < 4:
+        assert "small" in labels and "memcp" in labels and '{"met' in labels
+
+
 def _check_candidates(hc, oracle_mod, dims, perm, elts=(4, 8), max_cands=None, seed=0):
     for elt in elts:
         n = hc.cutt_hostcheck_num_candidates(len(dims), _iarr(dims), _iarr(perm), elt)
