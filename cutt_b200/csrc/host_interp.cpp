@@ -140,13 +140,31 @@ static int run_small(const SmallDesc& S, const unsigned char* in, unsigned char*
 
 static DeviceInfo g_dev;
 
+// Candidate list of the last problem asked for (tests run candidate 0, 1, 2, ... of one problem
+// in a row; enumerating is the expensive part).
+static const std::vector<Candidate>& candidates_of(const Problem& P) {
+  static Problem last;
+  static std::vector<Candidate> list;
+  static bool have = false;
+  bool same = have && last.rank == P.rank && last.elt == P.elt && last.peerDim == P.peerDim &&
+              last.inBase == P.inBase && last.outBase == P.outBase && last.inElems == P.inElems;
+  for (int j = 0; same && j < P.rank; j++)
+    same = last.d[j] == P.d[j] && last.is[j] == P.is[j] && last.os[j] == P.os[j];
+  if (!same) {
+    list = enumerate_candidates(P, g_dev);
+    last = P;
+    have = true;
+  }
+  return list;
+}
+
 extern "C" {
 
 // Number of candidates the planner enumerates for a cuTT-style problem (0 on invalid input).
 int cutt_hostcheck_num_candidates(int rank, const int* dim, const int* perm, int elt) {
   Problem P;
   if (!problem_from_cutt(rank, dim, perm, elt, P)) return 0;
-  return (int)enumerate_candidates(P, g_dev).size();
+  return (int)candidates_of(P).size();
 }
 
 // Executes candidate `index` on host memory.  Returns 0 on success; `label` receives the
@@ -155,7 +173,7 @@ int cutt_hostcheck_run(int rank, const int* dim, const int* perm, int elt, int i
                        const void* in, void* out, char* label, int labelLen) {
   Problem P;
   if (!problem_from_cutt(rank, dim, perm, elt, P)) return 2;
-  std::vector<Candidate> cands = enumerate_candidates(P, g_dev);
+  const std::vector<Candidate>& cands = candidates_of(P);
   if (index < 0 || index >= (int)cands.size()) return 3;
   const Candidate& c = cands[index];
   if (label && labelLen > 0) snprintf(label, labelLen, "%s", describe(P, c).c_str());
@@ -193,7 +211,7 @@ int cutt_hostcheck_run_ext(int rank, const int* dim, const int* perm, int eltByt
                S.storeAlongB ? "" : " rows", S.numTiles);
     return run_small(S, (const unsigned char*)in, (unsigned char*)out);
   }
-  std::vector<Candidate> cands = enumerate_candidates(P, g_dev);
+  const std::vector<Candidate>& cands = candidates_of(P);
   if (index < 0 || index >= (int)cands.size()) return 3;
   const Candidate& c = cands[index];
   if (label && labelLen > 0) snprintf(label, labelLen, "%s", describe(P, c).c_str());
@@ -229,7 +247,7 @@ int cutt_hostcheck_run_sharded(int rank, const int* dim, const int* perm, int el
   Problem P;
   ShardInfo info;
   if (!problem_from_cutt_sharded(rank, dim, perm, elt, world, me, P, info)) return -2;
-  std::vector<Candidate> cands = enumerate_candidates(P, g_dev);
+  const std::vector<Candidate>& cands = candidates_of(P);
   if (cands.empty()) return -3;
   if (index < 0) index = 0;
   index %= (int)cands.size();
@@ -280,7 +298,7 @@ int cutt_hostcheck_run_chunked(int rank, const int* dim, const int* perm, int el
     if (!problem_from_cutt_chunk(rank, dim, perm, elt, ext, P)) return 2;
     const unsigned char* pin = (const unsigned char*)in + (size_t)c0 * isLast * elt;
     unsigned char* pout = (unsigned char*)out + (size_t)c0 * osLast * elt;
-    std::vector<Candidate> cands = enumerate_candidates(P, g_dev);
+    const std::vector<Candidate>& cands = candidates_of(P);
     if (cands.empty()) return 3;
     Candidate c = cands[(size_t)index % cands.size()];
     if (c.method == kMethodTiles) {

@@ -661,12 +661,22 @@ static double predicted_efficiency(const float* f) {
 double model_cost(const Problem& P, const Candidate& c, const DeviceInfo& dev) {
   static_assert(cost_model::kFeatures == kNumFeatures, "regenerate cost_model_data.h");
   const double bytes = 2.0 * (double)P.volume * P.elt;
-  // tensors far smaller than the training shapes are launch/latency bound: the fitted model
-  // has not seen them, use the closed form there
-  if (bytes < 64e6) return analytic_cost(P, c, dev);
   double eff = predicted_efficiency(c.feat);
   if (eff < 0.02) eff = 0.02;
-  return bytes / (cost_model::kRefGBs * 1e9 * eff) + 4e-6;
+  const double stream = bytes / (cost_model::kRefGBs * 1e9 * eff);
+  if (bytes < 64e6) {
+    // Tensors far smaller than the training shapes are latency bound: what counts is how many
+    // tiles are in flight at once and how long one block needs for its tile.  Constants fitted
+    // to B200 timings of every candidate of 20 shapes between 0.3 and 48 MB (launch floor
+    // 4.5 us; 0.5 us per tile plus 80 MB/s per thread; 0.6 us for the two-stage prologue).
+    const TileDesc& D = c.desc;
+    const double conc = std::min((double)D.numTiles, (double)dev.numSM * std::max(1, c.blocksPerSM));
+    const double waves = std::ceil((double)D.numTiles / conc);
+    const double tileBytes = bytes / (double)D.numTiles;   // read + written
+    const double perTile = 0.5e-6 + tileBytes / ((double)D.nthreads * 80e6) + (D.stages >= 2 ? 0.6e-6 : 0.0);
+    return 4.5e-6 + std::max(stream, waves * perTile);
+  }
+  return stream + 4e-6;
 }
 
 bool build_rowcopy(const Problem& P, const DeviceInfo& dev, Candidate& out) {
