@@ -239,8 +239,9 @@ std::string plain_label(const Plan& p) {
   if (p.method == kMethodMemcpy) return "memcpy";
   if (p.method == kMethodSmall) {
     char buf[96];
-    snprintf(buf, sizeof buf, "small t=%ux%u%s tiles=%u", 1u << p.small.logTA, 1u << p.small.logTB,
-             p.small.storeAlongB ? "" : " rows", p.small.numTiles);
+    snprintf(buf, sizeof buf, "small t=%ux%u%s%s%s tiles=%u", 1u << p.small.logTA, 1u << p.small.logTB,
+             p.small.storeAlongB ? "" : " rows", p.small.packLoad ? " ld32" : "",
+             p.small.packStore ? " st32" : "", p.small.numTiles);
     return buf;
   }
   return "?";

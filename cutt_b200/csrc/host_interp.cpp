@@ -120,18 +120,22 @@ static int run_rowcopy(const RowCopyDesc& R, const unsigned char* in, unsigned c
 }
 
 // Small-element method: every tile, every thread, both phases, all accesses range-checked.
-static int run_small(const SmallDesc& S, const unsigned char* in, unsigned char* out) {
-  std::vector<unsigned char> smem(S.smemBytes);
+static int run_small(const SmallDesc& plan, const unsigned char* in, unsigned char* out) {
+  SmallDesc S = plan;   // as the launcher: 32-bit accesses only on 4-byte aligned buffers
+  if ((uintptr_t)in % 4) S.packLoad = 0;
+  if ((uintptr_t)out % 4) S.packStore = 0;
+  std::vector<uint32_t> smemWords(S.smemBytes / 4 + 1);
+  unsigned char* smemBase = reinterpret_cast<unsigned char*>(smemWords.data());
   small_violations() = 0;
   for (uint32_t tile = 0; tile < S.numTiles; tile++) {
     const SmallOrigin o = small_origin(S, tile);
     for (uint32_t tid = 0; tid < (uint32_t)kSmallThreads; tid++) {
-      if (S.elt == 1) small_load<1>(S, o, in, smem.data(), tid, kSmallThreads);
-      else small_load<2>(S, o, in, smem.data(), tid, kSmallThreads);
+      if (S.elt == 1) small_load<1>(S, o, in, smemBase, tid, kSmallThreads);
+      else small_load<2>(S, o, in, smemBase, tid, kSmallThreads);
     }
     for (uint32_t tid = 0; tid < (uint32_t)kSmallThreads; tid++) {
-      if (S.elt == 1) small_store<1>(S, o, out, smem.data(), tid, kSmallThreads);
-      else small_store<2>(S, o, out, smem.data(), tid, kSmallThreads);
+      if (S.elt == 1) small_store<1>(S, o, out, smemBase, tid, kSmallThreads);
+      else small_store<2>(S, o, out, smemBase, tid, kSmallThreads);
     }
   }
   if (small_violations()) { fprintf(stderr, "hostcheck: %lld bad small-element accesses\n", small_violations()); return 9; }
@@ -207,8 +211,8 @@ int cutt_hostcheck_run_ext(int rank, const int* dim, const int* perm, int eltByt
     SmallDesc S;
     if (!build_small(P, S)) return 5;
     if (label && labelLen > 0)
-      snprintf(label, labelLen, "small t=%ux%u%s tiles=%u", 1u << S.logTA, 1u << S.logTB,
-               S.storeAlongB ? "" : " rows", S.numTiles);
+      snprintf(label, labelLen, "small t=%ux%u%s%s%s tiles=%u", 1u << S.logTA, 1u << S.logTB,
+               S.storeAlongB ? "" : " rows", S.packLoad ? " ld32" : "", S.packStore ? " st32" : "", S.numTiles);
     return run_small(S, (const unsigned char*)in, (unsigned char*)out);
   }
   const std::vector<Candidate>& cands = candidates_of(P);

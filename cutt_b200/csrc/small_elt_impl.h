@@ -33,6 +33,8 @@ struct SmallDesc {
   uint32_t storeAlongB;  // 1: B is the fastest output dimension, lanes store along B
   uint32_t numTiles;
   uint32_t smemBytes;
+  uint32_t packLoad;     // 1: the strides allow 4-byte global loads (buffer 4-byte aligned)
+  uint32_t packStore;    // 1: the same for the stores
   uint64_t dA, dB;       // extents
   int64_t isB;           // input stride of B (A has input stride 1), elements
   int64_t osA, osB;      // output strides
@@ -58,6 +60,27 @@ inline bool small_ok(uint64_t idx, uint64_t n) {
 #else
 CUTT_HD bool small_ok(uint64_t, uint64_t) { return true; }
 #endif
+
+// Alignment check of the host interpreter (a misaligned 32-bit access faults on the device).
+#if !defined(__CUDA_ARCH__) && defined(CUTT_HOSTCHECK_BOUNDS)
+inline bool small_aligned4(const void* p) {
+  if (((uintptr_t)p & 3) == 0) return true;
+  small_violations()++;
+  return false;
+}
+#else
+CUTT_HD bool small_aligned4(const void*) { return true; }
+#endif
+
+CUTT_HD uint32_t small_ldg32(const void* p) {
+#if defined(__CUDA_ARCH__)
+  return __ldg(reinterpret_cast<const uint32_t*>(p));
+#else
+  uint32_t w;
+  memcpy(&w, p, 4);
+  return w;
+#endif
+}
 
 struct SmallOrigin {
   uint64_t a0, b0;     // coordinates of the tile's first element along A and B
@@ -96,6 +119,29 @@ CUTT_HD void small_load(const SmallDesc& D, const SmallOrigin& o, const unsigned
   const uint32_t extA = ra < TA ? (uint32_t)ra : TA;
   const uint32_t extB = rb < TB ? (uint32_t)rb : TB;
   const uint32_t n = TA << D.logTB;
+  if (D.packLoad) {
+    // one 32-bit word (K elements along A) per step; the ragged end of a row element by element
+    constexpr uint32_t K = 4 / ELT, LK = ELT == 2 ? 1 : 2;
+    const uint32_t logWA = D.logTA - LK;
+#if defined(__CUDA_ARCH__)
+#pragma unroll 4
+#endif
+    for (uint32_t i = tid; i < (n >> LK); i += nthreads) {
+      const uint32_t a = (i & ((1u << logWA) - 1)) << LK, b = i >> logWA;
+      if (a >= extA || b >= extB) continue;
+      const int64_t gi = o.ioff + (int64_t)a + (int64_t)b * D.isB;
+      const uint32_t si = b * D.pitch + a;
+      if (a + K <= extA) {
+        if (small_ok((uint64_t)gi + K - 1, D.volume) && small_ok((uint64_t)(si + K) * ELT - 1, D.smemBytes) &&
+            small_aligned4(g + gi) && small_aligned4(s + si))
+          *reinterpret_cast<uint32_t*>(s + si) = small_ldg32(g + gi);
+      } else {
+        for (uint32_t k = 0; a + k < extA; k++)
+          if (small_ok((uint64_t)gi + k, D.volume) && small_ok((uint64_t)(si + k) * ELT, D.smemBytes)) s[si + k] = g[gi + k];
+      }
+    }
+    return;
+  }
 #if defined(__CUDA_ARCH__)
 #pragma unroll 8
 #endif
@@ -121,6 +167,52 @@ CUTT_HD void small_store(const SmallDesc& D, const SmallOrigin& o, unsigned char
   const uint32_t extA = ra < TA ? (uint32_t)ra : TA;
   const uint32_t extB = rb < TB ? (uint32_t)rb : TB;
   const uint32_t n = TA << D.logTB;
+  if (D.packStore) {
+    constexpr uint32_t K = 4 / ELT, LK = ELT == 2 ? 1 : 2;
+#if defined(__CUDA_ARCH__)
+#pragma unroll 4
+#endif
+    for (uint32_t i = tid; i < (n >> LK); i += nthreads) {
+      if (D.storeAlongB) {
+        // K neighbouring lanes take the K columns that share one shared-memory word (a broadcast,
+        // not a bank conflict); each gathers K rows of its column into one output word
+        const uint32_t da = i & (K - 1);
+        const uint32_t b = ((i >> LK) & ((TB >> LK) - 1)) << LK;
+        const uint32_t a = ((i >> D.logTB) << LK) + da;
+        if (a >= extA || b >= extB) continue;
+        const int64_t gi = o.ooff + (int64_t)a * D.osA + (int64_t)b;
+        const uint32_t si = b * D.pitch + a;
+        if (b + K <= extB) {
+          uint32_t w = 0;
+          bool ok = small_ok((uint64_t)gi + K - 1, D.volume) && small_aligned4(g + gi);
+          for (uint32_t k = 0; k < K; k++) {
+            if (!small_ok((uint64_t)(si + k * D.pitch) * ELT, D.smemBytes)) { ok = false; break; }
+            w |= (uint32_t)s[si + k * D.pitch] << (8 * ELT * k);
+          }
+          if (ok) *reinterpret_cast<uint32_t*>(g + gi) = w;
+        } else {
+          for (uint32_t k = 0; b + k < extB; k++)
+            if (small_ok((uint64_t)gi + k, D.volume) && small_ok((uint64_t)(si + k * D.pitch) * ELT, D.smemBytes))
+              g[gi + k] = s[si + k * D.pitch];
+        }
+      } else {
+        const uint32_t logWA = D.logTA - LK;
+        const uint32_t a = (i & ((1u << logWA) - 1)) << LK, b = i >> logWA;
+        if (a >= extA || b >= extB) continue;
+        const int64_t gi = o.ooff + (int64_t)a + (int64_t)b * D.osB;
+        const uint32_t si = b * D.pitch + a;
+        if (a + K <= extA) {
+          if (small_ok((uint64_t)gi + K - 1, D.volume) && small_ok((uint64_t)(si + K) * ELT - 1, D.smemBytes) &&
+              small_aligned4(g + gi) && small_aligned4(s + si))
+            *reinterpret_cast<uint32_t*>(g + gi) = *reinterpret_cast<const uint32_t*>(s + si);
+        } else {
+          for (uint32_t k = 0; a + k < extA; k++)
+            if (small_ok((uint64_t)gi + k, D.volume) && small_ok((uint64_t)(si + k) * ELT, D.smemBytes)) g[gi + k] = s[si + k];
+        }
+      }
+    }
+    return;
+  }
 #if defined(__CUDA_ARCH__)
 #pragma unroll 8
 #endif
@@ -187,6 +279,17 @@ inline bool build_small(const Problem& P, SmallDesc& D) {
     D.nloop++;
   }
   D.numTiles = (uint32_t)tiles;
+  // 4-byte accesses need every row of a tile to start on a 4-byte boundary
+  const int64_t K = 4 / P.elt;
+  bool inOk = D.logTA >= (P.elt == 2 ? 1u : 2u) && D.isB % K == 0;
+  bool outOk = D.storeAlongB ? (D.logTB >= (P.elt == 2 ? 1u : 2u) && D.logTA >= (P.elt == 2 ? 1u : 2u) && D.osA % K == 0)
+                             : (D.logTA >= (P.elt == 2 ? 1u : 2u) && D.osB % K == 0);
+  for (uint32_t k = 0; k < D.nloop; k++) {
+    if (D.loopIs[k] % K) inOk = false;
+    if (D.loopOs[k] % K) outOk = false;
+  }
+  D.packLoad = inOk ? 1u : 0u;
+  D.packStore = outOk ? 1u : 0u;
   return true;
 }
 

@@ -58,7 +58,7 @@ def raw_bytes(n, seed):
 
 @pytest.mark.parametrize("elt", [1, 2, 16])
 def test_small_shapes_all_permutations(native, oracle_mod, elt):
-    for dims in ([3, 5], [4, 6], [8, 3, 5], [2, 3, 4, 5], [7, 66, 5], [130, 70], [258, 3, 9]):
+    for dims in ([3, 5], [4, 6], [8, 3, 5], [2, 3, 4, 5], [7, 66, 5], [130, 70], [258, 3, 9], [132, 76], [8, 12, 20]):
         raw = raw_bytes(volume(dims) * elt, 11 + elt)
         for perm in itertools.permutations(range(len(dims))):
             out, desc = run_ext(native, dims, list(perm), elt, raw)
@@ -78,6 +78,9 @@ def test_random_ranks(native, oracle_mod, elt):
 
 @pytest.mark.parametrize("elt,dims,perm", [
     (2, [4100, 3001], [1, 0]),            # element-wise kernel, partial tiles on both sides
+    (2, [4100, 3002], [1, 0]),            # the same with 4-byte packing on both sides
+    (1, [5004, 4100], [1, 0]),
+    (1, [5004, 4099], [1, 0]),            # packed loads, element stores
     (1, [5003, 4099], [1, 0]),
     (2, [6, 2000, 700], [2, 0, 1]),       # short fastest dimension
     (2, [64, 300, 500], [0, 2, 1]),       # kept run of 128 bytes: re-stated in 8-byte units
@@ -112,6 +115,8 @@ def test_method_choice(native):
     (1, [36, 30, 70], [0, 2, 1]),
     (16, [30, 25, 40], [2, 0, 1]),
     (2, [301, 200], [1, 0]),
+    (2, [300, 200], [1, 0]),          # 4-byte packing planned, dropped for these buffers
+    (1, [64, 300], [1, 0]),
 ])
 def test_buffers_aligned_for_the_element_type_only(native, oracle_mod, elt, dims, perm):
     raw = raw_bytes(volume(dims) * elt, 9)

@@ -53,11 +53,12 @@ def test_extension_element_sizes(hc, oracle_mod, elt):
                                           ctypes.c_char_p, ctypes.c_int]
     rng = random.Random(31 + elt)
     cases = []
-    for dims in ([3, 5], [4, 6], [8, 3, 5], [2, 3, 4, 5], [7, 66, 5], [130, 70], [258, 3, 9], [5, 300, 2, 3]):
+    for dims in ([3, 5], [4, 6], [8, 3, 5], [2, 3, 4, 5], [7, 66, 5], [130, 70], [258, 3, 9], [5, 300, 2, 3],
+                 [132, 76], [8, 12, 20], [6, 4, 10, 8]):
         cases += [(dims, list(p)) for p in itertools.permutations(range(len(dims)))]
     for rank in range(2, 10):
         cases += [random_case(rng, rank, 60_000) for _ in range(3)]
-    labels = set()
+    labels, seen = set(), set()
     for dims, perm in cases:
         raw = np.random.default_rng(volume(dims)).integers(0, 256, volume(dims) * elt, dtype=np.uint8)
         want = _ext_expected(oracle_mod, dims, perm, elt, raw)
@@ -71,8 +72,10 @@ def test_extension_element_sizes(hc, oracle_mod, elt):
             assert rc == 0, (rc, dims, perm, elt, idx)
             assert np.array_equal(out, want), (dims, perm, elt, idx, lab.value.decode())
             labels.add(lab.value.decode()[:5])
+            seen.add(lab.value.decode()[:40])
     if elt < 4:
         assert "small" in labels and "memcp" in labels and '{"met' in labels
+        assert any("ld32" in l for l in seen) and any("st32" in l for l in seen) and any("rows" in l for l in seen)
 
 
 def _check_candidates(hc, oracle_mod, dims, perm, elts=(4, 8), max_cands=None, seed=0):
