@@ -38,11 +38,19 @@ def _reference_permute(tin, dims, perm):
 
 def run_case(C, torch, dims, perm, elt, measure, buf_in, buf_out, check=True):
     vol = _vol(dims)
-    dt = torch.int32 if elt == 4 else torch.int64
-    tin = buf_in[:vol * elt // 8 + 1].view(dt)[:vol]
-    tout = buf_out[:vol * elt // 8 + 1].view(dt)[:vol]
+    words = 1
+    if elt == 16:   # checked as two 64-bit words per element under an unpermuted innermost dimension
+        words = 2
+    dt = {1: torch.uint8, 2: torch.int16, 4: torch.int32, 8: torch.int64, 16: torch.int64}[elt]
+    tin = buf_in[:vol * elt // 8 + 1].view(dt)[:vol * words]
+    tout = buf_out[:vol * elt // 8 + 1].view(dt)[:vol * words]
     stream = torch.cuda.current_stream().cuda_stream
-    if measure:
+    if elt not in (4, 8):   # sizes the original rejects: extension entry points
+        if measure:
+            rc, h = C.plan_measure_ext(dims, perm, elt, stream, tin.data_ptr(), tout.data_ptr())
+        else:
+            rc, h = C.plan_ext(dims, perm, elt, stream)
+    elif measure:
         rc, h = C.cuttPlanMeasure(len(dims), dims, perm, elt, stream, tin.data_ptr(), tout.data_ptr())
     else:
         rc, h = C.cuttPlan(len(dims), dims, perm, elt, stream)
@@ -50,7 +58,7 @@ def run_case(C, torch, dims, perm, elt, measure, buf_in, buf_out, check=True):
         raise RuntimeError("plan failed with code %d for %s %s" % (rc, dims, perm))
     times = []
     for _ in range(4):
-        tout.fill_(-1)
+        tout.fill_(255 if elt == 1 else -1)
         torch.cuda.synchronize()
         e0 = torch.cuda.Event(enable_timing=True)
         e1 = torch.cuda.Event(enable_timing=True)
@@ -64,7 +72,10 @@ def run_case(C, torch, dims, perm, elt, measure, buf_in, buf_out, check=True):
     C.cuttDestroy(h)
     ok = True
     if check:
-        ok = bool(torch.equal(tout, _reference_permute(tin, dims, perm)))
+        if elt == 16:
+            ok = bool(torch.equal(tout, _reference_permute(tin, [2] + list(dims), [0] + [p + 1 for p in perm])))
+        else:
+            ok = bool(torch.equal(tout, _reference_permute(tin, dims, perm)))
     gbs = [2 * vol * elt / (t * 1e-3) / 1e9 for t in times]
     return gbs, ok, plan
 
@@ -108,7 +119,8 @@ def main(argv=None):
     ap.add_argument("-device", type=int, default=0)
     ap.add_argument("-measure", action="store_true")
     ap.add_argument("-seed", type=int, default=12345)
-    ap.add_argument("-elemsize", type=int, default=8, choices=[4, 8])
+    ap.add_argument("-elemsize", type=int, default=8, choices=[1, 2, 4, 8, 16],
+                    help="4 and 8 as in the original; 1, 2 and 16 go through the extension entry points")
     ap.add_argument("-dim", type=int, nargs="+")
     ap.add_argument("-permutation", type=int, nargs="+")
     ap.add_argument("-bench", type=int, default=0)
