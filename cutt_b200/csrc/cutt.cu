@@ -745,7 +745,16 @@ int cutt_c_transpose_host(int rank, const int* dim, const int* permutation, size
   const int dlast = dim[last];
   int nslab = 1;
   if (bytes >= (size_t)64 << 20) nslab = dlast < 8 ? dlast : 8;
-  if (bytes >= (size_t)512 << 20 && dlast >= 256) nslab = 16;  // shorter unoverlapped head and tail
+  if (bytes >= (size_t)512 << 20 && dlast >= 256) {
+    // measured on B200 hosts (PCIe 5 x16, 0.8 and 1.6 GB tensors): 6-9 slabs are fastest; every
+    // slab beyond that costs about 1 ms, fewer leave a long unoverlapped head and tail
+    const size_t n = bytes / ((size_t)160 << 20);
+    nslab = n < 6 ? 6 : (n > 8 ? 8 : (int)n);
+  }
+  {
+    const size_t forced = env_size("CUTT_HOST_SLABS", 0);     // tuning aid
+    if (forced >= 1 && (int)forced <= dlast) nslab = (int)forced;
+  }
   // strides of the slowest input dimension on both sides (elements)
   size_t isLast = 1, osLast = 1;
   for (int i = 0; i < last; i++) isLast *= (size_t)dim[i];
