@@ -32,6 +32,7 @@ sys.path.insert(0, ROOT)
 
 METRIC = "effective_transpose_bandwidth"
 UNIT = "GB/s"
+C2_WORKLOAD = "c2: rank-2 transpose (14142,14142) perm (1,0), fp32 then fp64 per step"
 
 
 def _peaks():
@@ -99,7 +100,8 @@ def run_reference(args):
         "steps": steps, "warmup": min(args.warmup, 1), "ms_per_step": dt * 1e3,
         "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
         "dtype": "b32+b64 (bit moves)", "data": "synthetic",
-        "config": {"workload": args.workload, "cases": [[n, d, p, e] for n, d, p, e in cases]},
+        "config": {"workload": C2_WORKLOAD if args.workload == "c2" else args.workload,
+                   "cases": [[n, d, p, e] for n, d, p, e in cases]},
         "cpu_baseline": {"value": val, "unit": UNIT, "cores": cores, "kind": "port",
                          "sample": "%d full steps of the workload (blocked OpenMP loop nest)" % steps},
         "e2e": {"value": val, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
@@ -348,8 +350,7 @@ def run_ours(args):
         del hbufs
 
     line = base_line(args, value, ms_per_step, world)
-    line["config"] = {"workload": "c2: rank-2 transpose (14142,14142) perm (1,0), fp32 then fp64 per step"
-                      if args.workload == "c2" else args.workload,
+    line["config"] = {"workload": C2_WORKLOAD if args.workload == "c2" else args.workload,
                       "cases": [[p[0], p[1], p[2], p[3]] for p in plans],
                       "l2": "inputs larger than L2 (0.8 GB and 1.6 GB per side)", "per_case": per_case,
                       "d2d_copy_gbs": d2d, "own_copy_kernel_gbs": own_copy}

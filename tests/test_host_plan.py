@@ -94,6 +94,21 @@ def _check_candidates(hc, oracle_mod, dims, perm, elts=(4, 8), max_cands=None, s
             assert np.array_equal(out, want), (dims, perm, elt, i, lab.value.decode())
 
 
+def test_small_tensors_get_enough_tiles(hc):
+    """Latency-bound tensors: the model's first pick must spread the work over the SMs (the README
+    example is 0.8 MB; a 64 KB tile would leave 135 of 148 SMs idle)."""
+    for dims, perm in (README_CASE, ([256, 256], [1, 0]), ([64, 64, 64], [2, 1, 0])):
+        for elt in (4, 8):
+            a = raw_bits(volume(dims), elt, 1)
+            out = np.empty_like(a)
+            lab = ctypes.create_string_buffer(4096)
+            rc = hc.cutt_hostcheck_run(len(dims), _iarr(dims), _iarr(perm), elt, 0, a.ctypes.data,
+                                       out.ctypes.data, lab, 4096)
+            assert rc == 0
+            d = json.loads(lab.value.decode())
+            assert d["num_tiles"] >= 64, (dims, elt, d["label"])
+
+
 def test_fastdiv(hc):
     for d in [1, 2, 3, 5, 7, 31, 32, 33, 549, 1000, 14142, 65535, 65536, 65537,
               2**31 - 1, 2**31, 2**31 + 1, 2**32 - 1]:
