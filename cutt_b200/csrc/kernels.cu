@@ -87,6 +87,9 @@ permute_tiles_kernel(const __grid_constant__ TileDesc D, const unsigned char* __
   }
 }
 
+static_assert(sizeof(TileDesc) + sizeof(void*) + sizeof(PeerPtrs) <= 4096,
+              "kernel parameters must fit the 4 KB parameter space");
+
 typedef void (*TilesKernel)(const TileDesc, const unsigned char*, const PeerPtrs);
 
 static TilesKernel pick_tiles_kernel(const TileDesc& D) {

@@ -121,6 +121,7 @@ struct RowDim {
   Skew skew;
   uint32_t ishift;   // aligned over-fetch mode: input stride of this dimension modulo the vector
                      // width (elements) if the dimension selects input rows, else 0
+  FastDiv div;       // division by ext (row-table construction)
 };
 
 // A dimension inside the output side's run: turns a position along the run into a
@@ -290,8 +291,9 @@ CUTT_HD void make_row(const Side& S, uint32_t r, int64_t& goff, uint32_t& soffB,
   uint32_t resid = 0;
   for (uint32_t k = 0; k < S.nRowDims; k++) {
     const RowDim& R = S.rowDim[k];
-    uint32_t cc = r % R.ext;
-    r /= R.ext;
+    const uint32_t nr = fdiv(r, R.div);
+    uint32_t cc = r - nr * R.ext;
+    r = nr;
     goff += (int64_t)cc * R.gstride;
     soffB += cc * R.sstrideB + skew_bytes(R.skew, cc);
     resid += cc * R.ishift;
@@ -336,6 +338,9 @@ CUTT_HD void build_tables(const TileDesc& D, unsigned char* tables, uint32_t tid
   RowCoord* coIn = reinterpret_cast<RowCoord*>(tables + L.coordIn);
   RowCoord* coOut = reinterpret_cast<RowCoord*>(tables + L.coordOut);
   uint32_t* qtab = reinterpret_cast<uint32_t*>(tables + L.qtab);
+  // a side with at most one row dimension computes its row offsets by multiplication and never
+  // reads its tables
+  if (D.in.nRowDims > 1)
   for (uint32_t r = tid; r < D.in.nrows; r += nthreads) {
     int64_t g; uint32_t s; RowCoord rc;
     make_row(D.in, r, g, s, rc);
@@ -343,6 +348,7 @@ CUTT_HD void build_tables(const TileDesc& D, unsigned char* tables, uint32_t tid
     tabIn[r].soffB = s;
     coIn[r] = rc;
   }
+  if (D.out.nRowDims > 1)
   for (uint32_t r = tid; r < D.out.nrows; r += nthreads) {
     int64_t g; uint32_t s; RowCoord rc;
     make_row(D.out, r, g, s, rc);

@@ -186,6 +186,11 @@ CUTT_HD void aof_row(sptr_t srow, const unsigned char* grow, uint32_t valid, uin
   const uint32_t sh = (uint32_t)(((uintptr_t)grow / ELT) & (VE - 1));
   const unsigned char* gal = grow - sh * ELT;
   const uint32_t nvec = (sh + valid + VE - 1) / VE;
+  if (gal >= lo && gal + 16u * (size_t)nvec <= hi) {
+    // the whole aligned range lies inside the buffer (every row but the first and last few)
+    for (uint32_t v = tq; v < nvec; v += Tq) copy_g2s<16>(srow + 16u * v, gal + 16u * (size_t)v);
+    return;
+  }
   for (uint32_t v = tq; v < nvec; v += Tq) {
     const unsigned char* src = gal + 16u * v;
     if (src >= lo && src + 16 <= hi) {

@@ -438,6 +438,7 @@ bool build_tile(const Problem& P, const TileParams& tp, const DeviceInfo& dev, C
       RowDim& R = S.rowDim[S.nRowDims++];
       const int64_t blk = (!input && j == 0) ? V : 1;
       R.ext = (uint32_t)(t[j] / blk);
+      R.div = make_fastdiv(R.ext);
       R.sstrideB = (uint32_t)(ss[j] * blk * elt);
       R.gstride = (input ? P.is[j] : P.os[j]) * blk;
       R.slot = slotOf[j];
