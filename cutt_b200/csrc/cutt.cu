@@ -490,7 +490,7 @@ cuttResult make_plan(cuttHandle* handle, int rank, const int* dim, const int* pe
           if (warm > 0.0) scored.push_back(std::make_pair(tmin, (int)i));
           if (tmin < best) { best = tmin; bestIdx = (int)i; bestFirst = first; }
         }
-        // Play-off: candidates within 3 % of the winner (at most four) are timed five more
+        // Play-off: candidates within 3 % of the winner (at most four) are timed seven more
         // times each, alternating, and ranked by their median - two runs cannot separate them.
         std::sort(scored.begin(), scored.end());
         while (scored.size() > 4 || (!scored.empty() && scored.back().first > 1.03 * scored.front().first))
@@ -498,7 +498,7 @@ cuttResult make_plan(cuttHandle* handle, int rank, const int* dim, const int* pe
         if (scored.size() >= 2) {
           std::vector<std::vector<float>> t(scored.size());
           bool fail = false;
-          for (int round = 0; round < 5 && !fail; round++) {
+          for (int round = 0; round < 7 && !fail; round++) {
             for (size_t k = 0; k < scored.size() && !fail; k++) {
               if (!adopt_candidate(trial, dev, cands[scored[k].second])) { fail = true; break; }
               const int batch = scored[k].first < 0.05 ? 8 : 1;
@@ -516,12 +516,17 @@ cuttResult make_plan(cuttHandle* handle, int rank, const int* dim, const int* pe
             cudaGetLastError();
           } else {
             double bestMed = 1e30;
+            std::vector<double> med(scored.size());
             for (size_t k = 0; k < scored.size(); k++) {
               std::sort(t[k].begin(), t[k].end());
-              const double med = t[k][t[k].size() / 2];
-              if (verbose) fprintf(stderr, "[cutt] play-off %2d median %8.4f ms\n", scored[k].second, med);
-              if (med < bestMed) { bestMed = med; bestIdx = scored[k].second; }
+              med[k] = t[k][t[k].size() / 2];
+              if (verbose) fprintf(stderr, "[cutt] play-off %2d median %8.4f ms\n", scored[k].second, med[k]);
+              if (med[k] < bestMed) bestMed = med[k];
             }
+            // medians within 0.5 % are a tie: the cost model's order decides
+            bestIdx = -1;
+            for (size_t k = 0; k < scored.size(); k++)
+              if (med[k] <= 1.005 * bestMed && (bestIdx < 0 || scored[k].second < bestIdx)) bestIdx = scored[k].second;
           }
         }
         cudaEventDestroy(e0);
