@@ -276,6 +276,36 @@ CUTT_HD void tile_store_aof(const TileDesc& D, const TileCtx& c, const Tables<WI
     }
     unsigned char* gq = gbase + (size_t)q * ELT;
     unsigned char* g = gq + g0off;
+    if (single && ((Tr * R.ishift) & (VE - 1)) == 0) {
+      // the row residue is the same for every row this thread visits: fold it into the
+      // position offsets once
+      const uint32_t rres0 = tr * R.ishift;
+      uint32_t sofs[W];
+#pragma unroll
+      for (int i = 0; i < W; i++) sofs[i] = so[i] + ((qr[i] + rres0) & (VE - 1)) * ELT;
+#pragma unroll 2
+      for (uint32_t row = tr; row < nr; row += Tr) {
+        uint32_t soff = row * R.sstrideB;
+        if (skewed) soff += skew_bytes(R.skew, row);
+        uint32_t x[W][V * EW];
+#pragma unroll
+        for (int i = 0; i < W; i++) lds<ELT * V>(x[i], sbuf + soff + sofs[i]);
+        unsigned char* gg = g;
+#pragma unroll
+        for (int j = 0; j < V; j++) {
+          uint32_t y[W * EW];
+#pragma unroll
+          for (int i = 0; i < W; i++) {
+#pragma unroll
+            for (int w = 0; w < EW; w++) y[i * EW + w] = x[i][j * EW + w];
+          }
+          stg<ELT * W>(gg, y);
+          gg += vstepB;
+        }
+        g += gstepB;
+      }
+      continue;
+    }
 #pragma unroll 2
     for (uint32_t row = tr; row < nr; row += Tr) {
       uint32_t soff, rres;
