@@ -222,6 +222,22 @@ CUTT_HD void tile_load_aof(const TileDesc& D, const TileCtx& c, const Tables<WID
     const int64_t gstepB = S.nRowDims ? R.gstride * (int64_t)(Tr * ELT) : 0;
     const unsigned char* g0 = gbase + (S.nRowDims ? R.gstride * (int64_t)(tr * ELT) : 0);
     const bool skewed = S.nRowDims && R.skew.mask != 0;
+    // Strides are positive, so rows 0 and nr-1 bound the tile: when both lie inside the buffer with
+    // a vector to spare on either side, no row of the tile needs the per-row range test.
+    const unsigned char* lastRow = gbase + (S.nRowDims && nr ? R.gstride * (int64_t)((nr - 1) * ELT) : 0);
+    if ((uintptr_t)gbase >= (uintptr_t)lo + 16 && (uintptr_t)lastRow + (size_t)valid * ELT + 16 <= (uintptr_t)hi) {
+      constexpr uint32_t VE = 16 / ELT;
+      for (uint32_t row = tr; row < nr; row += Tr) {
+        sptr_t s = sbuf + row * R.sstrideB;
+        if (skewed) s += skew_bytes(R.skew, row);
+        const uint32_t sh = (uint32_t)(((uintptr_t)g0 / ELT) & (VE - 1));
+        const unsigned char* gal = g0 - sh * ELT;
+        const uint32_t nvec = (sh + valid + VE - 1) / VE;
+        for (uint32_t v = tq; v < nvec; v += S.tq) copy_g2s<16>(s + 16u * v, gal + 16u * (size_t)v);
+        g0 += gstepB;
+      }
+      return;
+    }
     for (uint32_t row = tr; row < nr; row += Tr) {
       sptr_t s = sbuf + row * R.sstrideB;
       if (skewed) s += skew_bytes(R.skew, row);
