@@ -58,7 +58,7 @@ def raw_bytes(n, seed):
 
 @pytest.mark.parametrize("elt", [1, 2, 16])
 def test_small_shapes_all_permutations(native, oracle_mod, elt):
-    for dims in ([3, 5], [4, 6], [8, 3, 5], [2, 3, 4, 5], [7, 66, 5], [130, 70], [258, 3, 9], [132, 76], [8, 12, 20]):
+    for dims in ([3, 5], [4, 6], [8, 3, 5], [2, 3, 4, 5], [7, 66, 5], [130, 70], [258, 3, 9], [132, 76], [8, 12, 20], [2, 5000], [4, 3000]):
         raw = raw_bytes(volume(dims) * elt, 11 + elt)
         for perm in itertools.permutations(range(len(dims))):
             out, desc = run_ext(native, dims, list(perm), elt, raw)

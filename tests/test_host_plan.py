@@ -54,7 +54,7 @@ def test_extension_element_sizes(hc, oracle_mod, elt):
     rng = random.Random(31 + elt)
     cases = []
     for dims in ([3, 5], [4, 6], [8, 3, 5], [2, 3, 4, 5], [7, 66, 5], [130, 70], [258, 3, 9], [5, 300, 2, 3],
-                 [132, 76], [8, 12, 20], [6, 4, 10, 8]):
+                 [132, 76], [8, 12, 20], [6, 4, 10, 8], [2, 5000], [4, 3000]):
         cases += [(dims, list(p)) for p in itertools.permutations(range(len(dims)))]
     for rank in range(2, 10):
         cases += [random_case(rng, rank, 60_000) for _ in range(3)]
