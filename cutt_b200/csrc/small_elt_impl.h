@@ -107,71 +107,50 @@ CUTT_HD SmallOrigin small_origin(const SmallDesc& D, uint32_t tile) {
   return o;
 }
 
-// How one thread walks a 2-D index space of 2^logNI inner positions (consecutive threads take
-// consecutive inner positions) by NO outer positions.  When the inner extent fits the block, a
-// thread keeps its inner position and steps through the outer ones, so the addresses advance by
-// constants; otherwise it strides through the inner positions of every outer one.
-struct SmallIter {
-  uint32_t in0, inStep, o0, oStep;
-};
-CUTT_HD SmallIter small_iter(uint32_t logNI, uint32_t tid, uint32_t nthreads) {
-  SmallIter it;
-  const uint32_t NI = 1u << logNI;
-  if (NI <= nthreads) {  // both powers of two
-    it.in0 = tid & (NI - 1);
-    it.inStep = NI;
-    it.o0 = tid >> logNI;
-    it.oStep = nthreads >> logNI;
-  } else {
-    it.in0 = tid;
-    it.inStep = nthreads;
-    it.o0 = 0;
-    it.oStep = 1;
-  }
-  return it;
-}
-
 // Global -> shared, lanes along A.
 template <int ELT>
 CUTT_HD void small_load(const SmallDesc& D, const SmallOrigin& o, const unsigned char* in,
                         unsigned char* smem, uint32_t tid, uint32_t nthreads) {
   typedef typename SmallType<ELT>::type T;
-  const T* g = reinterpret_cast<const T*>(in) + o.ioff;
+  const T* g = reinterpret_cast<const T*>(in);
   T* s = reinterpret_cast<T*>(smem);
   const uint64_t ra = D.dA - o.a0, rb = D.dB - o.b0;
   const uint32_t TA = 1u << D.logTA, TB = 1u << D.logTB;
   const uint32_t extA = ra < TA ? (uint32_t)ra : TA;
   const uint32_t extB = rb < TB ? (uint32_t)rb : TB;
-  const uint64_t left = D.volume - (uint64_t)o.ioff;   // elements from the tile origin to the end
+  const uint32_t n = TA << D.logTB;
   if (D.packLoad) {
     // one 32-bit word (K elements along A) per step; the ragged end of a row element by element
     constexpr uint32_t K = 4 / ELT, LK = ELT == 2 ? 1 : 2;
     const uint32_t logWA = D.logTA - LK;
-    const SmallIter it = small_iter(logWA, tid, nthreads);
-    for (uint32_t b = it.o0; b < extB; b += it.oStep) {
-      for (uint32_t aw = it.in0; aw < (1u << logWA); aw += it.inStep) {
-        const uint32_t a = aw << LK;
-        if (a >= extA) continue;
-        const int64_t gi = (int64_t)a + (int64_t)b * D.isB;
-        const uint32_t si = b * D.pitch + a;
-        if (a + K <= extA) {
-          if (small_ok((uint64_t)gi + K - 1, left) && small_ok((uint64_t)(si + K) * ELT - 1, D.smemBytes) &&
-              small_aligned4(g + gi) && small_aligned4(s + si))
-            *reinterpret_cast<uint32_t*>(s + si) = small_ldg32(g + gi);
-        } else {
-          for (uint32_t k = 0; a + k < extA; k++)
-            if (small_ok((uint64_t)gi + k, left) && small_ok((uint64_t)(si + k) * ELT, D.smemBytes)) s[si + k] = g[gi + k];
-        }
+#if defined(__CUDA_ARCH__)
+#pragma unroll 4
+#endif
+    for (uint32_t i = tid; i < (n >> LK); i += nthreads) {
+      const uint32_t a = (i & ((1u << logWA) - 1)) << LK, b = i >> logWA;
+      if (a >= extA || b >= extB) continue;
+      const int64_t gi = o.ioff + (int64_t)a + (int64_t)b * D.isB;
+      const uint32_t si = b * D.pitch + a;
+      if (a + K <= extA) {
+        if (small_ok((uint64_t)gi + K - 1, D.volume) && small_ok((uint64_t)(si + K) * ELT - 1, D.smemBytes) &&
+            small_aligned4(g + gi) && small_aligned4(s + si))
+          *reinterpret_cast<uint32_t*>(s + si) = small_ldg32(g + gi);
+      } else {
+        for (uint32_t k = 0; a + k < extA; k++)
+          if (small_ok((uint64_t)gi + k, D.volume) && small_ok((uint64_t)(si + k) * ELT, D.smemBytes)) s[si + k] = g[gi + k];
       }
     }
     return;
   }
-  const SmallIter it = small_iter(D.logTA, tid, nthreads);
-  for (uint32_t b = it.o0; b < extB; b += it.oStep) {
-    for (uint32_t a = it.in0; a < extA; a += it.inStep) {
-      const int64_t gi = (int64_t)a + (int64_t)b * D.isB;
+#if defined(__CUDA_ARCH__)
+#pragma unroll 8
+#endif
+  for (uint32_t i = tid; i < n; i += nthreads) {
+    const uint32_t a = i & (TA - 1), b = i >> D.logTA;
+    if (a < extA && b < extB) {
+      const int64_t gi = o.ioff + (int64_t)a + (int64_t)b * D.isB;
       const uint32_t si = b * D.pitch + a;
-      if (small_ok((uint64_t)gi, left) && small_ok((uint64_t)si * ELT, D.smemBytes)) s[si] = g[gi];
+      if (small_ok((uint64_t)gi, D.volume) && small_ok((uint64_t)si * ELT, D.smemBytes)) s[si] = g[gi];
     }
   }
 }
@@ -181,83 +160,70 @@ template <int ELT>
 CUTT_HD void small_store(const SmallDesc& D, const SmallOrigin& o, unsigned char* out,
                          const unsigned char* smem, uint32_t tid, uint32_t nthreads) {
   typedef typename SmallType<ELT>::type T;
-  T* g = reinterpret_cast<T*>(out) + o.ooff;
+  T* g = reinterpret_cast<T*>(out);
   const T* s = reinterpret_cast<const T*>(smem);
   const uint64_t ra = D.dA - o.a0, rb = D.dB - o.b0;
   const uint32_t TA = 1u << D.logTA, TB = 1u << D.logTB;
   const uint32_t extA = ra < TA ? (uint32_t)ra : TA;
   const uint32_t extB = rb < TB ? (uint32_t)rb : TB;
-  const uint64_t left = D.volume - (uint64_t)o.ooff;
-  constexpr uint32_t K = 4 / ELT, LK = ELT == 2 ? 1 : 2;
-  if (D.storeAlongB) {
-    if (D.packStore) {
-      // Inner position j names (column within a group of K, row group): K neighbouring lanes take
-      // the K columns that share one shared-memory word (a broadcast, not a bank conflict); each
-      // gathers K rows of its column into one output word.  The outer position is the column group.
-      const SmallIter it = small_iter(D.logTB, tid, nthreads);
-      const uint32_t groupsA = (extA + K - 1) >> LK;
-      for (uint32_t ag = it.o0; ag < groupsA; ag += it.oStep) {
-        for (uint32_t j = it.in0; j < TB; j += it.inStep) {
-          const uint32_t a = (ag << LK) + (j & (K - 1));
-          const uint32_t b = (j >> LK) << LK;
-          if (a >= extA || b >= extB) continue;
-          const int64_t gi = (int64_t)a * D.osA + (int64_t)b;
-          const uint32_t si = b * D.pitch + a;
-          if (b + K <= extB) {
-            uint32_t w = 0;
-            bool ok = small_ok((uint64_t)gi + K - 1, left) && small_aligned4(g + gi);
-            for (uint32_t k = 0; k < K; k++) {
-              if (!small_ok((uint64_t)(si + k * D.pitch) * ELT, D.smemBytes)) { ok = false; break; }
-              w |= (uint32_t)s[si + k * D.pitch] << (8 * ELT * k);
-            }
-            if (ok) *reinterpret_cast<uint32_t*>(g + gi) = w;
-          } else {
-            for (uint32_t k = 0; b + k < extB; k++)
-              if (small_ok((uint64_t)gi + k, left) && small_ok((uint64_t)(si + k * D.pitch) * ELT, D.smemBytes))
-                g[gi + k] = s[si + k * D.pitch];
-          }
-        }
-      }
-      return;
-    }
-    const SmallIter it = small_iter(D.logTB, tid, nthreads);
-    for (uint32_t a = it.o0; a < extA; a += it.oStep) {
-      for (uint32_t b = it.in0; b < extB; b += it.inStep) {
-        const int64_t gi = (int64_t)a * D.osA + (int64_t)b;
-        const uint32_t si = b * D.pitch + a;
-        if (small_ok((uint64_t)gi, left) && small_ok((uint64_t)si * ELT, D.smemBytes)) g[gi] = s[si];
-      }
-    }
-    return;
-  }
-  // rows run along A on both sides
+  const uint32_t n = TA << D.logTB;
   if (D.packStore) {
-    const uint32_t logWA = D.logTA - LK;
-    const SmallIter it = small_iter(logWA, tid, nthreads);
-    for (uint32_t b = it.o0; b < extB; b += it.oStep) {
-      for (uint32_t aw = it.in0; aw < (1u << logWA); aw += it.inStep) {
-        const uint32_t a = aw << LK;
-        if (a >= extA) continue;
-        const int64_t gi = (int64_t)a + (int64_t)b * D.osB;
+    constexpr uint32_t K = 4 / ELT, LK = ELT == 2 ? 1 : 2;
+#if defined(__CUDA_ARCH__)
+#pragma unroll 4
+#endif
+    for (uint32_t i = tid; i < (n >> LK); i += nthreads) {
+      if (D.storeAlongB) {
+        // K neighbouring lanes take the K columns that share one shared-memory word (a broadcast,
+        // not a bank conflict); each gathers K rows of its column into one output word
+        const uint32_t da = i & (K - 1);
+        const uint32_t b = ((i >> LK) & ((TB >> LK) - 1)) << LK;
+        const uint32_t a = ((i >> D.logTB) << LK) + da;
+        if (a >= extA || b >= extB) continue;
+        const int64_t gi = o.ooff + (int64_t)a * D.osA + (int64_t)b;
+        const uint32_t si = b * D.pitch + a;
+        if (b + K <= extB) {
+          uint32_t w = 0;
+          bool ok = small_ok((uint64_t)gi + K - 1, D.volume) && small_aligned4(g + gi);
+          for (uint32_t k = 0; k < K; k++) {
+            if (!small_ok((uint64_t)(si + k * D.pitch) * ELT, D.smemBytes)) { ok = false; break; }
+            w |= (uint32_t)s[si + k * D.pitch] << (8 * ELT * k);
+          }
+          if (ok) *reinterpret_cast<uint32_t*>(g + gi) = w;
+        } else {
+          for (uint32_t k = 0; b + k < extB; k++)
+            if (small_ok((uint64_t)gi + k, D.volume) && small_ok((uint64_t)(si + k * D.pitch) * ELT, D.smemBytes))
+              g[gi + k] = s[si + k * D.pitch];
+        }
+      } else {
+        const uint32_t logWA = D.logTA - LK;
+        const uint32_t a = (i & ((1u << logWA) - 1)) << LK, b = i >> logWA;
+        if (a >= extA || b >= extB) continue;
+        const int64_t gi = o.ooff + (int64_t)a + (int64_t)b * D.osB;
         const uint32_t si = b * D.pitch + a;
         if (a + K <= extA) {
-          if (small_ok((uint64_t)gi + K - 1, left) && small_ok((uint64_t)(si + K) * ELT - 1, D.smemBytes) &&
+          if (small_ok((uint64_t)gi + K - 1, D.volume) && small_ok((uint64_t)(si + K) * ELT - 1, D.smemBytes) &&
               small_aligned4(g + gi) && small_aligned4(s + si))
             *reinterpret_cast<uint32_t*>(g + gi) = *reinterpret_cast<const uint32_t*>(s + si);
         } else {
           for (uint32_t k = 0; a + k < extA; k++)
-            if (small_ok((uint64_t)gi + k, left) && small_ok((uint64_t)(si + k) * ELT, D.smemBytes)) g[gi + k] = s[si + k];
+            if (small_ok((uint64_t)gi + k, D.volume) && small_ok((uint64_t)(si + k) * ELT, D.smemBytes)) g[gi + k] = s[si + k];
         }
       }
     }
     return;
   }
-  const SmallIter it = small_iter(D.logTA, tid, nthreads);
-  for (uint32_t b = it.o0; b < extB; b += it.oStep) {
-    for (uint32_t a = it.in0; a < extA; a += it.inStep) {
-      const int64_t gi = (int64_t)a + (int64_t)b * D.osB;
+#if defined(__CUDA_ARCH__)
+#pragma unroll 8
+#endif
+  for (uint32_t i = tid; i < n; i += nthreads) {
+    uint32_t a, b;
+    if (D.storeAlongB) { b = i & (TB - 1); a = i >> D.logTB; }
+    else { a = i & (TA - 1); b = i >> D.logTA; }
+    if (a < extA && b < extB) {
+      const int64_t gi = o.ooff + (int64_t)a * D.osA + (int64_t)b * D.osB;
       const uint32_t si = b * D.pitch + a;
-      if (small_ok((uint64_t)gi, left) && small_ok((uint64_t)si * ELT, D.smemBytes)) g[gi] = s[si];
+      if (small_ok((uint64_t)gi, D.volume) && small_ok((uint64_t)si * ELT, D.smemBytes)) g[gi] = s[si];
     }
   }
 }
