@@ -2,7 +2,8 @@
 
 Times every candidate of the benchmark shapes (C2, C4, C5 slabs, the random C3 suite) through the
 C ABI, three repetitions each, and writes one JSON line per candidate with the feature vector
-the library reports.  usage: python -m cutt_b200.cost_model.sweep OUT.jsonl FIRST_CASE LAST_CASE
+the library reports.  usage: python -m cutt_b200.cost_model.sweep OUT.jsonl FIRST_CASE LAST_CASE   (cases 0-99: the committed suite;
+100 and up: further seeds of the same generator)
 """
 import json, sys, os
 sys.path.insert(0, os.path.dirname(os.path.dirname(os.path.dirname(os.path.abspath(__file__)))))
@@ -19,6 +20,10 @@ def main():
     for i, (d, p) in enumerate(W.c3_cases(100)):
         if lo <= i < hi:
             cases += [("C3_%d" % i, d, p, 8), ("C3_%d" % i, d, p, 4)]
+    # indices from 100 on: further shapes from the same generator (other seeds), training data only
+    for i in range(max(lo, 100), hi):
+        d, p = W.generate_c3_case(i)
+        cases += [("X3_%d" % i, d, p, 8), ("X3_%d" % i, d, p, 4)]
     buf_in = torch.randint(-2**31, 2**31 - 1, (550_000_000,), dtype=torch.int64, device="cuda")
     buf_out = torch.empty_like(buf_in)
     for name, dims, perm, elt in cases:
