@@ -367,6 +367,15 @@ def run_ours(args):
         line["cpu_baseline"] = cpu_baseline(cases)
     if rank == 0 and not args.no_extras and world == 1:
         try:
+            # the cost model alone first (cuttPlan would otherwise find the measured winners in the plan cache)
+            C.clear_plan_cache()
+            res0 = run_suite(C, W.c3_cases(args.suite_cases), stream, reps=5, measure=False)
+            med0 = statistics.median(r["gbs"] for r in res0)
+            extras["c3_suite_cuttPlan"] = {"cases": len(res0), "median_gbs": med0, "frac_of_peak": med0 / peak,
+                                           "min_gbs": min(r["gbs"] for r in res0)}
+        except Exception as e:
+            extras["c3_suite_cuttPlan"] = {"error": repr(e)}
+        try:
             res = run_suite(C, W.c3_cases(args.suite_cases), stream, reps=5)
             med = statistics.median(r["gbs"] for r in res)
             extras["c3_suite"] = {"cases": len(res), "median_gbs": med, "frac_of_peak": med / peak,
@@ -503,8 +512,9 @@ def base_line(args, value, ms_per_step, world):
             "scaling": "weak", "vs_baseline": None, "dtype": "b32+b64 (bit moves)", "data": "synthetic"}
 
 
-def run_suite(C, cases, stream, reps=5):
-    """cuttPlanMeasure + timed cuttExecute for every case, fp64 then fp32."""
+def run_suite(C, cases, stream, reps=5, measure=True):
+    """cuttPlanMeasure (or cuttPlan: the cost model's first pick) + timed cuttExecute for every
+    case, fp64 then fp32."""
     import torch
     out = []
     maxvol = max(_vol(d) for d, _ in cases)
@@ -513,7 +523,10 @@ def run_suite(C, cases, stream, reps=5):
     for ci, (dims, perm) in enumerate(cases):
         vol = _vol(dims)
         for elt in (8, 4):
-            rc, h = C.cuttPlanMeasure(len(dims), dims, perm, elt, stream, buf_in.data_ptr(), buf_out.data_ptr())
+            if measure:
+                rc, h = C.cuttPlanMeasure(len(dims), dims, perm, elt, stream, buf_in.data_ptr(), buf_out.data_ptr())
+            else:
+                rc, h = C.cuttPlan(len(dims), dims, perm, elt, stream)
             if rc != 0:
                 raise RuntimeError("plan failed %s %s" % (dims, perm))
             C.cuttExecute(h, buf_in.data_ptr(), buf_out.data_ptr())
