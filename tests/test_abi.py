@@ -128,3 +128,23 @@ def test_c3_case_list_is_reproducible():
             vol *= d
         assert abs(vol - 2.0e8) <= 0.05 * 2.0e8 and 2 <= len(dims) <= 7 and all(d >= 2 for d in dims)
         assert sorted(perm) == list(range(len(dims))) and perm != sorted(perm)
+
+
+def test_cost_model_evaluate_tool(tmp_path):
+    """The fitted model header parses and ranks sweep records (cutt_b200/cost_model/evaluate.py)."""
+    import json
+    import subprocess
+    import sys
+    import numpy as np
+    rng = np.random.default_rng(0)
+    path = tmp_path / "sweep.jsonl"
+    with open(path, "w") as f:
+        for case in ("A", "B"):
+            for i in range(12):
+                feat = [float(x) for x in rng.uniform(0, 64, 32)]
+                f.write(json.dumps({"case": case, "elt": 4, "idx": i, "gbs": float(1000 + 100 * i), "ms": 1.0,
+                                    "label": "tiles synthetic %d" % i, "feat": feat, "model_us": 1.0}) + "\n")
+    res = subprocess.run([sys.executable, "-m", "cutt_b200.cost_model.evaluate", str(path)], cwd=ROOT,
+                         stdout=subprocess.PIPE, stderr=subprocess.PIPE, text=True, timeout=300)
+    assert res.returncode == 0, res.stderr
+    assert "records 24, groups 2" in res.stdout and "best of first 48: median 1.000" in res.stdout
