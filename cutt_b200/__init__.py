@@ -20,7 +20,7 @@ __all__ = [
     "CUTT_INTERNAL_ERROR", "CUTT_UNDEFINED_ERROR", "CuttError", "lib", "lib_path",
     "cuttPlan", "cuttPlanMeasure", "cuttExecute", "cuttDestroy", "plan_describe",
     "num_candidates", "plan_candidate", "plan_params", "transpose_host", "launch_count", "copy_timeouts", "copy_noalloc", "copy_noalloc_timeouts",
-    "clear_plan_cache", "plan_cache_save", "plan_cache_load", "plan_cache_size", "Plan",
+    "clear_plan_cache", "debug_force_wide", "plan_cache_save", "plan_cache_load", "plan_cache_size", "Plan",
 ]
 
 # cuttResult (src/cutt.h:34-41): fixed values
@@ -79,6 +79,8 @@ def lib() -> ctypes.CDLL:
     L.cutt_c_transpose_host.argtypes = [ctypes.c_int, ip, ip, ctypes.c_size_t, vp, vp]
     L.cutt_c_launch_count.restype = ctypes.c_ulonglong
     L.cutt_c_clear_plan_cache.restype = None
+    L.cutt_c_debug_force_wide.argtypes = [ctypes.c_int]
+    L.cutt_c_debug_force_wide.restype = None
     L.cutt_c_version.restype = ctypes.c_char_p
     L.cutt_c_plan_cache_save.argtypes = [ctypes.c_char_p]
     L.cutt_c_plan_cache_load.argtypes = [ctypes.c_char_p]
@@ -210,6 +212,11 @@ def copy_noalloc(src: int, dst: int, nbytes: int, stream: int = 0) -> int:
 
 def copy_noalloc_timeouts() -> int:
     return int(lib().cutt_c_copy_noalloc_timeouts())
+
+
+def debug_force_wide(on: bool) -> None:
+    """Test aid: build every tiled plan with 64-bit row offsets from now on (see cutt_c.h)."""
+    lib().cutt_c_debug_force_wide(1 if on else 0)
 
 
 def clear_plan_cache() -> None:

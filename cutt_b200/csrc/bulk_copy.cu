@@ -66,10 +66,12 @@ __device__ __forceinline__ void bulk_wait_read_all() { asm volatile("cp.async.bu
 // all committed stores are complete
 __device__ __forceinline__ void bulk_wait_all() { asm volatile("cp.async.bulk.wait_group 0;\n" ::: "memory"); }
 
-// nbytes: multiple of 16; in/out: 16-byte aligned.
-__global__ void __launch_bounds__(32, 1)
-bulk_copy_kernel(const unsigned char* __restrict__ in, unsigned char* __restrict__ out,
-                 unsigned long long nbytes, unsigned int* __restrict__ status) {
+// The copy pipeline of one thread block (its thread 0).  nbytes: multiple of 16; in/out: 16-byte
+// aligned.  A barrier wait that runs out is reported in status[blockIdx.x] (PER_BLOCK: one word
+// per block, set to 1) or counted in status[0].
+template <bool PER_BLOCK>
+__device__ __forceinline__ void bulk_copy_block(const unsigned char* __restrict__ in, unsigned char* __restrict__ out,
+                                                unsigned long long nbytes, unsigned int* __restrict__ status) {
   extern __shared__ __align__(128) unsigned char stages[];
   __shared__ __align__(8) unsigned long long full[kBulkStages];
   if (threadIdx.x != 0) return;  // the copy engine does the work; one thread issues and waits
@@ -116,13 +118,20 @@ bulk_copy_kernel(const unsigned char* __restrict__ in, unsigned char* __restrict
     }
   }
   if (failed) {
-    atomicAdd(status, 1u);
+    if (PER_BLOCK) status[blockIdx.x] = 1u;
+    else atomicAdd(status, 1u);
     // loads i .. issued-1 may still be in flight: give each its (bounded) chance to land so that
     // nothing is written into this block's shared memory after it has exited
     for (unsigned long long j = i; j < issued; j++)
       mbar_wait_bounded(bar0 + 8u * (uint32_t)(j % kBulkStages), (uint32_t)((j / kBulkStages) & 1ull));
   }
   bulk_wait_all();
+}
+
+__global__ void __launch_bounds__(32, 1)
+bulk_copy_kernel(const unsigned char* __restrict__ in, unsigned char* __restrict__ out,
+                 unsigned long long nbytes, unsigned int* __restrict__ status) {
+  bulk_copy_block<false>(in, out, nbytes, status);
 }
 
 // Per-device status word (timeouts observed by bulk_copy_kernel), allocated on first use.
@@ -177,7 +186,9 @@ cudaError_t launch_bulk_copy(const void* in, void* out, size_t bytes16, int numS
   return launch_bulk_copy_with_status(in, out, bytes16, numSM, st, stream);
 }
 
-// Timeouts counted on the current device since the library was loaded (synchronises the device).
+// Timeouts counted on the current device since the library was loaded.  Waits for all work on the
+// device first (cudaDeviceSynchronize: a plain blocking copy would not wait for streams created
+// with cudaStreamNonBlocking).
 int bulk_copy_timeouts() {
   int dev = 0;
   if (cudaGetDevice(&dev) != cudaSuccess) return -1;
@@ -189,6 +200,7 @@ int bulk_copy_timeouts() {
     st = it->second;
   }
   unsigned int v = 0;
+  if (cudaDeviceSynchronize() != cudaSuccess) return -1;
   if (cudaMemcpy(&v, st, sizeof v, cudaMemcpyDeviceToHost) != cudaSuccess) return -1;
   return (int)v;
 }
@@ -216,51 +228,7 @@ static __device__ __align__(256) unsigned int g_noalloc_status[kNoAllocMaxBlocks
 __global__ void __launch_bounds__(32, 1)
 bulk_copy_noalloc_kernel(const unsigned char* __restrict__ in, unsigned char* __restrict__ out,
                          unsigned long long nbytes, unsigned int* __restrict__ status) {
-  extern __shared__ __align__(128) unsigned char stages[];
-  __shared__ __align__(8) unsigned long long full[kBulkStages];
-  if (threadIdx.x != 0) return;
-  const uint32_t bar0 = shared_addr(full);
-  const uint32_t st0 = shared_addr(stages);
-  for (int s = 0; s < kBulkStages; s++) mbar_init(bar0 + 8u * s, 1);
-  asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
-  asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");
-
-  const unsigned long long nchunks = (nbytes + kBulkChunk - 1) / kBulkChunk;
-  const unsigned long long first = blockIdx.x, stride = gridDim.x;
-  if (first >= nchunks) return;
-  const unsigned long long nlocal = (nchunks - first + stride - 1) / stride;
-  unsigned long long issued = 0, i = 0;
-  bool failed = false;
-  while (issued < nlocal && issued < (unsigned long long)kBulkStages) {
-    const unsigned long long off = (first + issued * stride) * kBulkChunk;
-    const uint32_t bytes = nbytes - off < kBulkChunk ? (uint32_t)(nbytes - off) : kBulkChunk;
-    const uint32_t s = (uint32_t)(issued % kBulkStages);
-    mbar_expect_tx(bar0 + 8u * s, bytes);
-    bulk_g2s(st0 + s * kBulkChunk, in + off, bytes, bar0 + 8u * s);
-    issued++;
-  }
-  for (; i < nlocal; i++) {
-    const uint32_t s = (uint32_t)(i % kBulkStages);
-    if (!mbar_wait_bounded(bar0 + 8u * s, (uint32_t)((i / kBulkStages) & 1ull))) { failed = true; break; }
-    const unsigned long long off = (first + i * stride) * kBulkChunk;
-    const uint32_t bytes = nbytes - off < kBulkChunk ? (uint32_t)(nbytes - off) : kBulkChunk;
-    bulk_s2g(out + off, st0 + s * kBulkChunk, bytes);
-    bulk_commit();
-    if (issued < nlocal) {
-      bulk_wait_read_all();
-      const unsigned long long noff = (first + issued * stride) * kBulkChunk;
-      const uint32_t nb = nbytes - noff < kBulkChunk ? (uint32_t)(nbytes - noff) : kBulkChunk;
-      mbar_expect_tx(bar0 + 8u * s, nb);
-      bulk_g2s(st0 + s * kBulkChunk, in + noff, nb, bar0 + 8u * s);
-      issued++;
-    }
-  }
-  if (failed) {
-    status[blockIdx.x] = 1u;
-    for (unsigned long long j = i; j < issued; j++)
-      mbar_wait_bounded(bar0 + 8u * (uint32_t)(j % kBulkStages), (uint32_t)((j / kBulkStages) & 1ull));
-  }
-  bulk_wait_all();
+  bulk_copy_block<true>(in, out, nbytes, status);
 }
 
 struct NoAllocDevice {
@@ -296,8 +264,9 @@ static cudaError_t noalloc_setup(int dev, NoAllocDevice& out) {
 extern "C" {
 
 // Declared in include/cutt_c.h.  0 success, 2 invalid parameter (null or misaligned pointers, size
-// not a multiple of 16, size over the limit, more thread blocks needed than status words exist),
-// 4 a CUDA call failed.
+// not a multiple of 16, size over the limit), 4 a CUDA call failed.  The launch uses one thread
+// block per SM but never more than the array has status words (the kernel strides over the
+// chunks, so a smaller grid only means more chunks per block).
 int cutt_c_copy_noalloc(const void* src, void* dst, size_t bytes, void* stream) {
   using namespace cuttb;
   if (!src || !dst || src == dst) return 2;
@@ -312,22 +281,21 @@ int cutt_c_copy_noalloc(const void* src, void* dst, size_t bytes, void* stream) 
   NoAllocDevice d;
   if (noalloc_setup(dev, d) != cudaSuccess) { cudaGetLastError(); return 4; }
   const unsigned long long nchunks = ((unsigned long long)bytes + kBulkChunk - 1) / kBulkChunk;
-  const unsigned long long want = nchunks < (unsigned long long)d.numSM ? nchunks : (unsigned long long)d.numSM;
-  if (want > (unsigned long long)kNoAllocMaxBlocks) {
-    fprintf(stderr, "cutt_c_copy_noalloc: the launch needs %llu status words, the fixed array holds %d\n", want, kNoAllocMaxBlocks);
-    return 2;
-  }
+  unsigned long long want = nchunks < (unsigned long long)d.numSM ? nchunks : (unsigned long long)d.numSM;
+  if (want > (unsigned long long)kNoAllocMaxBlocks) want = kNoAllocMaxBlocks;
   const int grid = (int)want;
   cudaStream_t st = (cudaStream_t)stream;
-  // the array keeps what the previous call left: this call's words start at zero
-  if (cudaMemsetAsync(d.status, 0, sizeof(unsigned int) * grid, st) != cudaSuccess) { cudaGetLastError(); return 4; }
+  // the array keeps what earlier calls left (a larger launch may have set words this one does not
+  // use): the whole array starts at zero for every call
+  if (cudaMemsetAsync(d.status, 0, sizeof(unsigned int) * kNoAllocMaxBlocks, st) != cudaSuccess) { cudaGetLastError(); return 4; }
   bulk_copy_noalloc_kernel<<<grid, 32, kBulkStages * (int)kBulkChunk, st>>>(
       (const unsigned char*)src, (unsigned char*)dst, (unsigned long long)bytes, d.status);
   return cudaGetLastError() == cudaSuccess ? 0 : 4;
 }
 
-// Barrier waits that ran out during the most recent cutt_c_copy_noalloc on the current device
-// (0 in a healthy run).  Synchronises the device; -1 on error or before the first call.
+// Thread blocks whose barrier wait ran out during the most recent cutt_c_copy_noalloc on the
+// current device (0 in a healthy run).  Waits for all work on the device, whatever stream it is on
+// (cudaDeviceSynchronize), before reading the words; -1 on error or before the first call.
 int cutt_c_copy_noalloc_timeouts(void) {
   using namespace cuttb;
   int dev = 0;
@@ -340,6 +308,7 @@ int cutt_c_copy_noalloc_timeouts(void) {
     d = it->second;
   }
   unsigned int host[kNoAllocMaxBlocks];
+  if (cudaDeviceSynchronize() != cudaSuccess) { cudaGetLastError(); return -1; }
   if (cudaMemcpy(host, d.status, sizeof host, cudaMemcpyDeviceToHost) != cudaSuccess) { cudaGetLastError(); return -1; }
   int n = 0;
   for (int b = 0; b < kNoAllocMaxBlocks; b++) n += host[b] ? 1 : 0;

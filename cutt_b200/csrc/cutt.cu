@@ -45,8 +45,8 @@ struct Plan {
   bool haveFallback = false;
   Candidate fallback;      // same tile with element-sized accesses, for unaligned pointers
   int fallbackGrid = 0;
-  NaiveDesc naive;
-  int numSM = 148;
+  NaiveDesc naive{};
+  int numSM = 0;           // set from the device when the plan is made
   std::string note;
   // multi-GPU plans (cutt_mg.h)
   int mgWorld = 0;
@@ -55,7 +55,7 @@ struct Plan {
   long long mgLocalVolume = 0;
   // plans of the extension entry points (element sizes 1, 2, 16)
   int extBytes = 0;        // the caller's element size; 0 for ordinary plans
-  SmallDesc small;         // kMethodSmall
+  SmallDesc small{};       // kMethodSmall
 };
 
 struct CachedChoice {
@@ -102,7 +102,9 @@ class PlanCache {
 };
 
 std::mutex g_mutex;
-std::unordered_map<cuttHandle, std::unique_ptr<Plan>> g_plans;
+// Plans are shared: cuttExecute copies the pointer under the lock and keeps the plan alive while it
+// launches, so a concurrent cuttDestroy cannot free it under the launch.
+std::unordered_map<cuttHandle, std::shared_ptr<Plan>> g_plans;
 cuttHandle g_nextHandle = 0;
 std::unordered_map<int, DeviceInfo> g_devices;
 
@@ -207,7 +209,7 @@ cudaError_t run_plan(const Plan& p, const void* in, void* out, cudaStream_t stre
       ((uintptr_t)in % p.elt || (uintptr_t)out % p.elt)) {
     // a re-stated problem moves 4- or 8-byte units; buffers aligned for the caller's smaller
     // type only are permuted element by element
-    return launch_naive(p.naive, in, out, stream);
+    return launch_naive(p.naive, p.numSM, in, out, stream);
   }
   switch (p.method) {
     case kMethodSmall:
@@ -217,7 +219,7 @@ cudaError_t run_plan(const Plan& p, const void* in, void* out, cudaStream_t stre
     case kMethodCopy:
       return launch_copy(in, out, p.bytes, p.numSM, stream);
     case kMethodNaive:
-      return launch_naive(p.naive, in, out, stream);
+      return launch_naive(p.naive, p.numSM, in, out, stream);
     case kMethodRowCopy:
       if ((uintptr_t)in % p.elt || (uintptr_t)out % p.elt) return cudaErrorInvalidValue;
       return launch_rowcopy(p.cand.rc, p.numSM, in, out, stream);
@@ -227,7 +229,7 @@ cudaError_t run_plan(const Plan& p, const void* in, void* out, cudaStream_t stre
       if (tiles_pointers_aligned(p.cand, in, out)) return launch_tiles(p.cand, p.grid, in, pp, stream);
       if (p.haveFallback) return launch_tiles(p.fallback, p.fallbackGrid, in, pp, stream);
       if (p.mgMode >= 1) return cudaErrorInvalidValue;
-      return launch_naive(p.naive, in, out, stream);
+      return launch_naive(p.naive, p.numSM, in, out, stream);
     }
   }
   return cudaErrorInvalidValue;
@@ -298,11 +300,29 @@ struct PlanRequest {
   bool ext = false;            // extension entry point: element sizes 1, 2 and 16 as well
 };
 
+// Values a tile parameter set may take (what the enumerator and the test entry point produce);
+// anything else in a persisted plan cache is a damaged or foreign entry.
+bool valid_tile_params(const TileParams& t) {
+  auto one_of = [](int v, std::initializer_list<int> ok) {
+    for (int x : ok) if (v == x) return true;
+    return false;
+  };
+  return one_of(t.nthreads, {64, 128, 256, 512}) && one_of(t.stages, {1, 2}) &&
+         one_of(t.maxVecBytes, {4, 8, 16}) && one_of(t.maxVBytes, {4, 8, 16}) &&
+         one_of(t.extend, {0, 1}) && one_of(t.loopOrder, {0, 1}) && one_of(t.groupIn, {1, 2, 4}) &&
+         one_of(t.groupOut, {1, 2, 4}) && one_of(t.cutInRun, {0, 1}) && one_of(t.allowAof, {0, 1}) &&
+         one_of(t.oneTilePerBlock, {0, 1}) && t.tinBytes >= 4 && t.tinBytes <= (1u << 16) &&
+         t.toutBytes >= 4 && t.toutBytes <= (1u << 16) && t.vtargetBytes >= 4 && t.vtargetBytes <= (1u << 20);
+}
+
+// With `internalOut` the plan is handed to the caller instead of entering the public handle table
+// (no handle number is consumed): plans the library makes for its own use.
 cuttResult make_plan(cuttHandle* handle, int rank, const int* dim, const int* perm, size_t elt,
-                     cudaStream_t stream, const PlanRequest& req) {
+                     cudaStream_t stream, const PlanRequest& req,
+                     std::shared_ptr<Plan>* internalOut = nullptr) {
   cuttResult chk = check_input(rank, dim, perm, elt, req.ext);
   if (chk != CUTT_SUCCESS) return chk;
-  if (!handle) return CUTT_INVALID_PARAMETER;
+  if (!handle && !internalOut) return CUTT_INVALID_PARAMETER;
   const bool extSize = req.ext && elt != 4 && elt != 8;
   if (extSize && (rank > 31 || req.world > 0 || req.chunkLast > 0 ||
                   (req.mode != kByModel && req.mode != kByMeasure)))
@@ -310,14 +330,16 @@ cuttResult make_plan(cuttHandle* handle, int rank, const int* dim, const int* pe
   if (req.mode == kByMeasure && req.idata == req.odata) return CUTT_INVALID_PARAMETER;
 
   std::unique_lock<std::mutex> lk(g_mutex);
-  *handle = g_nextHandle++;
-  if (g_plans.count(*handle)) return CUTT_INTERNAL_ERROR;
+  if (!internalOut) {
+    *handle = g_nextHandle++;
+    if (g_plans.count(*handle)) return CUTT_INTERNAL_ERROR;
+  }
 
   int devId = 0;
   DeviceInfo dev;
   if (!device_info(devId, dev)) return CUTT_INTERNAL_ERROR;
 
-  std::unique_ptr<Plan> p(new Plan);
+  std::shared_ptr<Plan> p(new Plan);
   p->device = devId;
   p->stream = stream;
   p->elt = (int)elt;
@@ -420,17 +442,30 @@ cuttResult make_plan(cuttHandle* handle, int rank, const int* dim, const int* pe
       CachedChoice cc;
       bool hit = plan_cache().get(key, cc);
       if (hit) {
+        // An entry is only a hint (the cache may come from a file): it is used when it describes
+        // a legal plan for THIS problem, and ignored - the model or the measurement decides -
+        // otherwise.  Copy methods are legal for identity permutations only.
         if (cc.method == kMethodTiles) {
           Candidate c;
-          ok = build_tile(p->prob, cc.params, dev, c) && adopt_candidate(*p, dev, c);
+          ok = !p->prob.identity && valid_tile_params(cc.params) && build_tile(p->prob, cc.params, dev, c) &&
+               adopt_candidate(*p, dev, c);
         } else if (cc.method == kMethodRowCopy) {
           Candidate c;
           ok = build_rowcopy(p->prob, dev, c) && adopt_candidate(*p, dev, c);
-        } else {
-          p->method = cc.method;
-          ok = true;
+        } else if (cc.method == kMethodCopy || cc.method == kMethodMemcpy) {
+          ok = p->prob.identity;
+          if (ok) p->method = cc.method;
         }
         if (ok) p->note = "cache";
+        if (ok && req.mode == kByMeasure) {
+          // nothing is timed, but the visible effects of cuttPlanMeasure stay those of
+          // src/cutt.cpp:240-250: odata is overwritten and the device is synchronised
+          if (cudaMemsetAsync(measureOut, 0xFF, p->bytes, stream) != cudaSuccess ||
+              cudaDeviceSynchronize() != cudaSuccess) {
+            cudaGetLastError();
+            return CUTT_INTERNAL_ERROR;
+          }
+        }
       }
       if (!ok && req.mode == kByModel) {
         for (size_t i = 0; i < cands.size() && !ok; i++) ok = adopt_candidate(*p, dev, cands[i]);
@@ -554,7 +589,8 @@ cuttResult make_plan(cuttHandle* handle, int rank, const int* dim, const int* pe
     fprintf(stderr, "[cutt] plan %u (%s): %s\n", *handle, p->note.c_str(),
             canon ? describe(p->prob, shown).c_str() : "naive (rank too high after fusion)");
   }
-  g_plans[*handle] = std::move(p);
+  if (internalOut) *internalOut = p;
+  else g_plans[*handle] = p;
   return CUTT_SUCCESS;
 }
 
@@ -588,12 +624,12 @@ cuttResult cuttDestroy(cuttHandle handle) {
 }
 
 cuttResult cuttExecute(cuttHandle handle, void* idata, void* odata) {
-  const Plan* p = nullptr;
+  std::shared_ptr<Plan> p;
   {
     std::lock_guard<std::mutex> lk(g_mutex);
     auto it = g_plans.find(handle);
     if (it == g_plans.end()) return CUTT_INVALID_PLAN;
-    p = it->second.get();
+    p = it->second;
   }
   if (idata == odata) return CUTT_INVALID_PARAMETER;
   if (p->mgMode == 1) return CUTT_INVALID_PARAMETER;  // needs the peers' slabs: cutt_mg_execute
@@ -606,6 +642,37 @@ cuttResult cuttExecute(cuttHandle handle, void* idata, void* odata) {
   if (dev != p->device) return CUTT_INVALID_DEVICE;
   return run_plan(*p, idata, odata, p->stream) == cudaSuccess ? CUTT_SUCCESS : CUTT_INTERNAL_ERROR;
 }
+
+// ---------------------------------------------------------------------------------------
+// Host-buffer pipeline state (cutt_c_transpose_host), one per device: scratch buffers (grown on
+// demand, kept), three streams, events and the plans of recent problems.  The plans are the
+// library's own: they never enter the public handle table, and the least recently used one is
+// dropped beyond kHostPlanLimit.
+namespace {
+
+struct HostPipe {
+  void* dIn = nullptr;
+  void* dOut = nullptr;
+  size_t cap = 0;
+  cudaStream_t sUp = nullptr, sRun = nullptr, sDown = nullptr;
+  std::vector<cudaEvent_t> evUp, evRun;
+  std::list<std::pair<std::string, std::shared_ptr<Plan>>> plans;  // most recently used first
+};
+constexpr size_t kHostPlanLimit = 64;
+std::mutex g_hostMutex;
+std::unordered_map<int, HostPipe> g_hostPipes;
+
+// Error exit of the pipeline: nothing may still be reading or writing the caller's host buffers
+// when the call returns.
+int host_pipe_fail(HostPipe& hp, int code) {
+  if (hp.sUp) cudaStreamSynchronize(hp.sUp);
+  if (hp.sRun) cudaStreamSynchronize(hp.sRun);
+  if (hp.sDown) cudaStreamSynchronize(hp.sDown);
+  cudaGetLastError();
+  return code;
+}
+
+}  // namespace
 
 // ---------------------------------------------------------------------------------------
 // C ABI (include/cutt_c.h)
@@ -705,46 +772,38 @@ int cutt_c_plan_params(unsigned int* handle, int rank, const int* dim, const int
 
 int cutt_c_transpose_host(int rank, const int* dim, const int* permutation, size_t sizeofType,
                           const void* hin, void* hout) {
-  // Device scratch (one pair of buffers per process, grown on demand, kept), three streams and a
-  // few events; calls are serialised.  Large tensors are cut into slabs along the slowest input
-  // dimension so that the upload of slab k+1, the kernel of slab k and the download of slab k-1
-  // overlap (PCIe is full duplex); each slab is permuted straight into its strided place in the
-  // device output, which is downloaded with a 2-D copy.
-  static std::mutex hostMutex;
-  static void* dIn = nullptr;
-  static void* dOut = nullptr;
-  static size_t cap = 0;
-  static int capDev = -1;
-  static cudaStream_t sUp = nullptr, sRun = nullptr, sDown = nullptr;
-  static std::vector<cudaEvent_t> evUp, evRun;
-  static std::unordered_map<std::string, cuttHandle> plans;
+  // Calls are serialised.  Large tensors are cut into slabs along the slowest input dimension so
+  // that the upload of slab k+1, the kernel of slab k and the download of slab k-1 overlap (PCIe
+  // is full duplex); each slab is permuted straight into its strided place in the device output,
+  // which is downloaded with a 2-D copy.
   if (check_input(rank, dim, permutation, sizeofType) != CUTT_SUCCESS) return CUTT_INVALID_PARAMETER;
   if (!hin || !hout) return CUTT_INVALID_PARAMETER;
-  std::lock_guard<std::mutex> lk(hostMutex);
+  std::lock_guard<std::mutex> lk(g_hostMutex);
   int dev = 0;
   if (cudaGetDevice(&dev) != cudaSuccess) return CUTT_INTERNAL_ERROR;
+  HostPipe& hp = g_hostPipes[dev];
   size_t bytes = sizeofType;
   for (int i = 0; i < rank; i++) bytes *= (size_t)dim[i];
-  if (dev != capDev && capDev >= 0) return CUTT_INVALID_DEVICE;  // the scratch belongs to the first device used
-  if (bytes > cap) {
-    if (dIn) cudaFree(dIn);
-    if (dOut) cudaFree(dOut);
-    dIn = dOut = nullptr;
-    cap = 0;
-    if (cudaMalloc(&dIn, bytes) != cudaSuccess || cudaMalloc(&dOut, bytes) != cudaSuccess) {
-      if (dIn) cudaFree(dIn);
-      dIn = dOut = nullptr;
+  if (bytes > hp.cap) {
+    if (hp.dIn) cudaFree(hp.dIn);
+    if (hp.dOut) cudaFree(hp.dOut);
+    hp.dIn = hp.dOut = nullptr;
+    hp.cap = 0;
+    if (cudaMalloc(&hp.dIn, bytes) != cudaSuccess || cudaMalloc(&hp.dOut, bytes) != cudaSuccess) {
+      if (hp.dIn) cudaFree(hp.dIn);
+      hp.dIn = hp.dOut = nullptr;
       cudaGetLastError();
       return CUTT_INTERNAL_ERROR;
     }
-    cap = bytes;
-    capDev = dev;
+    hp.cap = bytes;
   }
-  if (!sUp) {
-    if (cudaStreamCreateWithFlags(&sUp, cudaStreamNonBlocking) != cudaSuccess ||
-        cudaStreamCreateWithFlags(&sRun, cudaStreamNonBlocking) != cudaSuccess ||
-        cudaStreamCreateWithFlags(&sDown, cudaStreamNonBlocking) != cudaSuccess)
+  if (!hp.sDown) {
+    if ((!hp.sUp && cudaStreamCreateWithFlags(&hp.sUp, cudaStreamNonBlocking) != cudaSuccess) ||
+        (!hp.sRun && cudaStreamCreateWithFlags(&hp.sRun, cudaStreamNonBlocking) != cudaSuccess) ||
+        cudaStreamCreateWithFlags(&hp.sDown, cudaStreamNonBlocking) != cudaSuccess) {
+      cudaGetLastError();
       return CUTT_INTERNAL_ERROR;
+    }
   }
   const int last = rank - 1;
   const int dlast = dim[last];
@@ -770,55 +829,58 @@ int cutt_c_transpose_host(int rank, const int* dim, const int* permutation, size
   int chunk = (dlast + nslab - 1) / nslab;
   if (nslab > 1 && chunk >= 32) chunk = (chunk + 15) / 16 * 16;  // keeps slab offsets 16-byte aligned
   nslab = (dlast + chunk - 1) / chunk;
-  while ((int)evUp.size() < nslab) {
+  while ((int)hp.evUp.size() < nslab) {
     cudaEvent_t a, b;
-    if (cudaEventCreateWithFlags(&a, cudaEventDisableTiming) != cudaSuccess ||
-        cudaEventCreateWithFlags(&b, cudaEventDisableTiming) != cudaSuccess)
+    if (cudaEventCreateWithFlags(&a, cudaEventDisableTiming) != cudaSuccess) { cudaGetLastError(); return CUTT_INTERNAL_ERROR; }
+    if (cudaEventCreateWithFlags(&b, cudaEventDisableTiming) != cudaSuccess) {
+      cudaEventDestroy(a);
+      cudaGetLastError();
       return CUTT_INTERNAL_ERROR;
-    evUp.push_back(a);
-    evRun.push_back(b);
+    }
+    hp.evUp.push_back(a);
+    hp.evRun.push_back(b);
   }
-  auto plan_for = [&](int extent, cuttHandle& h) -> cuttResult {
-    std::string key = problem_key(dev, rank, dim, permutation, sizeofType) + "/host" + std::to_string(extent);
-    auto it = plans.find(key);
-    if (it != plans.end()) { h = it->second; return CUTT_SUCCESS; }
+  auto plan_for = [&](int extent, std::shared_ptr<Plan>& out) -> cuttResult {
+    const std::string key = problem_key(dev, rank, dim, permutation, sizeofType) + "/host" + std::to_string(extent);
+    for (auto it = hp.plans.begin(); it != hp.plans.end(); ++it) {
+      if (it->first != key) continue;
+      out = it->second;
+      hp.plans.splice(hp.plans.begin(), hp.plans, it);
+      return CUTT_SUCCESS;
+    }
     PlanRequest req;
     if (extent != dlast) req.chunkLast = extent;
-    cuttResult r = make_plan(&h, rank, dim, permutation, sizeofType, sRun, req);
-    if (r == CUTT_SUCCESS) plans[key] = h;
-    return r;
+    cuttResult r = make_plan(nullptr, rank, dim, permutation, sizeofType, hp.sRun, req, &out);
+    if (r != CUTT_SUCCESS) return r;
+    hp.plans.emplace_front(key, out);
+    while (hp.plans.size() > kHostPlanLimit) hp.plans.pop_back();
+    return CUTT_SUCCESS;
   };
   for (int k = 0; k < nslab; k++) {
     const int c0 = k * chunk;
     const int ext = (c0 + chunk <= dlast) ? chunk : dlast - c0;
-    cuttHandle h;
-    cuttResult r = plan_for(ext, h);
-    if (r != CUTT_SUCCESS) return r;
+    std::shared_ptr<Plan> p;
+    cuttResult r = plan_for(ext, p);
+    if (r != CUTT_SUCCESS) return host_pipe_fail(hp, r);
     const size_t inOff = (size_t)c0 * isLast * sizeofType;
     const size_t inBytes = (size_t)ext * isLast * sizeofType;
     const size_t outOff = (size_t)c0 * osLast * sizeofType;
     const size_t width = (size_t)ext * osLast * sizeofType;
-    if (cudaMemcpyAsync((char*)dIn + inOff, (const char*)hin + inOff, inBytes, cudaMemcpyHostToDevice, sUp) != cudaSuccess ||
-        cudaEventRecord(evUp[k], sUp) != cudaSuccess || cudaStreamWaitEvent(sRun, evUp[k], 0) != cudaSuccess)
-      return CUTT_INTERNAL_ERROR;
-    const Plan* p = nullptr;
-    {
-      std::lock_guard<std::mutex> lk2(g_mutex);
-      auto it = g_plans.find(h);
-      if (it == g_plans.end()) return CUTT_INTERNAL_ERROR;
-      p = it->second.get();
-    }
-    if (run_plan(*p, (char*)dIn + inOff, (char*)dOut + outOff, sRun) != cudaSuccess) return CUTT_INTERNAL_ERROR;
-    if (cudaEventRecord(evRun[k], sRun) != cudaSuccess || cudaStreamWaitEvent(sDown, evRun[k], 0) != cudaSuccess)
-      return CUTT_INTERNAL_ERROR;
+    if (cudaMemcpyAsync((char*)hp.dIn + inOff, (const char*)hin + inOff, inBytes, cudaMemcpyHostToDevice, hp.sUp) != cudaSuccess ||
+        cudaEventRecord(hp.evUp[k], hp.sUp) != cudaSuccess || cudaStreamWaitEvent(hp.sRun, hp.evUp[k], 0) != cudaSuccess)
+      return host_pipe_fail(hp, CUTT_INTERNAL_ERROR);
+    if (run_plan(*p, (char*)hp.dIn + inOff, (char*)hp.dOut + outOff, hp.sRun) != cudaSuccess)
+      return host_pipe_fail(hp, CUTT_INTERNAL_ERROR);
+    if (cudaEventRecord(hp.evRun[k], hp.sRun) != cudaSuccess || cudaStreamWaitEvent(hp.sDown, hp.evRun[k], 0) != cudaSuccess)
+      return host_pipe_fail(hp, CUTT_INTERNAL_ERROR);
     cudaError_t e;
-    if (nslab == 1) e = cudaMemcpyAsync(hout, dOut, bytes, cudaMemcpyDeviceToHost, sDown);
-    else if (height == 1) e = cudaMemcpyAsync((char*)hout + outOff, (char*)dOut + outOff, width, cudaMemcpyDeviceToHost, sDown);
-    else e = cudaMemcpy2DAsync((char*)hout + outOff, pitch, (char*)dOut + outOff, pitch, width, height,
-                               cudaMemcpyDeviceToHost, sDown);
-    if (e != cudaSuccess) return CUTT_INTERNAL_ERROR;
+    if (nslab == 1) e = cudaMemcpyAsync(hout, hp.dOut, bytes, cudaMemcpyDeviceToHost, hp.sDown);
+    else if (height == 1) e = cudaMemcpyAsync((char*)hout + outOff, (char*)hp.dOut + outOff, width, cudaMemcpyDeviceToHost, hp.sDown);
+    else e = cudaMemcpy2DAsync((char*)hout + outOff, pitch, (char*)hp.dOut + outOff, pitch, width, height,
+                               cudaMemcpyDeviceToHost, hp.sDown);
+    if (e != cudaSuccess) return host_pipe_fail(hp, CUTT_INTERNAL_ERROR);
   }
-  if (cudaStreamSynchronize(sDown) != cudaSuccess) return CUTT_INTERNAL_ERROR;
+  if (cudaStreamSynchronize(hp.sDown) != cudaSuccess) return host_pipe_fail(hp, CUTT_INTERNAL_ERROR);
   return CUTT_SUCCESS;
 }
 
@@ -862,12 +924,12 @@ long long cutt_mg_local_volume(unsigned int handle) {
 }
 
 int cutt_mg_execute(unsigned int handle, void* idata, void* const* odata) {
-  const Plan* p = nullptr;
+  std::shared_ptr<Plan> p;
   {
     std::lock_guard<std::mutex> lk(g_mutex);
     auto it = g_plans.find(handle);
     if (it == g_plans.end()) return CUTT_INVALID_PLAN;
-    p = it->second.get();
+    p = it->second;
   }
   if (p->mgWorld == 0 || !odata || !idata) return CUTT_INVALID_PARAMETER;
   for (int h = 0; h < p->mgWorld; h++)
@@ -966,10 +1028,19 @@ unsigned long long cutt_c_launch_count(void) { return launch_count(); }
 
 int cutt_c_copy_timeouts(void) { return bulk_copy_timeouts(); }
 
+void cutt_c_debug_force_wide(int on) {
+  std::lock_guard<std::mutex> lk(g_mutex);
+  debug_force_wide_offsets(on != 0);
+  g_enumKey.clear();   // candidate lists built so far no longer apply
+  g_enumList.clear();
+}
+
 void cutt_c_clear_plan_cache(void) {
   std::lock_guard<std::mutex> lk(g_mutex);
   plan_cache().clear();
 }
+
+static const char kPlanCacheHeader[] = "# cutt-b200 plan cache v3";
 
 // One line per entry: key, method and the tile parameters of the measured winner.
 int cutt_c_plan_cache_save(const char* path) {
@@ -977,7 +1048,7 @@ int cutt_c_plan_cache_save(const char* path) {
   std::lock_guard<std::mutex> lk(g_mutex);
   FILE* f = fopen(path, "w");
   if (!f) return CUTT_INTERNAL_ERROR;
-  fprintf(f, "# cutt-b200 plan cache v3\n");
+  fprintf(f, "%s\n", kPlanCacheHeader);
   plan_cache().for_each_oldest_first([&](const std::string& k, const CachedChoice& c) {
     const TileParams& t = c.params;
     fprintf(f, "%s %d %u %u %u %d %d %d %d %d %d %d %d %d %d %d\n", k.c_str(), (int)c.method, t.tinBytes, t.toutBytes,
@@ -988,12 +1059,22 @@ int cutt_c_plan_cache_save(const char* path) {
   return CUTT_SUCCESS;
 }
 
+// Only files written by cutt_c_plan_cache_save of this format version are accepted (first line =
+// the version header); lines whose method or tile parameters are out of range are skipped.  What
+// is loaded is still only a hint: cuttPlan re-validates every entry against the problem it is
+// asked to plan before using it.
 int cutt_c_plan_cache_load(const char* path) {
   if (!path) return CUTT_INVALID_PARAMETER;
   std::lock_guard<std::mutex> lk(g_mutex);
   FILE* f = fopen(path, "r");
   if (!f) return CUTT_INVALID_PARAMETER;
   char line[1024];
+  const size_t hl = strlen(kPlanCacheHeader);
+  if (!fgets(line, sizeof line, f) || strncmp(line, kPlanCacheHeader, hl) != 0 ||
+      (line[hl] != '\n' && line[hl] != '\r' && line[hl] != '\0')) {
+    fclose(f);
+    return CUTT_INVALID_PARAMETER;
+  }
   int n = 0;
   while (fgets(line, sizeof line, f)) {
     if (line[0] == '#') continue;
@@ -1005,7 +1086,9 @@ int cutt_c_plan_cache_load(const char* path) {
                &t.vtargetBytes, &t.extend, &t.nthreads, &t.stages, &t.maxVecBytes, &t.maxVBytes,
                &t.loopOrder, &t.groupIn, &t.groupOut, &t.cutInRun, &t.allowAof, &t.oneTilePerBlock) != 16)
       continue;
-    if (method < 0 || method > (int)kMethodRowCopy) continue;
+    // winners are tiled plans, row copies or (identity permutations) the two copy methods
+    if (method != kMethodTiles && method != kMethodRowCopy && method != kMethodCopy && method != kMethodMemcpy) continue;
+    if (method == kMethodTiles && !valid_tile_params(t)) continue;
     c.method = (Method)method;
     plan_cache().put(key, c);
     n++;

@@ -146,10 +146,12 @@ static DeviceInfo g_dev;
 
 // Candidate list of the last problem asked for (tests run candidate 0, 1, 2, ... of one problem
 // in a row; enumerating is the expensive part).
+static bool g_candidatesStale = false;
 static const std::vector<Candidate>& candidates_of(const Problem& P) {
   static Problem last;
   static std::vector<Candidate> list;
   static bool have = false;
+  if (g_candidatesStale) { have = false; g_candidatesStale = false; }
   bool same = have && last.rank == P.rank && last.elt == P.elt && last.peerDim == P.peerDim &&
               last.inBase == P.inBase && last.outBase == P.outBase && last.inElems == P.inElems;
   for (int j = 0; same && j < P.rank; j++)
@@ -351,6 +353,12 @@ long long cutt_hostcheck_fastdiv(unsigned d, unsigned long long nmax, unsigned l
   const uint32_t edge[] = {0u, 1u, d - 1, d, d + 1, 0x7fffffffu, 0x80000000u, 0xfffffffeu, 0xffffffffu};
   for (uint32_t n : edge) if (fdiv(n, f) != n / d) bad++;
   return bad;
+}
+
+// Builds every tile with 64-bit row offsets from now on (on != 0) or as the planner decides.
+void cutt_hostcheck_force_wide(int on) {
+  debug_force_wide_offsets(on != 0);
+  g_candidatesStale = true;
 }
 
 }  // extern "C"

@@ -275,10 +275,11 @@ naive_kernel(const __grid_constant__ NaiveDesc d, const T* __restrict__ in, T* _
   }
 }
 
-cudaError_t launch_naive(const NaiveDesc& d, const void* in, void* out, cudaStream_t stream) {
+cudaError_t launch_naive(const NaiveDesc& d, int numSM, const void* in, void* out, cudaStream_t stream) {
   const int threads = 256;
   unsigned long long want = (d.volume + threads - 1) / threads;
-  int grid = (int)(want < 148ull * 16 ? want : 148ull * 16);
+  const unsigned long long cap = (unsigned long long)(numSM > 0 ? numSM : 1) * 16;
+  int grid = (int)(want < cap ? want : cap);
   if (grid < 1) grid = 1;
   if (d.elt == 4) naive_kernel<uint32_t><<<grid, threads, 0, stream>>>(d, (const uint32_t*)in, (uint32_t*)out);
   else if (d.elt == 2) naive_kernel<uint16_t><<<grid, threads, 0, stream>>>(d, (const uint16_t*)in, (uint16_t*)out);

@@ -29,7 +29,7 @@ bool tiles_pointers_aligned(const Candidate& c, const void* in, const void* out)
 cudaError_t launch_tiles(const Candidate& c, int gridBlocks, const void* in, const PeerPtrs& outs,
                          cudaStream_t stream);
 cudaError_t launch_copy(const void* in, void* out, size_t bytes, int numSM, cudaStream_t stream);
-cudaError_t launch_naive(const NaiveDesc& d, const void* in, void* out, cudaStream_t stream);
+cudaError_t launch_naive(const NaiveDesc& d, int numSM, const void* in, void* out, cudaStream_t stream);
 
 // Bulk-copy-engine copy (bulk_copy.cu): both pointers 16-byte aligned, bytes16 a multiple of 16.
 bool bulk_copy_usable(const void* in, const void* out, size_t bytes);

@@ -11,6 +11,11 @@ namespace cuttb {
 
 static inline int64_t ceil_div(int64_t a, int64_t b) { return (a + b - 1) / b; }
 
+// Test aid: build every tile with 64-bit row offsets, so that the kernel variant which tensors of
+// 2^32 elements and more select is also exercised by small problems.
+static bool g_forceWideOffsets = false;
+void debug_force_wide_offsets(bool on) { g_forceWideOffsets = on; }
+
 bool canonicalize(int rank, const int64_t* d, const int64_t* is, const int64_t* os, int elt,
                   int peerDim, Problem& P) {
   struct Dim { int64_t d, is, os; bool peer; };
@@ -349,7 +354,7 @@ bool build_tile(const Problem& P, const TileParams& tp, const DeviceInfo& dev, C
   {
     int64_t spanIn = 1, spanOut = 1;
     for (int j = 0; j < r; j++) { spanIn += (t[j] - 1) * P.is[j]; spanOut += (t[j] - 1) * P.os[j]; }
-    wide = spanIn >= (1ll << 32) || spanOut >= (1ll << 32);
+    wide = spanIn >= (1ll << 32) || spanOut >= (1ll << 32) || g_forceWideOffsets;
   }
 
   // register blocking of the output side along dimension 0

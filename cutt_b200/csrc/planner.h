@@ -128,6 +128,10 @@ std::vector<Candidate> enumerate_candidates(const Problem& P, const DeviceInfo& 
 double analytic_cost(const Problem& P, const Candidate& c, const DeviceInfo& dev);
 double model_cost(const Problem& P, const Candidate& c, const DeviceInfo& dev);
 
+// Test aid: while on, every tile is built with 64-bit row offsets (the kernel variant that tiles
+// spanning 2^32 elements and more need).  Not thread-safe; meant for test processes only.
+void debug_force_wide_offsets(bool on);
+
 // One-line JSON description (used by tests and by CUTT_VERBOSE).
 std::string describe(const Problem& P, const Candidate& c);
 

@@ -69,6 +69,17 @@ def c3_cases(n: int = 100):
     return [generate_c3_case(i) for i in range(n)]
 
 
+def c3_holdout_cases(n: int = 100):
+    """Further cases of the same generator (seeds 2000 and up) that the planner's cost model was
+    never fitted to: its training sweep covered cases 0-199 (seeds 1000-1199)."""
+    return [generate_c3_case(1000 + i) for i in range(n)]
+
+
+# Bounded sample of the multi-GPU tensor for legs that run on the host cores or through host
+# buffers: the same permutation on a slab of 8 positions of the sharded dimension (1.07 GB per side).
+C5_SAMPLE_DIMS = [1024, 1024, 32, 8]
+
+
 def write_c3_file(n: int = 100):
     cases = [generate_c3_case(i) for i in range(n)]
     with open(C3_FILE, "w") as f:

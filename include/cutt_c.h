@@ -77,7 +77,7 @@ unsigned long long cutt_c_launch_count(void);
 
 /* The copy kernel used for identity permutations waits on hardware barriers with a poll limit;
  * this returns how many such waits have run out on the current device since the library was
- * loaded (0 in a healthy run; synchronises the device; -1 on error). */
+ * loaded (0 in a healthy run; waits for all work on the device first; -1 on error). */
 int cutt_c_copy_timeouts(void);
 
 /*
@@ -88,28 +88,39 @@ int cutt_c_copy_timeouts(void);
  * device's memory belongs to their own memory manager, or they run in a loop where the
  * device-wide synchronisation of an allocation is not tolerable.  The kernel is the bulk-copy
  * kernel used for identity permutations; the status words it needs are a fixed 1 KB array inside
- * the library image (256 words: one per thread block, so launches of up to 256 blocks), which
- * every GPU that loads the library holds until the process exits.
+ * the library image (256 words, one per thread block: a launch uses one block per SM and at most
+ * 256 blocks), which every GPU that loads the library holds until the process exits.
  *
  * Rules: src and dst are device pointers aligned to 16 bytes, bytes is a multiple of 16 and at
  * most 2^40; anything else returns CUTT_INVALID_PARAMETER (2) with a message on stderr for the
  * two size limits.  The first call on a device looks up the array's device address and sets the
  * kernel's shared-memory limit; make that first call before any stream capture begins.  All
- * calls share the one array and each call clears the words it uses, so two calls whose kernels
- * overlap on the GPU (different streams) race on it: issue them on one stream or order them
- * with events.  The copy is asynchronous on `stream`.
+ * calls share the one array and each call clears it on its stream before its kernel runs, so two
+ * calls whose kernels overlap on the GPU (different streams) race on it: issue them on one stream
+ * or order them with events.  The copy is asynchronous on `stream`.
  */
 int cutt_c_copy_noalloc(const void* src, void* dst, size_t bytes, void* stream);
 
-/* Hardware-barrier waits that ran out during the most recent cutt_c_copy_noalloc on the current
- * device (0 in a healthy run; synchronises the device; -1 before the first call or on error). */
+/* Thread blocks whose hardware-barrier wait ran out during the most recent cutt_c_copy_noalloc on
+ * the current device (0 in a healthy run; -1 before the first call or on error).  Waits for all
+ * work on the device, on every stream, before it reads the status words. */
 int cutt_c_copy_noalloc_timeouts(void);
+
+/* Test aid: while on (on != 0) every tiled plan is built with 64-bit row offsets, the kernel
+ * variant that otherwise only tiles spanning 2^32 elements or more select.  Affects plans made
+ * afterwards; meant for test processes, not thread-safe against concurrent planning. */
+void cutt_c_debug_force_wide(int on);
 
 /* Empties the plan cache (the cuttPlanMeasure winners). */
 void cutt_c_clear_plan_cache(void);
 
 /* Writes / reads the plan cache as a text file, so that winners measured in one process are
- * reused by cuttPlan and cuttPlanMeasure in the next.  Keys include the device ordinal. */
+ * reused by cuttPlan and cuttPlanMeasure in the next.  Keys include the device ordinal.
+ * Loading accepts only files with this format's version header and skips entries whose fields are
+ * out of range; a loaded entry is a hint that cuttPlan re-validates against the problem (a copy
+ * method is never used for a non-identity permutation).  cuttPlanMeasure served from the cache
+ * times nothing but still overwrites odata and synchronises the device, like the original
+ * (src/cutt.cpp:240-250). */
 int cutt_c_plan_cache_save(const char* path);
 int cutt_c_plan_cache_load(const char* path);
 int cutt_c_plan_cache_size(void);

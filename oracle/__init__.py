@@ -13,4 +13,5 @@ from .oracle import (  # noqa: F401
     source_index_formula_py,
     index_pattern,
     num_threads,
+    use_all_cores,
 )

@@ -20,10 +20,13 @@ SOURCES = ["cutt.cpp", "cuttplan.cpp", "cuttkernel.cu", "cuttGpuModel.cpp", "cut
            "CudaUtils.cu", "cuttTimer.cpp"]
 
 
-def build(reference_root: str = "/root/reference", force: bool = False):
-    src = os.path.join(reference_root, "src")
+def build(reference_root: str | None = None, force: bool = False):
+    """reference_root: checkout of the original library (argument, else $CUTT_REFERENCE_ROOT).
+    Without one, a library built earlier is kept and returned."""
+    reference_root = reference_root or os.environ.get("CUTT_REFERENCE_ROOT") or ""
+    src = os.path.join(reference_root, "src") if reference_root else ""
     lib = os.path.join(OUT, "libcutt_ref.so")
-    if not os.path.isdir(src):
+    if not src or not os.path.isdir(src):
         return lib if os.path.exists(lib) else None
     if os.path.exists(lib) and not force:
         return lib
@@ -43,4 +46,4 @@ def build(reference_root: str = "/root/reference", force: bool = False):
 
 
 if __name__ == "__main__":
-    print(build(force=True))
+    print(build(sys.argv[1] if len(sys.argv) > 1 else None, force=True))

@@ -180,3 +180,15 @@ int cutt_oracle_num_threads(void) {
   return 1;
 #endif
 }
+
+/* Sets the number of OpenMP threads later calls use (launchers such as torchrun export
+ * OMP_NUM_THREADS=1 to their children). Returns the value now in effect. */
+int cutt_oracle_set_num_threads(int n) {
+#ifdef _OPENMP
+  if (n >= 1) omp_set_num_threads(n);
+  return omp_get_max_threads();
+#else
+  (void)n;
+  return 1;
+#endif
+}

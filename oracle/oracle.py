@@ -52,6 +52,8 @@ def load():
         lib.cutt_oracle_check_input.argtypes = [ctypes.c_int, ip, ip, ctypes.c_size_t]
         lib.cutt_oracle_check_input.restype = ctypes.c_int
         lib.cutt_oracle_num_threads.restype = ctypes.c_int
+        lib.cutt_oracle_set_num_threads.argtypes = [ctypes.c_int]
+        lib.cutt_oracle_set_num_threads.restype = ctypes.c_int
         _lib = lib
     return _lib
 
@@ -67,13 +69,18 @@ def _as_words(a: np.ndarray, elt: int) -> np.ndarray:
     return a.view(np.uint32 if elt == 4 else np.uint64)
 
 
-def _call_c(name, dim, perm, a: np.ndarray) -> np.ndarray:
+def _call_c(name, dim, perm, a: np.ndarray, out: np.ndarray | None = None) -> np.ndarray:
     elt = a.dtype.itemsize
     src = _as_words(a, elt)
     vol = int(np.prod([int(d) for d in dim], dtype=np.int64))
     if src.size != vol:
         raise ValueError("input has %d elements, dims need %d" % (src.size, vol))
-    dst = np.empty_like(src)
+    if out is None:
+        dst = np.empty_like(src)
+    else:  # caller-owned output (timing loops: no allocation or page faults inside the loop)
+        if out.dtype.itemsize != elt or out.size != vol or not out.flags.c_contiguous:
+            raise ValueError("out must be a contiguous array of the input's shape and element size")
+        dst = out.reshape(-1).view(src.dtype)
     rc = getattr(load(), name)(len(dim), _iarr(dim), _iarr(perm), elt,
                                src.ctypes.data, dst.ctypes.data)
     if rc != 0:
@@ -86,9 +93,9 @@ def transpose_formula(dim, perm, a: np.ndarray) -> np.ndarray:
     return _call_c("cutt_oracle_formula", dim, perm, a)
 
 
-def transpose_blocked(dim, perm, a: np.ndarray) -> np.ndarray:
+def transpose_blocked(dim, perm, a: np.ndarray, out: np.ndarray | None = None) -> np.ndarray:
     """Blocked OpenMP loop nest (C); the CPU baseline of the benchmark."""
-    return _call_c("cutt_oracle_blocked", dim, perm, a)
+    return _call_c("cutt_oracle_blocked", dim, perm, a, out)
 
 
 def transpose_numpy(dim, perm, a: np.ndarray) -> np.ndarray:
@@ -121,3 +128,13 @@ def index_pattern(vol: int, elt: int) -> np.ndarray:
 
 def num_threads() -> int:
     return int(load().cutt_oracle_num_threads())
+
+
+def use_all_cores() -> int:
+    """Lets the OpenMP loops use every core this process may run on, whatever OMP_NUM_THREADS
+    the launcher exported.  Returns the thread count now in effect."""
+    try:
+        n = len(os.sched_getaffinity(0))
+    except AttributeError:
+        n = os.cpu_count() or 1
+    return int(load().cutt_oracle_set_num_threads(n))

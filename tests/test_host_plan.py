@@ -206,3 +206,34 @@ def test_candidate_descriptions_are_json(hc):
     assert hc.cutt_hostcheck_run(3, _iarr(dims), _iarr(perm), 4, 0, a.ctypes.data, out.ctypes.data, lab, 2048) == 0
     d = json.loads(lab.value.decode())
     assert d["fused_dims"] == [64, 48, 20] and d["elt"] == 4 and d["num_tiles"] >= 1
+
+
+def test_wide_row_offsets(hc, oracle_mod):
+    """The kernel variant with 64-bit row offsets (selected by tiles that span 2^32 elements or
+    more) on small problems: the planner is told to build every tile that way."""
+    hc.cutt_hostcheck_force_wide.argtypes = [ctypes.c_int]
+    hc.cutt_hostcheck_force_wide(1)
+    try:
+        rng = random.Random(77)
+        cases = [README_CASE, ([129, 130], [1, 0]), ([4, 3, 5, 40, 7, 24], [4, 1, 5, 0, 3, 2]),
+                 ([1305, 59, 8], [0, 2, 1]), ([64, 48, 20], [2, 1, 0])]
+        cases += [random_case(rng, r, 40_000) for r in (2, 3, 4, 5, 6, 7)]
+        wide = 0
+        for dims, perm in cases:
+            if perm == sorted(perm):
+                continue
+            for elt in (4, 8):
+                n = hc.cutt_hostcheck_num_candidates(len(dims), _iarr(dims), _iarr(perm), elt)
+                a = raw_bits(volume(dims), elt, 5 + elt)
+                want = oracle_mod.transpose_blocked(dims, perm, a)
+                for i in sorted(random.Random(elt).sample(range(n), min(n, 6))):
+                    out = np.full_like(a, 0xAB)
+                    lab = ctypes.create_string_buffer(2048)
+                    rc = hc.cutt_hostcheck_run(len(dims), _iarr(dims), _iarr(perm), elt, i, a.ctypes.data,
+                                               out.ctypes.data, lab, 2048)
+                    assert rc == 0, (rc, dims, perm, elt, i)
+                    assert np.array_equal(out, want), (dims, perm, elt, i, lab.value.decode())
+                    wide += 1 if " wide" in lab.value.decode() else 0
+        assert wide > 20
+    finally:
+        hc.cutt_hostcheck_force_wide(0)

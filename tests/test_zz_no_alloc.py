@@ -56,3 +56,25 @@ def test_no_alloc_copy_matches_regular_copy(native):
     assert native.copy_noalloc(a.data_ptr(), b.data_ptr(), (1 << 40) + 16, 0) == bad  # over the size limit
     assert native.copy_noalloc(0, b.data_ptr(), 1024, 0) == bad
     assert native.copy_noalloc_timeouts() == 0
+
+
+def test_no_alloc_status_after_a_large_then_a_small_copy_on_a_side_stream(native):
+    """The status reader must wait for the copy itself (the stream here is one of torch's side
+    streams, which a plain blocking copy does not wait for) and must report only the latest call:
+    a large launch (one block per SM) is followed by a one-block launch, with no synchronisation
+    by the caller in between or before the status is read."""
+    import torch
+    side = torch.cuda.Stream()
+    big = torch.arange(64 << 20, dtype=torch.int32, device="cuda")      # 256 MB: every SM gets chunks
+    big_out = torch.zeros_like(big)
+    small = torch.arange(2048, dtype=torch.int32, device="cuda") * 3    # 8 KB: a single block
+    small_out = torch.zeros_like(small)
+    torch.cuda.synchronize()
+    s = side.cuda_stream
+    assert native.copy_noalloc(big.data_ptr(), big_out.data_ptr(), big.numel() * 4, s) == 0
+    assert native.copy_noalloc(small.data_ptr(), small_out.data_ptr(), small.numel() * 4, s) == 0
+    assert native.copy_noalloc_timeouts() == 0      # waits for both copies before reading
+    assert torch.equal(small_out, small)
+    assert torch.equal(big_out, big)
+    # the regular copy's counter has the same waiting rule
+    assert native.copy_timeouts() == 0
