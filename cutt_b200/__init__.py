@@ -95,6 +95,8 @@ def lib() -> ctypes.CDLL:
     L.cutt_mg_plan.argtypes = [up, ctypes.c_int, ip, ip, ctypes.c_size_t, vp, ctypes.c_int, ctypes.c_int]
     L.cutt_mg_plan_measure.argtypes = [up, ctypes.c_int, ip, ip, ctypes.c_size_t, vp, ctypes.c_int, ctypes.c_int, vp, vpp]
     L.cutt_mg_execute.argtypes = [ctypes.c_uint, vp, vpp]
+    L.cutt_mg_num_candidates.argtypes = [ctypes.c_int, ip, ip, ctypes.c_size_t, ctypes.c_int, ctypes.c_int]
+    L.cutt_mg_plan_candidate.argtypes = [up, ctypes.c_int, ip, ip, ctypes.c_size_t, vp, ctypes.c_int, ctypes.c_int, ctypes.c_int]
     L.cutt_mg_mode.argtypes = [ctypes.c_uint]
     L.cutt_mg_local_volume.argtypes = [ctypes.c_uint]
     L.cutt_mg_local_volume.restype = ctypes.c_longlong
@@ -102,7 +104,7 @@ def lib() -> ctypes.CDLL:
     L.cutt_mg_ipc_open.argtypes = [ctypes.c_char_p, vpp]
     L.cutt_mg_ipc_close.argtypes = [vp]
     L.cutt_mg_enable_peer_access.argtypes = [ctypes.c_int]
-    for name in ("cutt_mg_plan", "cutt_mg_plan_measure", "cutt_mg_execute", "cutt_mg_mode", "cutt_mg_ipc_export",
+    for name in ("cutt_mg_plan", "cutt_mg_plan_measure", "cutt_mg_num_candidates", "cutt_mg_plan_candidate", "cutt_mg_execute", "cutt_mg_mode", "cutt_mg_ipc_export",
                  "cutt_mg_ipc_open", "cutt_mg_ipc_close", "cutt_mg_enable_peer_access"):
         getattr(L, name).restype = ctypes.c_int
     for name in ("cutt_c_plan", "cutt_c_plan_measure", "cutt_c_execute", "cutt_c_destroy",

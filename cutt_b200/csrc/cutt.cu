@@ -311,7 +311,7 @@ bool valid_tile_params(const TileParams& t) {
          one_of(t.maxVecBytes, {4, 8, 16}) && one_of(t.maxVBytes, {4, 8, 16}) &&
          one_of(t.extend, {0, 1}) && one_of(t.loopOrder, {0, 1}) && one_of(t.groupIn, {1, 2, 4}) &&
          one_of(t.groupOut, {1, 2, 4}) && one_of(t.cutInRun, {0, 1}) && one_of(t.allowAof, {0, 1}) &&
-         one_of(t.oneTilePerBlock, {0, 1}) && t.tinBytes >= 4 && t.tinBytes <= (1u << 16) &&
+         one_of(t.oneTilePerBlock, {0, 1}) && one_of(t.peerOrder, {0, 1}) && t.tinBytes >= 4 && t.tinBytes <= (1u << 16) &&
          t.toutBytes >= 4 && t.toutBytes <= (1u << 16) && t.vtargetBytes >= 4 && t.vtargetBytes <= (1u << 20);
 }
 
@@ -909,6 +909,33 @@ int cutt_mg_plan_measure(unsigned int* handle, int rank, const int* dim, const i
   return (int)make_plan(handle, rank, dim, permutation, sizeofType, (cudaStream_t)stream, req);
 }
 
+int cutt_mg_num_candidates(int rank, const int* dim, const int* permutation, size_t sizeofType,
+                           int world, int me) {
+  if (world < 1 || world > CUTT_MG_MAX_WORLD || me < 0 || me >= world) return 0;
+  if (check_input(rank, dim, permutation, sizeofType) != CUTT_SUCCESS) return 0;
+  std::lock_guard<std::mutex> lk(g_mutex);
+  int devId;
+  DeviceInfo dev;
+  if (!device_info(devId, dev)) return 0;
+  Problem P;
+  ShardInfo info;
+  if (!problem_from_cutt_sharded(rank, dim, permutation, (int)sizeofType, world, me, P, info)) return 0;
+  const std::string key = problem_key(devId, rank, dim, permutation, sizeofType) + "/mg" + std::to_string(world) +
+                          "." + std::to_string(me);
+  return (int)enumerate_cached(key, P, dev).size();
+}
+
+int cutt_mg_plan_candidate(unsigned int* handle, int rank, const int* dim, const int* permutation,
+                           size_t sizeofType, void* stream, int world, int me, int index) {
+  if (world < 1 || world > CUTT_MG_MAX_WORLD || me < 0 || me >= world) return CUTT_INVALID_PARAMETER;
+  PlanRequest req;
+  req.mode = kByIndex;
+  req.world = world;
+  req.me = me;
+  req.index = index;
+  return (int)make_plan(handle, rank, dim, permutation, sizeofType, (cudaStream_t)stream, req);
+}
+
 int cutt_mg_mode(unsigned int handle) {
   std::lock_guard<std::mutex> lk(g_mutex);
   auto it = g_plans.find(handle);
@@ -1040,7 +1067,7 @@ void cutt_c_clear_plan_cache(void) {
   plan_cache().clear();
 }
 
-static const char kPlanCacheHeader[] = "# cutt-b200 plan cache v3";
+static const char kPlanCacheHeader[] = "# cutt-b200 plan cache v4";
 
 // One line per entry: key, method and the tile parameters of the measured winner.
 int cutt_c_plan_cache_save(const char* path) {
@@ -1051,9 +1078,9 @@ int cutt_c_plan_cache_save(const char* path) {
   fprintf(f, "%s\n", kPlanCacheHeader);
   plan_cache().for_each_oldest_first([&](const std::string& k, const CachedChoice& c) {
     const TileParams& t = c.params;
-    fprintf(f, "%s %d %u %u %u %d %d %d %d %d %d %d %d %d %d %d\n", k.c_str(), (int)c.method, t.tinBytes, t.toutBytes,
+    fprintf(f, "%s %d %u %u %u %d %d %d %d %d %d %d %d %d %d %d %d\n", k.c_str(), (int)c.method, t.tinBytes, t.toutBytes,
             t.vtargetBytes, t.extend, t.nthreads, t.stages, t.maxVecBytes, t.maxVBytes, t.loopOrder,
-            t.groupIn, t.groupOut, t.cutInRun, t.allowAof, t.oneTilePerBlock);
+            t.groupIn, t.groupOut, t.cutInRun, t.allowAof, t.oneTilePerBlock, t.peerOrder);
   });
   fclose(f);
   return CUTT_SUCCESS;
@@ -1082,9 +1109,10 @@ int cutt_c_plan_cache_load(const char* path) {
     int method;
     CachedChoice c;
     TileParams& t = c.params;
-    if (sscanf(line, "%511s %d %u %u %u %d %d %d %d %d %d %d %d %d %d %d", key, &method, &t.tinBytes, &t.toutBytes,
+    if (sscanf(line, "%511s %d %u %u %u %d %d %d %d %d %d %d %d %d %d %d %d", key, &method, &t.tinBytes, &t.toutBytes,
                &t.vtargetBytes, &t.extend, &t.nthreads, &t.stages, &t.maxVecBytes, &t.maxVBytes,
-               &t.loopOrder, &t.groupIn, &t.groupOut, &t.cutInRun, &t.allowAof, &t.oneTilePerBlock) != 16)
+               &t.loopOrder, &t.groupIn, &t.groupOut, &t.cutInRun, &t.allowAof, &t.oneTilePerBlock,
+               &t.peerOrder) != 17)
       continue;
     // winners are tiled plans, row copies or (identity permutations) the two copy methods
     if (method != kMethodTiles && method != kMethodRowCopy && method != kMethodCopy && method != kMethodMemcpy) continue;

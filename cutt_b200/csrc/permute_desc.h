@@ -188,6 +188,10 @@ struct TileDesc {
   uint32_t wide;        // 1: 64-bit row offsets
   int32_t peerLoopDim;  // loop dimension whose coordinate selects the destination GPU, or -1
   uint32_t aof;         // 1: aligned over-fetch loads (see below)
+  uint32_t peerRot;     // added (modulo the GPU count) to the peer digit of the tile index: GPU r
+                        // starts with destination r, so that at any moment the GPUs of a job write
+                        // to different destinations instead of all to the same one
+  uint32_t pad0_;
   int64_t inElems;      // elements of the input buffer (bounds of the over-fetch)
   int64_t vstep;        // output offset between the V rows of a group (elements)
   int64_t inBase;       // element offset added to the input pointer
@@ -255,9 +259,14 @@ CUTT_HD void decode_tile(const TileDesc& D, uint32_t tile, TileCtx& c) {
     uint32_t q = fdiv(id, L.div);
     uint32_t cc = id - q * L.n;
     id = q;
+    if ((int32_t)k == D.peerLoopDim) {
+      cc += D.peerRot;
+      if (cc >= L.n) cc -= L.n;
+      c.peer = cc;
+    } else {
+      c.outOff += (int64_t)cc * L.ostep;
+    }
     c.inOff += (int64_t)cc * L.istep;
-    if ((int32_t)k == D.peerLoopDim) c.peer = cc;
-    else c.outOff += (int64_t)cc * L.ostep;
     if (L.part == 0) {
       set_rem(c, L.slot, L.d - cc * L.t, L.t);
     } else if (L.which == 0) {

@@ -147,6 +147,7 @@ bool problem_from_cutt_sharded(int rank, const int* dim, const int* perm, int el
   if (!canonicalize((int)d2.size(), d2.data(), is2.data(), os2.data(), elt, peer, P)) return false;
   // this GPU's slab of input dimension `last` lands at this offset of every output slab
   P.outBase = (int64_t)me * info.localDim[last] * os[last];
+  P.peerRot = me;
   P.identity = false;
   return true;
 }
@@ -264,8 +265,8 @@ bool build_tile(const Problem& P, const TileParams& tp, const DeviceInfo& dev, C
     std::string key;
     char kb[64];
     for (int j = 0; j < r; j++) { snprintf(kb, sizeof kb, "%lld,", (long long)t[j]); key += kb; }
-    snprintf(kb, sizeof kb, "|%d%d%d%d%d%d%d%d%d", tp.nthreads, tp.stages, tp.maxVecBytes, tp.maxVBytes, tp.loopOrder,
-             tp.cutInRun, tp.allowAof, tp.groupIn * 16 + tp.groupOut, tp.oneTilePerBlock);
+    snprintf(kb, sizeof kb, "|%d%d%d%d%d%d%d%d%d%d", tp.nthreads, tp.stages, tp.maxVecBytes, tp.maxVBytes, tp.loopOrder,
+             tp.cutInRun, tp.allowAof, tp.groupIn * 16 + tp.groupOut, tp.oneTilePerBlock, tp.peerOrder);
     key += kb;
     if (!seenExtents->insert(key).second) return false;
   }
@@ -494,6 +495,16 @@ bool build_tile(const Problem& P, const TileParams& tp, const DeviceInfo& dev, C
   {
     int order[kMaxDims];
     for (int k = 0; k < r; k++) order[k] = tp.loopOrder == 0 ? k : oo[k];
+    const bool balanced = tp.peerOrder == 1 && P.peerDim >= 0;
+    if (balanced) {  // the destination GPU becomes the fastest digit
+      int n = 0;
+      order[n++] = P.peerDim;
+      for (int k = 0; k < r; k++) {
+        const int j = tp.loopOrder == 0 ? k : oo[k];
+        if (j != P.peerDim) order[n++] = j;
+      }
+    }
+    D.peerRot = balanced ? (uint32_t)P.peerRot : 0u;
     // optional inner groups along the chunked dimensions of the two runs
     int splitDim[2] = {-1, -1};
     int64_t splitS[2] = {1, 1};
@@ -568,6 +579,7 @@ bool build_tile(const Problem& P, const TileParams& tp, const DeviceInfo& dev, C
              D.split[1].used ? tp.groupOut : 1);
   }
   if (tp.oneTilePerBlock) snprintf(buf + strlen(buf), sizeof buf - strlen(buf), " 1tpb");
+  if (D.peerLoopDim >= 0 && tp.peerOrder == 1) snprintf(buf + strlen(buf), sizeof buf - strlen(buf), " peers-first");
   out.label = buf;
 
   // features of the cost model
@@ -762,13 +774,17 @@ std::vector<Candidate> enumerate_candidates(const Problem& P, const DeviceInfo& 
           for (int lo = 0; lo < 2; lo++)
             for (const auto& g : groups)
               for (int nt = 256; nt <= 512; nt *= 2)
-                for (int aof = 1; aof >= 0; aof--) {
+                for (int aofpo = 3; aofpo >= 0; aofpo--) {
+                  // all-to-all plans come in both destination orders (TileParams::peerOrder)
+                  const int aof = aofpo & 1, po = aofpo >> 1;
+                  if (po && P.peerDim < 0) continue;
                   TileParams tp;
                   tp.tinBytes = tinB; tp.toutBytes = toutB; tp.vtargetBytes = vB;
                   tp.extend = ext; tp.loopOrder = lo;
                   tp.groupIn = g[0]; tp.groupOut = g[1];
                   tp.nthreads = nt;
                   tp.allowAof = aof;
+                  tp.peerOrder = po;
                   Candidate c;
                   if (!build_tile(P, tp, dev, c, &seenExt)) continue;
                   // same tile with the input run cut in front of the output's first dimension
@@ -796,10 +812,13 @@ std::vector<Candidate> enumerate_candidates(const Problem& P, const DeviceInfo& 
         for (uint32_t vB : svols)
           for (int lo = 0; lo < 2; lo++)
             for (int nt = 128; nt <= 256; nt *= 2)
-              for (int aof = 1; aof >= 0; aof--) {
+              for (int aofpo = 3; aofpo >= 0; aofpo--) {
+                const int aof = aofpo & 1, po = aofpo >> 1;
+                if (po && P.peerDim < 0) continue;
                 TileParams tp;
                 tp.tinBytes = tinB; tp.toutBytes = toutB; tp.vtargetBytes = vB;
                 tp.loopOrder = lo; tp.nthreads = nt; tp.stages = 1; tp.oneTilePerBlock = 1; tp.allowAof = aof;
+                tp.peerOrder = po;
                 Candidate c;
                 if (!build_tile(P, tp, dev, c, &seenExt)) continue;
                 if (c.smemBytes > 24 * 1024) continue;

@@ -31,6 +31,7 @@ struct Problem {
   int64_t os[kMaxDims];
   int64_t inBase = 0, outBase = 0;
   int peerDim = -1;   // canonical dimension whose coordinate selects the destination GPU
+  int peerRot = 0;    // this GPU's rank: first destination of the balanced tile order (TileParams::peerOrder)
   int64_t volume = 0;
   int64_t inElems = 0;  // elements of the input buffer this problem reads from
   bool identity = false;  // one contiguous run on both sides: a plain copy
@@ -95,6 +96,12 @@ struct TileParams {
   int loopOrder = 0;           // tile index runs fastest along 0: input order, 1: output order
   int groupIn = 1;             // neighbouring tiles along the input run's chunked dimension taken first
   int groupOut = 1;            // then this many along the output run's chunked dimension
+  int peerOrder = 0;           // multi-GPU all-to-all plans: 0 = the destination GPU is one more digit of
+                               // the tile index at its place in the loop order (every GPU works through
+                               // destination 0, then 1, ...: all GPUs write to the same destination at the
+                               // same time); 1 = the destination is the FASTEST digit and GPU r starts
+                               // with destination r, so the blocks of one GPU spread their stores over
+                               // all destinations and no destination receives from everybody at once
 };
 
 constexpr int kNumFeatures = 32;

@@ -46,6 +46,17 @@ def mg_plan_measure(dims, perm, elt, world, me, stream, idata: int, odata: Seque
     return rc, h.value
 
 
+def mg_num_candidates(dims, perm, elt, world, me) -> int:
+    return lib().cutt_mg_num_candidates(len(dims), _iarr(dims), _iarr(perm), elt, world, me)
+
+
+def mg_plan_candidate(dims, perm, elt, world, me, index, stream=0):
+    h = ctypes.c_uint(0)
+    rc = lib().cutt_mg_plan_candidate(ctypes.byref(h), len(dims), _iarr(dims), _iarr(perm), elt, stream,
+                                      world, me, index)
+    return rc, h.value
+
+
 def mg_execute(handle: int, idata: int, odata: Sequence[int]) -> int:
     arr = (ctypes.c_void_p * len(odata))(*odata)
     return lib().cutt_mg_execute(handle, idata, arr)
@@ -83,7 +94,7 @@ class ShardedTranspose:
     barrier, after which ``out`` is complete everywhere.
     """
 
-    def __init__(self, dims, perm, elt, group=None, measure_input=None):
+    def __init__(self, dims, perm, elt, group=None, measure_input=None, measure_topk=32):
         import torch
         import torch.distributed as dist
         self.dist = dist
@@ -112,7 +123,10 @@ class ShardedTranspose:
         else:
             self.peer_ptrs = [self.out.data_ptr()] * self.world
         stream = torch.cuda.current_stream().cuda_stream
-        if measure_input is not None:
+        self.measured = None
+        if measure_input is not None and self.mode == 1 and self.world > 1:
+            rc, self.handle = self._measure_together(measure_input, stream, measure_topk)
+        elif measure_input is not None:
             self._barrier()
             rc, self.handle = mg_plan_measure(self.dims, self.perm, elt, self.world, self.me, stream,
                                               measure_input.data_ptr(), self.peer_ptrs)
@@ -126,6 +140,62 @@ class ShardedTranspose:
     def _barrier(self):
         if self.world > 1:
             self.dist.barrier(group=self.group)
+
+    def _reduce(self, value: float, op: str) -> float:
+        """max / min of a host number over the ranks (through a device tensor, so that it works
+        with the nccl backend as well as with gloo)."""
+        import torch
+        dev = "cuda" if self.dist.get_backend(self.group) == "nccl" else "cpu"
+        t = torch.tensor([value], dtype=torch.float64, device=dev)
+        self.dist.all_reduce(t, op=self.dist.ReduceOp.MAX if op == "max" else self.dist.ReduceOp.MIN,
+                             group=self.group)
+        return float(t.item())
+
+    def _measure_together(self, inp, stream, topk):
+        """All-to-all plans are chosen by the whole job: every rank builds candidate i of the
+        planner's list, all ranks run it at the same time, and the slowest rank's time counts -
+        what a rank's stores cost depends on what the other GPUs send meanwhile.  The score of a
+        candidate is the slower of two warm runs (as in the single-GPU measurement)."""
+        import torch
+        n = mg_num_candidates(self.dims, self.perm, self.elt, self.world, self.me)
+        n = int(self._reduce(float(n), "min"))
+        if n <= 0:
+            return CUTT_SUCCESS + 4, None
+        best_t, best_i, timings = None, None, []
+        e0 = torch.cuda.Event(enable_timing=True)
+        e1 = torch.cuda.Event(enable_timing=True)
+        for i in range(min(n, max(1, topk))):
+            rc, h = mg_plan_candidate(self.dims, self.perm, self.elt, self.world, self.me, i, stream)
+            ok = self._reduce(1.0 if rc == CUTT_SUCCESS else 0.0, "min") > 0.5
+            if not ok:
+                if rc == CUTT_SUCCESS:
+                    from . import cuttDestroy
+                    cuttDestroy(h)
+                continue
+            ts = []
+            for rep in range(3):
+                torch.cuda.synchronize()
+                self._barrier()
+                e0.record()
+                rc = mg_execute(h, inp.data_ptr(), self.peer_ptrs)
+                e1.record()
+                torch.cuda.synchronize()
+                t = self._reduce(e0.elapsed_time(e1) if rc == CUTT_SUCCESS else 1e30, "max")
+                ts.append(t)
+                # the first run doubles as warm-up; clearly slower candidates stop after it
+                if rep == 0 and best_t is not None and t > 1.3 * best_t:
+                    break
+            from . import cuttDestroy
+            cuttDestroy(h)
+            score = max(ts[1:]) if len(ts) == 3 else ts[0]
+            timings.append((i, score))
+            if len(ts) == 3 and (best_t is None or score < best_t):
+                best_t, best_i = score, i
+        self._barrier()
+        if best_i is None:
+            return mg_plan(self.dims, self.perm, self.elt, self.world, self.me, stream)
+        self.measured = {"candidate": best_i, "ms": best_t, "timed": len(timings)}
+        return mg_plan_candidate(self.dims, self.perm, self.elt, self.world, self.me, best_i, stream)
 
     def execute(self, inp) -> None:
         rc = mg_execute(self.handle, inp.data_ptr(), self.peer_ptrs)

@@ -57,6 +57,18 @@ int cutt_mg_plan_measure(unsigned int* handle, int rank, const int* dim, const i
                          size_t sizeofType, void* stream, int world, int me, void* idata,
                          void* const* odata);
 
+/* Candidate implementations the planner enumerates for rank `me`'s part, cheapest model estimate
+ * first (0 on invalid input), and a plan that uses candidate number `index` of that list.  The
+ * list depends on the problem only, so every rank sees the same list: a job can time candidate
+ * 0, 1, 2, ... on all ranks AT THE SAME TIME (barrier, execute, barrier), take the slowest rank's
+ * time and so choose one plan for the whole job, which is what an all-to-all needs - a plan's
+ * speed depends on what the other GPUs are sending meanwhile.  cutt_mg_plan_measure, in
+ * contrast, lets each rank time its candidates on its own. */
+int cutt_mg_num_candidates(int rank, const int* dim, const int* permutation, size_t sizeofType,
+                           int world, int me);
+int cutt_mg_plan_candidate(unsigned int* handle, int rank, const int* dim, const int* permutation,
+                           size_t sizeofType, void* stream, int world, int me, int index);
+
 /* 0 slab, 1 all-to-all; negative: not a multi-GPU plan. */
 int cutt_mg_mode(unsigned int handle);
 

@@ -105,13 +105,13 @@ def test_missing_library_fails_loudly(monkeypatch, native):
 def test_plan_cache_file_roundtrip(native, tmp_path):
     path = str(tmp_path / "plans.txt")
     with open(path, "w") as f:
-        f.write("# cutt-b200 plan cache v3\n0/4/64,48,/1,0, 2 128 512 65536 1 512 2 16 16 1 2 4 0 1 0\n")
+        f.write("# cutt-b200 plan cache v4\n0/4/64,48,/1,0, 2 128 512 65536 1 512 2 16 16 1 2 4 0 1 0 0\n")
     native.clear_plan_cache()
     assert native.plan_cache_load(path) == 0
     assert native.plan_cache_size() == 1
     out = str(tmp_path / "out.txt")
     assert native.plan_cache_save(out) == 0
-    assert "0/4/64,48,/1,0, 2 128 512 65536 1 512 2 16 16 1 2 4 0 1 0" in open(out).read()
+    assert "0/4/64,48,/1,0, 2 128 512 65536 1 512 2 16 16 1 2 4 0 1 0 0" in open(out).read()
     native.clear_plan_cache()
     assert native.plan_cache_size() == 0
 
@@ -119,7 +119,7 @@ def test_plan_cache_file_roundtrip(native, tmp_path):
 def test_plan_cache_load_rejects_foreign_and_damaged_files(native, tmp_path):
     """Only this format version is read; entries with fields out of range are skipped, so a stale
     or edited file can never install a method or tile parameters the planner would not produce."""
-    good = "0/4/64,48,/1,0, 2 128 512 65536 1 512 2 16 16 1 2 4 0 1 0"
+    good = "0/4/64,48,/1,0, 2 128 512 65536 1 512 2 16 16 1 2 4 0 1 0 0"
     bad_param = native.CUTT_INVALID_PARAMETER
 
     def load(text):
@@ -129,27 +129,27 @@ def test_plan_cache_load_rejects_foreign_and_damaged_files(native, tmp_path):
         native.clear_plan_cache()
         return native.plan_cache_load(path), native.plan_cache_size()
 
-    assert load("# cutt-b200 plan cache v3\n" + good + "\n") == (0, 1)
+    assert load("# cutt-b200 plan cache v4\n" + good + "\n") == (0, 1)
     # an older layout, no header, or a header that only starts the same way: nothing is read
-    assert load("# cutt-b200 plan cache v2\n" + good + "\n") == (bad_param, 0)
+    assert load("# cutt-b200 plan cache v3\n" + good + "\n") == (bad_param, 0)
     assert load(good + "\n") == (bad_param, 0)
-    assert load("# cutt-b200 plan cache v31\n" + good + "\n") == (bad_param, 0)
+    assert load("# cutt-b200 plan cache v41\n" + good + "\n") == (bad_param, 0)
     assert load("") == (bad_param, 0)
     # damaged entries: thread count 0 or not a power of two, 3 stages, odd vector bytes, the
     # element-wise methods (3, 5), unknown methods, short lines
     body = "\n".join([
-        "0/4/64,48,/1,0, 2 128 512 65536 1 0 2 16 16 1 2 4 0 1 0",
-        "0/4/64,48,/1,0, 2 128 512 65536 1 384 2 16 16 1 2 4 0 1 0",
-        "0/4/64,48,/1,0, 2 128 512 65536 1 256 3 16 16 1 2 4 0 1 0",
-        "0/4/64,48,/1,0, 2 128 512 65536 1 256 2 12 16 1 2 4 0 1 0",
-        "0/4/64,48,/1,0, 2 128 512 65536 1 256 2 16 16 1 3 4 0 1 0",
-        "0/4/64,48,/1,0, 3 128 512 65536 1 256 2 16 16 1 2 4 0 1 0",
-        "0/4/64,48,/1,0, 5 128 512 65536 1 256 2 16 16 1 2 4 0 1 0",
-        "0/4/64,48,/1,0, 9 128 512 65536 1 256 2 16 16 1 2 4 0 1 0",
+        "0/4/64,48,/1,0, 2 128 512 65536 1 0 2 16 16 1 2 4 0 1 0 0",
+        "0/4/64,48,/1,0, 2 128 512 65536 1 384 2 16 16 1 2 4 0 1 0 0",
+        "0/4/64,48,/1,0, 2 128 512 65536 1 256 3 16 16 1 2 4 0 1 0 0",
+        "0/4/64,48,/1,0, 2 128 512 65536 1 256 2 12 16 1 2 4 0 1 0 0",
+        "0/4/64,48,/1,0, 2 128 512 65536 1 256 2 16 16 1 3 4 0 1 0 0",
+        "0/4/64,48,/1,0, 3 128 512 65536 1 256 2 16 16 1 2 4 0 1 0 0",
+        "0/4/64,48,/1,0, 5 128 512 65536 1 256 2 16 16 1 2 4 0 1 0 0",
+        "0/4/64,48,/1,0, 9 128 512 65536 1 256 2 16 16 1 2 4 0 1 0 0",
         "0/4/64,48,/1,0, 2 128 512",
     ])
-    assert load("# cutt-b200 plan cache v3\n" + body + "\n") == (bad_param, 0)
-    assert load("# cutt-b200 plan cache v3\n" + body + "\n" + good + "\n") == (0, 1)
+    assert load("# cutt-b200 plan cache v4\n" + body + "\n") == (bad_param, 0)
+    assert load("# cutt-b200 plan cache v4\n" + body + "\n" + good + "\n") == (0, 1)
     native.clear_plan_cache()
 
 

@@ -67,6 +67,41 @@ def test_emulated_ranks_on_one_gpu(native, oracle_mod, dims, perm, world):
             assert_bit_exact(got, want, "%s %s world=%d %s" % (dims, perm, world, planner))
 
 
+@pytest.mark.parametrize("world", [2, 4, 8])
+def test_candidates_in_both_destination_orders(native, oracle_mod, world):
+    """cutt_mg_plan_candidate over the first candidates of an all-to-all problem (emulated ranks):
+    both tile orders - destination as an ordinary digit, and destination fastest and rotated by
+    the rank - produce the same slabs."""
+    import json
+    import torch
+    from cutt_b200 import multigpu as mg
+    dims, perm, elt = [256, 192, 8, 32], [3, 2, 0, 1], 4
+    a = raw_bits(volume(dims), elt, 6)
+    want = oracle_mod.transpose_blocked(dims, perm, a)
+    loc = volume(dims) // world
+    ins = [torch.from_numpy(a[g * loc:(g + 1) * loc].view(np.int32).copy()).cuda() for g in range(world)]
+    outs = [torch.full((loc,), -1, dtype=torch.int32, device="cuda") for _ in range(world)]
+    ptrs = [o.data_ptr() for o in outs]
+    n = min(mg.mg_num_candidates(dims, perm, elt, world, g) for g in range(world))
+    assert n > 4
+    seen = {True: 0, False: 0}
+    for index in list(range(min(n, 12))) + [n - 1]:
+        for o in outs:
+            o.fill_(-1)
+        for g in range(world):
+            rc, h = mg.mg_plan_candidate(dims, perm, elt, world, g, index)
+            assert rc == 0
+            if g == 0:
+                seen["peers-first" in json.loads(native.plan_describe(h))["label"]] += 1
+            assert mg.mg_execute(h, ins[g].data_ptr(), ptrs) == 0
+            native.cuttDestroy(h)
+        torch.cuda.synchronize()
+        assert_bit_exact(torch.cat(outs).cpu().numpy(), want, "world=%d candidate %d" % (world, index))
+    assert seen[True] > 0 and seen[False] > 0, seen
+    assert mg.mg_plan_candidate(dims, perm, elt, world, 0, n)[0] == native.CUTT_INVALID_PARAMETER
+    assert mg.mg_num_candidates(dims, perm, elt, 3, 0) == 0
+
+
 def test_mg_error_codes(native):
     import torch
     from cutt_b200 import multigpu as mg

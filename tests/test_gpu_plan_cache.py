@@ -74,12 +74,12 @@ def test_damaged_cache_entries_are_ignored(native, oracle_mod, tmp_path):
                            "".join("%d," % p for p in perm))
     a = raw_bits(volume(dims), elt, 9)
     want = oracle_mod.transpose_blocked(dims, perm, a)
-    for entry in ("1 256 256 16384 0 256 2 16 16 0 1 1 0 1 0",      # memcpy for a non-identity problem
-                  "0 256 256 16384 0 256 2 16 16 0 1 1 0 1 0",      # copy kernel, same
-                  "2 4 4 4 0 512 2 16 16 0 1 1 0 1 0"):             # legal fields, absurdly small tile
+    for entry in ("1 256 256 16384 0 256 2 16 16 0 1 1 0 1 0 0",    # memcpy for a non-identity problem
+                  "0 256 256 16384 0 256 2 16 16 0 1 1 0 1 0 0",    # copy kernel, same
+                  "2 4 4 4 0 512 2 16 16 0 1 1 0 1 0 0"):           # legal fields, absurdly small tile
         path = str(tmp_path / "c.txt")
         with open(path, "w") as f:
-            f.write("# cutt-b200 plan cache v3\n%s %s\n" % (key, entry))
+            f.write("# cutt-b200 plan cache v4\n%s %s\n" % (key, entry))
         native.clear_plan_cache()
         assert native.plan_cache_load(path) == 0
         out, desc = gpu_transpose(native, dims, perm, elt, a)

@@ -64,6 +64,36 @@ def test_sharded_plan_in_one_process(native, oracle_mod, dims, perm, world):
             assert np.array_equal(np.concatenate(outs), want), (dims, perm, world, elt, index)
 
 
+@pytest.mark.parametrize("world", [2, 4, 8])
+def test_both_destination_orders(native, oracle_mod, world):
+    """All-to-all plans exist in two tile orders: destination GPU as an ordinary digit of the tile
+    index, and destination fastest, rotated by the rank ("peers-first").  Both must give the
+    same output."""
+    lib = _hostcheck()
+    dims, perm, elt = [64, 48, 8, 16], [3, 2, 0, 1], 4
+    a = raw_bits(volume(dims), elt, 4)
+    want = oracle_mod.transpose_blocked(dims, perm, a)
+    loc = volume(dims) // world
+    outs = [np.zeros(loc, dtype=a.dtype) for _ in range(world)]
+    ptrs = (ctypes.c_void_p * world)(*[o.ctypes.data for o in outs])
+    seen = {True: 0, False: 0}
+    for index in range(24):
+        for o in outs:
+            o[:] = 0
+        first = None
+        for g in range(world):
+            src = np.ascontiguousarray(a[g * loc:(g + 1) * loc])
+            lab = ctypes.create_string_buffer(4096)
+            m = lib.cutt_hostcheck_run_sharded(len(dims), _iarr(dims), _iarr(perm), elt, world, g, index,
+                                               src.ctypes.data, ptrs, lab, 4096)
+            assert m == 1
+            if g == 0:
+                first = "peers-first" in lab.value.decode()
+        seen[first] += 1
+        assert np.array_equal(np.concatenate(outs), want), (world, index)
+    assert seen[True] > 0 and seen[False] > 0, seen
+
+
 def _gloo_worker(rank, world, port, dims, perm, elt, result_queue):
     sys.path.insert(0, ROOT)
     sys.path.insert(0, os.path.join(ROOT, "tests"))
