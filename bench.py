@@ -432,6 +432,73 @@ def time_sharded(ctx, which, steps, warmup, sample_clocks):
     return res
 
 
+def run_emulated(ctx):
+    """--emulate-world N on ONE GPU: the N ranks' parts of a sharded workload run back to back on
+    this device, every "peer" slab being another local buffer (the kernels never wait for each
+    other, so this is legitimate).  It exists to profile the peer-store kernel's instruction and
+    DRAM behaviour without NVLink; the GB/s it prints say nothing about a multi-GPU job."""
+    torch, C, W = ctx.torch, ctx.C, ctx.W
+    from cutt_b200 import multigpu as mg
+    args = ctx.args
+    world = args.emulate_world
+    dims = _c5_dims(args)
+    perm = W.C5A_PERM if args.workload == "c5a" else W.C5B_PERM
+    vol = _vol(dims)
+    loc = vol // world
+    ins, outs = [], []
+    for g in range(world):
+        t = torch.empty(loc, dtype=torch.int32, device="cuda")
+        ctx.DC.fill_pattern(t, first_index=g * loc)
+        ins.append(t)
+        outs.append(torch.full((loc,), -1, dtype=torch.int32, device="cuda"))
+    ptrs = [o.data_ptr() for o in outs]
+    handles = []
+    for g in range(world):
+        rc, h = mg.mg_plan_measure(dims, perm, 4, world, g, ctx.stream, ins[g].data_ptr(), ptrs)
+        if rc != 0:
+            raise SystemExit("cutt_mg_plan_measure failed: %d" % rc)
+        handles.append(h)
+
+    def step():
+        for g, h in enumerate(handles):
+            rc = mg.mg_execute(h, ins[g].data_ptr(), ptrs)
+            if rc != 0:
+                raise SystemExit("cutt_mg_execute failed: %d" % rc)
+
+    for _ in range(max(3, args.warmup)):
+        step()
+    torch.cuda.synchronize()
+    l0 = C.launch_count()
+    e0 = torch.cuda.Event(enable_timing=True)
+    e1 = torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(args.steps):
+        step()
+    e1.record()
+    torch.cuda.synchronize()
+    ms = e0.elapsed_time(e1) / args.steps
+    launches = C.launch_count() - l0
+    for o in outs:
+        o.fill_(-1)
+    step()
+    torch.cuda.synchronize()
+    for g in range(world):
+        ctx.check("%s_emulated" % args.workload, dims, perm, outs[g], None, out_first=g * loc)
+    value = 2 * vol * 4 / (ms * 1e-3) / 1e9
+    line = base_line(args, value, ms, 1, "weak")
+    line["config"] = workload_config(args, world)
+    line["config"]["workload"] += " - EMULATED: all %d ranks run back to back on one GPU" % world
+    line["detail"] = {"plans": [json.loads(C.plan_describe(h))["label"] for h in handles[:2]],
+                      "mode": "slab" if mg.mg_mode(handles[0]) == 0 else "all-to-all by stores into %d local slabs" % world}
+    line["roofline"] = {"bound": "hbm", "achieved": value, "peak": ctx.peak, "unit": UNIT, "frac": value / ctx.peak,
+                        "traffic": None, "peak_kind": ctx.peak_kind}
+    line["gpu_launches"] = launches
+    line["e2e"] = None
+    for h in handles:
+        C.cuttDestroy(h)
+    return line
+
+
 def e2e_host_leg(ctx, cases, steps):
     """The same metric through cutt_c_transpose_host: pinned host buffers in, pinned host buffers
     out, the uploads and downloads inside the timed region.  Every rank runs its own copy."""
@@ -828,7 +895,11 @@ def reference_gpu_baseline(cases, modes=(("cuttPlan", []), ("cuttPlanMeasure", [
 
 def run_ours(args):
     ctx = Ctx(args)
-    if args.workload in ("c5a", "c5b"):
+    if args.workload in ("c5a", "c5b") and args.emulate_world > 1:
+        if ctx.world != 1:
+            raise SystemExit("--emulate-world is a single-process, single-GPU mode")
+        line = run_emulated(ctx)
+    elif args.workload in ("c5a", "c5b"):
         line = run_default(ctx)
     elif args.workload == "c3":
         line = run_c3(ctx)
@@ -859,6 +930,8 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--workload", default="c5a", choices=["c1", "c2", "c3", "c4", "c5a", "c5b"])
     ap.add_argument("--c5-scale", type=int, default=1, help="divide dim 2 of the C5 tensor (quick checks)")
+    ap.add_argument("--emulate-world", type=int, default=0,
+                    help="c5a/c5b on ONE GPU with this many emulated ranks run back to back (profiling aid)")
     ap.add_argument("--suite-cases", type=int, default=100)
     ap.add_argument("--holdout-cases", type=int, default=50)
     ap.add_argument("--no-extras", action="store_true")

@@ -23,6 +23,11 @@ Python generator, so a seed reproduces a run here but not the original's rand() 
 The original's bench 6 (a fixed table taken from another project's benchmark, :551-690) is not
 reproduced; other bench numbers (a plain memory-copy benchmark there) are not offered.
 
+``-method M`` forces an implementation for every tensor (this library's method numbers: 0 copy
+kernel and 1 driver copy for identity permutations, 2 tiled kernel with default tile parameters,
+3 one thread per element, 4 strided row copy) and ``-offset B`` shifts both device buffers by B
+bytes (a multiple of the element size): profiling aids without a counterpart in the original.
+
 ``-volume`` scales every generated tensor (default 200 M elements, as the original); ``-samples``
 defaults to the original's counts (50 for bench 3, 500 for benches 5 and 7).
 """
@@ -57,17 +62,21 @@ def permute_checker(torch):
     return check
 
 
-def run_case(C, torch, dims, perm, elt, measure, buf_in, buf_out, checker=None, plantimer=False):
+def run_case(C, torch, dims, perm, elt, measure, buf_in, buf_out, checker=None, plantimer=False,
+             method=None, offset=0):
     vol = _vol(dims)
     words = 1
     if elt == 16:   # checked as two 64-bit words per element under an unpermuted innermost dimension
         words = 2
     dt = {1: torch.uint8, 2: torch.int16, 4: torch.int32, 8: torch.int64, 16: torch.int64}[elt]
-    tin = buf_in[:vol * elt // 8 + 1].view(dt)[:vol * words]
-    tout = buf_out[:vol * elt // 8 + 1].view(dt)[:vol * words]
+    e0 = offset // (elt // words)      # buffer offset in units of the checked word type
+    tin = buf_in[:(vol * elt + offset) // 8 + 1].view(dt)[e0:e0 + vol * words]
+    tout = buf_out[:(vol * elt + offset) // 8 + 1].view(dt)[e0:e0 + vol * words]
     stream = torch.cuda.current_stream().cuda_stream
     t0 = time.perf_counter()
-    if elt not in (4, 8):   # sizes the original rejects: extension entry points
+    if method is not None:
+        rc, h = C.plan_params(dims, perm, elt, stream, method=method)
+    elif elt not in (4, 8):   # sizes the original rejects: extension entry points
         if measure:
             rc, h = C.plan_measure_ext(dims, perm, elt, stream, tin.data_ptr(), tout.data_ptr())
         else:
@@ -233,6 +242,8 @@ def main(argv=None, checker="permute"):
     ap.add_argument("-volume", type=int, default=200_000_000, help="elements per generated tensor")
     ap.add_argument("-samples", type=int, default=None, help="random draws per rank (benches 3, 5RR, 7)")
     ap.add_argument("-nocheck", action="store_true")
+    ap.add_argument("-method", type=int, default=None, choices=[0, 1, 2, 3, 4])
+    ap.add_argument("-offset", type=int, default=0, help="byte offset of both device buffers")
     args = ap.parse_args(argv)
     import torch
     import cutt_b200 as C
@@ -256,14 +267,18 @@ def main(argv=None, checker="permute"):
         checker = None
     elif checker == "permute":
         checker = permute_checker(torch)
-    maxbytes = max(_vol(d) for d, _ in cases) * args.elemsize
+    if args.offset % args.elemsize or args.offset < 0:
+        raise SystemExit("-offset must be a non-negative multiple of the element size")
+    if args.method is not None and args.elemsize not in (4, 8):
+        raise SystemExit("-method needs -elemsize 4 or 8")
+    maxbytes = max(_vol(d) for d, _ in cases) * args.elemsize + args.offset
     buf_in = torch.randint(-2**62, 2**62, (maxbytes // 8 + 2,), dtype=torch.int64, device="cuda")
     buf_out = torch.empty_like(buf_in)
     per_rank = {}
     failed = 0
     for dims, perm in cases:
         gbs, ok, plan = run_case(C, torch, list(dims), list(perm), args.elemsize, args.measure, buf_in, buf_out,
-                                 checker=checker, plantimer=args.plantimer)
+                                 checker=checker, plantimer=args.plantimer, method=args.method, offset=args.offset)
         failed += 0 if ok else 1
         print("dims %s perm %s : %s GB/s %s  [%s]" % (list(dims), list(perm), " ".join("%.1f" % g for g in gbs),
                                                       "OK" if ok else "FAIL", plan))

@@ -149,6 +149,12 @@ static unsigned int* status_word(int dev) {
   return p;
 }
 
+unsigned int* bulk_copy_status_word() {
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess) return nullptr;
+  return status_word(dev);
+}
+
 bool bulk_copy_usable(const void* in, const void* out, size_t bytes) {
   return ((uintptr_t)in % 16 == 0) && ((uintptr_t)out % 16 == 0) && bytes >= (size_t)kBulkChunk;
 }

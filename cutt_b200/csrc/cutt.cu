@@ -138,6 +138,7 @@ bool device_info(int& dev, DeviceInfo& info) {
   d.smemPerSM = v;
   if (cudaDeviceGetAttribute(&v, cudaDevAttrMaxThreadsPerMultiProcessor, dev) != cudaSuccess) return false;
   d.maxThreadsPerSM = v;
+  d.tmaLoads = tma_supported() && !env_flag("CUTT_NO_TMA");
   g_devices[dev] = d;
   info = d;
   return true;
@@ -223,6 +224,19 @@ cudaError_t run_plan(const Plan& p, const void* in, void* out, cudaStream_t stre
     case kMethodRowCopy:
       if ((uintptr_t)in % p.elt || (uintptr_t)out % p.elt) return cudaErrorInvalidValue;
       return launch_rowcopy(p.cand.rc, p.numSM, in, out, stream);
+    case kMethodTma: {
+      // tensor maps and 16-byte stores need 16-byte aligned buffers; others take the tiled kernel
+      // with element-sized accesses
+      if ((uintptr_t)in % 16 == 0 && (uintptr_t)out % 16 == 0)
+        return launch_tma(p.cand.tma, p.cand.tmaMap, p.grid, in, out, stream);
+      if (p.haveFallback) {
+        PeerPtrs pp;
+        for (int i = 0; i < kMaxPeers; i++) pp.p[i] = (unsigned char*)out;
+        return launch_tiles(p.fallback, p.fallbackGrid, in, pp, stream);
+      }
+      if (p.mgMode >= 1) return cudaErrorInvalidValue;   // (no element-wise description of these)
+      return launch_naive(p.naive, p.numSM, in, out, stream);
+    }
     case kMethodTiles: {
       PeerPtrs pp;
       for (int i = 0; i < kMaxPeers; i++) pp.p[i] = (unsigned char*)out;
@@ -254,6 +268,27 @@ std::string plain_label(const Plan& p) {
 bool adopt_candidate(Plan& p, const DeviceInfo& dev, const Candidate& c) {
   p.method = c.method;
   p.cand = c;
+  if (c.method == kMethodTma) {
+    const int nb = tma_blocks_per_sm(p.cand.tma);
+    if (nb <= 0) return false;
+    p.cand.blocksPerSM = nb;
+    long long g = (long long)dev.numSM * nb;
+    if (g > (long long)c.tma.numTiles) g = c.tma.numTiles;
+    p.grid = (int)g;
+    p.cand.gridBlocks = p.grid;
+    // buffers that are not 16-byte aligned: a default tile with element-sized accesses
+    p.haveFallback = false;
+    TileParams tp;
+    tp.maxVecBytes = p.elt;
+    tp.maxVBytes = p.elt;
+    tp.allowAof = 0;
+    Candidate f;
+    if (build_tile(p.prob, tp, dev, f) && finalize_tiles(dev, f, p.fallbackGrid)) {
+      p.fallback = f;
+      p.haveFallback = true;
+    }
+    return true;
+  }
   if (c.method != kMethodTiles) return true;
   if (!finalize_tiles(dev, p.cand, p.grid)) return false;
   p.haveFallback = false;
@@ -302,12 +337,13 @@ struct PlanRequest {
 
 // Values a tile parameter set may take (what the enumerator and the test entry point produce);
 // anything else in a persisted plan cache is a damaged or foreign entry.
-bool valid_tile_params(const TileParams& t) {
+bool valid_tile_params(const TileParams& t, Method method = kMethodTiles) {
   auto one_of = [](int v, std::initializer_list<int> ok) {
     for (int x : ok) if (v == x) return true;
     return false;
   };
-  return one_of(t.nthreads, {64, 128, 256, 512}) && one_of(t.stages, {1, 2}) &&
+  if (method == kMethodTma ? (t.stages < 2 || t.stages > kTmaMaxStages) : (t.stages != 1 && t.stages != 2)) return false;
+  return one_of(t.nthreads, {64, 128, 256, 512}) &&
          one_of(t.maxVecBytes, {4, 8, 16}) && one_of(t.maxVBytes, {4, 8, 16}) &&
          one_of(t.extend, {0, 1}) && one_of(t.loopOrder, {0, 1}) && one_of(t.groupIn, {1, 2, 4}) &&
          one_of(t.groupOut, {1, 2, 4}) && one_of(t.cutInRun, {0, 1}) && one_of(t.allowAof, {0, 1}) &&
@@ -419,6 +455,11 @@ cuttResult make_plan(cuttHandle* handle, int rank, const int* dim, const int* pe
       if (!build_rowcopy(p->prob, dev, c)) return CUTT_INVALID_PARAMETER;
       ok = adopt_candidate(*p, dev, c);
     }
+    else if (req.method == kMethodTma) {
+      Candidate c;
+      if (!dev.tmaLoads || !build_tma(p->prob, req.params, dev, c)) return CUTT_INVALID_PARAMETER;
+      ok = adopt_candidate(*p, dev, c);
+    }
     else if (req.method == kMethodCopy || req.method == kMethodMemcpy) {
       if (!p->prob.identity) return CUTT_INVALID_PARAMETER;
       p->method = (Method)req.method; ok = true;
@@ -452,6 +493,10 @@ cuttResult make_plan(cuttHandle* handle, int rank, const int* dim, const int* pe
         } else if (cc.method == kMethodRowCopy) {
           Candidate c;
           ok = build_rowcopy(p->prob, dev, c) && adopt_candidate(*p, dev, c);
+        } else if (cc.method == kMethodTma) {
+          Candidate c;
+          ok = dev.tmaLoads && valid_tile_params(cc.params, kMethodTma) && build_tma(p->prob, cc.params, dev, c) &&
+               adopt_candidate(*p, dev, c);
         } else if (cc.method == kMethodCopy || cc.method == kMethodMemcpy) {
           ok = p->prob.identity;
           if (ok) p->method = cc.method;
@@ -584,7 +629,7 @@ cuttResult make_plan(cuttHandle* handle, int rank, const int* dim, const int* pe
   if (verbose) {
     Candidate shown = p->cand;
     shown.method = p->method;
-    if (p->method != kMethodTiles && p->method != kMethodRowCopy)
+    if (p->method != kMethodTiles && p->method != kMethodRowCopy && p->method != kMethodTma)
       shown.label = plain_label(*p);
     fprintf(stderr, "[cutt] plan %u (%s): %s\n", *handle, p->note.c_str(),
             canon ? describe(p->prob, shown).c_str() : "naive (rank too high after fusion)");
@@ -725,7 +770,7 @@ int cutt_c_plan_describe(unsigned int handle, char* buf, size_t len) {
   const Plan& p = *it->second;
   Candidate shown = p.cand;
   shown.method = p.method;
-  if (p.method != kMethodTiles && p.method != kMethodRowCopy) shown.label = plain_label(p);
+  if (p.method != kMethodTiles && p.method != kMethodRowCopy && p.method != kMethodTma) shown.label = plain_label(p);
   snprintf(buf, len, "%s", describe(p.prob, shown).c_str());
   return CUTT_SUCCESS;
 }
@@ -764,7 +809,8 @@ int cutt_c_plan_params(unsigned int* handle, int rank, const int* dim, const int
   req.params.maxVecBytes = maxVecBytes;
   req.params.maxVBytes = maxVBytes;
   if (nthreads != 64 && nthreads != 128 && nthreads != 256 && nthreads != 512) return CUTT_INVALID_PARAMETER;
-  if (stages != 1 && stages != 2) return CUTT_INVALID_PARAMETER;
+  if (method == kMethodTma ? (stages < 2 || stages > kTmaMaxStages) : (stages != 1 && stages != 2))
+    return CUTT_INVALID_PARAMETER;
   req.params.nthreads = nthreads;
   req.params.stages = stages;
   return (int)make_plan(handle, rank, dim, permutation, sizeofType, (cudaStream_t)stream, req);
@@ -1115,8 +1161,10 @@ int cutt_c_plan_cache_load(const char* path) {
                &t.peerOrder) != 17)
       continue;
     // winners are tiled plans, row copies or (identity permutations) the two copy methods
-    if (method != kMethodTiles && method != kMethodRowCopy && method != kMethodCopy && method != kMethodMemcpy) continue;
-    if (method == kMethodTiles && !valid_tile_params(t)) continue;
+    if (method != kMethodTiles && method != kMethodRowCopy && method != kMethodCopy && method != kMethodMemcpy &&
+        method != kMethodTma)
+      continue;
+    if ((method == kMethodTiles || method == kMethodTma) && !valid_tile_params(t, (Method)method)) continue;
     c.method = (Method)method;
     plan_cache().put(key, c);
     n++;

@@ -142,6 +142,49 @@ static int run_small(const SmallDesc& plan, const unsigned char* in, unsigned ch
   return 0;
 }
 
+// Tensor-map transpose: the box loads are emulated as the copy engine performs them (128-byte rows,
+// 16-byte chunk c of row r at chunk position c ^ (r & 7), zeros outside the tensor); the store
+// phase is the device code.
+static int run_tma(const Candidate& c, const unsigned char* in, unsigned char* out, size_t bytes,
+                   unsigned char* outLo = nullptr, unsigned char* outHi = nullptr) {
+  const TmaDesc& D = c.tma;
+  const TmaMapRecipe& R = c.tmaMap;
+  HostBounds& b = host_bounds();
+  b.gin0 = in; b.gin1 = in + bytes; b.violations = 0;
+  b.gout0 = outLo ? outLo : out; b.gout1 = outHi ? outHi : out + bytes;
+  const uint32_t elt = D.elt, V = 16 / elt;
+  const size_t stageBytes = (size_t)D.ta * D.tb * elt;
+  std::vector<unsigned char> raw(stageBytes + 1024 + 16);
+  unsigned char* stage = raw.data() + (1024 - ((uintptr_t)raw.data() & 1023)) % 1024;
+  b.s0 = stage; b.s1 = stage + stageBytes;
+  for (uint32_t tile = 0; tile < D.numTiles; tile++) {
+    TmaTile t;
+    tma_decode(D, tile, t);
+    memset(stage, 0xEE, stageBytes);
+    for (uint32_t k = 0; k < D.nboxes; k++)
+      for (uint32_t row = 0; row < D.tb; row++)
+        for (uint32_t chunk = 0; chunk < 8; chunk++)
+          for (uint32_t e = 0; e < V; e++) {
+            const uint64_t x[5] = {(uint64_t)t.c0 + k * (128 / elt) + chunk * V + e, (uint64_t)t.cp + row,
+                                   t.co[0], t.co[1], t.co[2]};
+            unsigned char* dst = stage + k * (D.tb * 128) + row * 128 + ((chunk ^ (row & 7u)) << 4) + e * elt;
+            bool inside = true;
+            for (int i = 0; i < 5; i++) inside = inside && x[i] < R.dims[i];
+            if (!inside) { memset(dst, 0, elt); continue; }
+            size_t off = (size_t)x[0] * elt;
+            for (int i = 1; i < 5; i++) off += (size_t)x[i] * R.strideBytes[i - 1];
+            if (off + elt > bytes) return 9;
+            memcpy(dst, in + off, elt);
+          }
+    const uint32_t nItems = tma_items_per_tile(D);
+    for (uint32_t it = 0; it < nItems; it++) {
+      if (elt == 4) tma_store_item<4>(D, t, stage, out, it);
+      else tma_store_item<8>(D, t, stage, out, it);
+    }
+  }
+  return b.violations ? 9 : 0;
+}
+
 static DeviceInfo g_dev;
 
 // Candidate list of the last problem asked for (tests run candidate 0, 1, 2, ... of one problem
@@ -188,7 +231,22 @@ int cutt_hostcheck_run(int rank, const int* dim, const int* perm, int elt, int i
     return 0;
   }
   if (c.method == kMethodRowCopy) return run_rowcopy(c.rc, (const unsigned char*)in, (unsigned char*)out, (size_t)P.volume * elt);
+  if (c.method == kMethodTma) return run_tma(c, (const unsigned char*)in, (unsigned char*)out, (size_t)P.volume * elt);
   return dispatch_checked(c.desc, (const unsigned char*)in, (unsigned char*)out, (size_t)P.volume * elt);
+}
+
+// Tensor-map transpose with explicit parameters (tile bytes along the two dimensions, stages,
+// threads, tile order).  Returns 2 when the problem is outside the method's class.
+int cutt_hostcheck_run_tma(int rank, const int* dim, const int* perm, int elt, unsigned taBytes, unsigned tbBytes,
+                           int stages, int nthreads, int order, const void* in, void* out, char* label, int labelLen) {
+  Problem P;
+  if (!problem_from_cutt(rank, dim, perm, elt, P)) return 2;
+  TileParams tp;
+  tp.tinBytes = taBytes; tp.toutBytes = tbBytes; tp.stages = stages; tp.nthreads = nthreads; tp.loopOrder = order;
+  Candidate c;
+  if (!build_tma(P, tp, g_dev, c)) return 2;
+  if (label && labelLen > 0) snprintf(label, labelLen, "%s", describe(P, c).c_str());
+  return run_tma(c, (const unsigned char*)in, (unsigned char*)out, (size_t)P.volume * elt);
 }
 
 // Extension element sizes (1, 2, 16 bytes besides 4 and 8): the problem as the library re-states
@@ -223,6 +281,7 @@ int cutt_hostcheck_run_ext(int rank, const int* dim, const int* perm, int eltByt
   if (label && labelLen > 0) snprintf(label, labelLen, "%s", describe(P, c).c_str());
   if (c.method == kMethodCopy || c.method == kMethodMemcpy) { memcpy(out, in, bytes); return 0; }
   if (c.method == kMethodRowCopy) return run_rowcopy(c.rc, (const unsigned char*)in, (unsigned char*)out, bytes);
+  if (c.method == kMethodTma) return run_tma(c, (const unsigned char*)in, (unsigned char*)out, bytes);
   return dispatch_checked(c.desc, (const unsigned char*)in, (unsigned char*)out, bytes);
 }
 
@@ -323,6 +382,9 @@ int cutt_hostcheck_run_chunked(int rank, const int* dim, const int* perm, int el
     }
     if (c.method == kMethodCopy || c.method == kMethodMemcpy) {
       memcpy(pout, pin, (size_t)P.volume * elt);
+    } else if (c.method == kMethodTma) {
+      if ((uintptr_t)pin % 16 || (uintptr_t)pout % 16) return 7;   // (the library would take its fallback tile)
+      if (run_tma(c, pin, pout, (size_t)P.volume * elt, (unsigned char*)out, (unsigned char*)out + total)) return 9;
     } else if (c.method == kMethodRowCopy) {
       rowcopy_bounds().in0 = pin; rowcopy_bounds().in1 = pin + (size_t)P.volume * elt;
       rowcopy_bounds().out0 = (unsigned char*)out; rowcopy_bounds().out1 = (unsigned char*)out + total;

@@ -37,6 +37,15 @@ cudaError_t launch_bulk_copy(const void* in, void* out, size_t bytes16, int numS
 cudaError_t launch_bulk_copy_with_status(const void* in, void* out, size_t bytes16, int numSM,
                                          unsigned int* status, cudaStream_t stream);
 int bulk_copy_timeouts();
+// Device word of the current device in which kernels count bounded waits that ran out (allocated
+// on first use; null if that fails).
+unsigned int* bulk_copy_status_word();
+
+// Tensor-map (TMA) transpose (tma_transpose.cu, tma_transpose.h).
+bool tma_supported();                       // the driver exports cuTensorMapEncodeTiled
+int tma_blocks_per_sm(const TmaDesc& D);    // resident blocks per SM (<= 0 on error)
+cudaError_t launch_tma(const TmaDesc& D, const TmaMapRecipe& R, int gridBlocks, const void* in, void* out,
+                       cudaStream_t stream);
 cudaError_t launch_rowcopy(const RowCopyDesc& d, int numSM, const void* in, void* out, cudaStream_t stream);
 
 // Permutation of 1- or 2-byte elements, one tile per block (small_elt.cu).

@@ -740,6 +740,95 @@ bool build_rowcopy(const Problem& P, const DeviceInfo& dev, Candidate& out) {
   return true;
 }
 
+bool build_tma(const Problem& P, const TileParams& tp, const DeviceInfo& dev, Candidate& out) {
+  const int r = P.rank;
+  const int elt = P.elt;
+  if (elt != 4 && elt != 8) return false;
+  if (r < 2 || r > 5 || P.peerDim >= 0 || P.inBase != 0 || P.outBase != 0 || P.identity) return false;
+  if (P.is[0] != 1) return false;
+  int p = 0;
+  for (int j = 1; j < r; j++) if (P.os[j] < P.os[p]) p = j;
+  if (p == 0 || P.os[p] != 1) return false;
+  const int64_t VE = 16 / elt;
+  for (int j = 0; j < r; j++) {
+    if (P.d[j] >= (1ll << 31)) return false;
+    if (j >= 1 && (P.is[j] % VE != 0 || P.is[j] * elt >= (1ll << 40))) return false;
+    if (j != p && P.os[j] % VE != 0) return false;
+  }
+  if (P.d[0] % VE != 0 || P.d[p] % VE != 0) return false;
+  const uint32_t ta = tp.tinBytes / elt, tb = tp.toutBytes / elt;
+  if (ta == 0 || (ta * elt) % 128 != 0 || ta * elt > 512) return false;
+  if (tb == 0 || tb % (8 * VE) != 0 || tb > 256) return false;
+  if (tp.stages < 2 || tp.stages > kTmaMaxStages) return false;
+  if (tp.nthreads != 128 && tp.nthreads != 256) return false;
+  // tiles far larger than the tensor along either dimension would be mostly padding
+  if (P.d[0] * elt < 64 || P.d[p] < (int64_t)tb / 4) return false;
+
+  out = Candidate();
+  out.method = kMethodTma;
+  out.params = tp;
+  TmaDesc& D = out.tma;
+  memset(&D, 0, sizeof D);
+  D.elt = elt;
+  D.ta = ta;
+  D.tb = tb;
+  D.nboxes = ta * elt / 128;
+  D.cbShift = ilog2_exact(ta * elt / 64);
+  if ((1u << D.cbShift) != ta * elt / 64) return false;
+  D.stages = tp.stages;
+  D.nthreads = tp.nthreads;
+  D.order = tp.loopOrder ? 1 : 0;
+  D.d0 = (uint32_t)P.d[0];
+  D.dp = (uint32_t)P.d[p];
+  D.nA = (uint32_t)ceil_div(P.d[0], ta);
+  D.nB = (uint32_t)ceil_div(P.d[p], tb);
+  D.divA = make_fastdiv(D.nA);
+  D.divB = make_fastdiv(D.nB);
+  D.os0 = P.os[0];
+  TmaMapRecipe& R = out.tmaMap;
+  memset(&R, 0, sizeof R);
+  for (int i = 0; i < 5; i++) { R.dims[i] = 1; R.box[i] = 1; }
+  for (int i = 0; i < 4; i++) R.strideBytes[i] = 16;   // (extent-1 dimensions: any legal stride)
+  R.dims[0] = (uint64_t)P.d[0];
+  R.box[0] = 128 / elt;
+  R.dims[1] = (uint64_t)P.d[p];
+  R.strideBytes[0] = (uint64_t)P.is[p] * elt;
+  R.box[1] = tb;
+  int64_t ntiles = (int64_t)D.nA * D.nB;
+  D.nOuter = 0;
+  for (int j = 1; j < r; j++) {
+    if (j == p) continue;
+    const uint32_t k = D.nOuter++;
+    D.nO[k] = (uint32_t)P.d[j];
+    D.divO[k] = make_fastdiv(D.nO[k]);
+    D.osO[k] = P.os[j];
+    R.dims[2 + k] = (uint64_t)P.d[j];
+    R.strideBytes[1 + k] = (uint64_t)P.is[j] * elt;
+    ntiles *= P.d[j];
+    if (ntiles >= (1ll << 31)) return false;
+  }
+  for (uint32_t k = D.nOuter; k < 3; k++) { D.nO[k] = 1; D.divO[k] = make_fastdiv(1); D.osO[k] = 0; }
+  D.numTiles = (uint32_t)ntiles;
+  out.smemBytes = (int)(D.stages * ta * tb * elt + 1024);
+  if (out.smemBytes > dev.maxSmemPerBlock) return false;
+  int bps = std::min(dev.smemPerSM / (out.smemBytes + 1024), dev.maxThreadsPerSM / tp.nthreads);
+  bps = std::max(1, std::min(bps, 16));
+  out.blocksPerSM = bps;
+  out.gridBlocks = (int)std::min<int64_t>(ntiles, (int64_t)dev.numSM * bps);
+  // Estimate: the copy rate, reduced by the share of each tile that lies outside the tensor and,
+  // for tensors too small to give every SM a few tiles, by the idle SMs.  Measured on B200: within
+  // its class this kernel runs at or above the rate of the best cp.async tile plan.
+  const double util = ((double)P.d[0] / ((double)D.nA * ta)) * ((double)P.d[p] / ((double)D.nB * tb));
+  const double fill = std::min(1.0, (double)ntiles / ((double)dev.numSM * 2.0));
+  const double eff = 0.96 * util * (0.25 + 0.75 * fill);
+  out.cost = 2.0 * (double)P.volume * elt / (dev.hbmGBs * 1e9 * eff) + 5e-6;
+  char buf[160];
+  snprintf(buf, sizeof buf, "tma t=%ux%u boxes=%u st=%u lo=%u nt=%u smem=%d tiles=%u", ta, tb, D.nboxes, D.stages,
+           D.order, D.nthreads, out.smemBytes, D.numTiles);
+  out.label = buf;
+  return true;
+}
+
 std::vector<Candidate> enumerate_candidates(const Problem& P, const DeviceInfo& dev) {
   std::vector<Candidate> res;
   if (P.identity) {
@@ -831,6 +920,20 @@ std::vector<Candidate> enumerate_candidates(const Problem& P, const DeviceInfo& 
     Candidate rc;
     if (build_rowcopy(P, dev, rc)) res.push_back(rc);
   }
+  // tensor-map transposes (legal strides only): a few tile shapes, both tile orders
+  if (dev.tmaLoads) {
+    const uint32_t ta[] = {128, 256}, tbB[] = {128, 256};
+    for (uint32_t a : ta)
+      for (uint32_t b : tbB)
+        for (int lo = 0; lo < 2; lo++)
+          for (int nt = 128; nt <= 256; nt *= 2) {
+            TileParams tp;
+            tp.tinBytes = a; tp.toutBytes = b; tp.loopOrder = lo; tp.nthreads = nt;
+            tp.stages = (a * b / (uint32_t)P.elt <= 8192) ? 4 : 3;
+            Candidate c;
+            if (build_tma(P, tp, dev, c)) res.push_back(c);
+          }
+  }
   std::stable_sort(res.begin(), res.end(), [](const Candidate& a, const Candidate& b) { return a.cost < b.cost; });
   return res;
 }
@@ -847,7 +950,8 @@ std::string describe(const Problem& P, const Candidate& c) {
            "{\"method\": %d, \"label\": \"%s\", \"fused_dims\": [%s], \"istride\": [%s], \"ostride\": [%s], "
            "\"elt\": %d, \"num_tiles\": %u, \"grid\": %d, \"smem\": %d, \"model_us\": %.2f, \"feat\": [",
            (int)c.method, c.label.c_str(), dims.c_str(), iss.c_str(), oss.c_str(), P.elt,
-           c.method == kMethodTiles ? c.desc.numTiles : 0u, c.gridBlocks, c.smemBytes, c.cost * 1e6);
+           c.method == kMethodTiles ? c.desc.numTiles : (c.method == kMethodTma ? c.tma.numTiles : 0u), c.gridBlocks,
+           c.smemBytes, c.cost * 1e6);
   std::string res = buf;
   for (int i = 0; i < kNumFeatures; i++) {
     snprintf(buf, sizeof buf, "%s%.4g", i ? "," : "", c.method == kMethodTiles ? (double)c.feat[i] : 0.0);

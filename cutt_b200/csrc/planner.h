@@ -11,6 +11,7 @@
 #include <vector>
 #include "permute_desc.h"
 #include "rowcopy_impl.h"
+#include "tma_transpose.h"
 
 namespace cuttb {
 
@@ -20,6 +21,7 @@ struct DeviceInfo {
   int smemPerSM = 228 * 1024;
   int maxThreadsPerSM = 2048;
   double hbmGBs = 6500.0;            // attainable copy bandwidth used by the cost model
+  bool tmaLoads = true;              // tensor-map loads available (the driver exports the encoder)
 };
 
 // A permutation as a strided copy, dimensions sorted by input stride, fused.
@@ -78,6 +80,7 @@ enum Method : int {
   kMethodNaive = 3,    // one thread per output element (fallback for rank > kMaxDims, debug)
   kMethodRowCopy = 4,  // strided copy of contiguous rows with register shifting (rowcopy_impl.h)
   kMethodSmall = 5,    // 1- and 2-byte elements moved one by one (small_elt_impl.h)
+  kMethodTma = 6,      // tensor-map box loads into swizzled shared memory (tma_transpose.h)
 };
 
 struct TileParams {
@@ -112,6 +115,8 @@ struct Candidate {
   TileParams params;
   TileDesc desc;
   RowCopyDesc rc;              // kMethodRowCopy only
+  TmaDesc tma;                 // kMethodTma only
+  TmaMapRecipe tmaMap;         // kMethodTma only
   int smemBytes = 0;
   int blocksPerSM = 1;
   int gridBlocks = 0;
@@ -124,6 +129,14 @@ struct Candidate {
 // false when the same tile extents and launch options were already built (enumeration dedup).
 bool build_tile(const Problem& P, const TileParams& tp, const DeviceInfo& dev, Candidate& out,
                 std::set<std::string>* seenExtents = nullptr);
+
+// Tensor-map transpose candidate (tma_transpose.h): tile of taBytes along dimension 0 by tbElems
+// along the output's fastest dimension; false if the problem is outside the class (strides not
+// multiples of 16 bytes, fused rank above 5, fastest dimension kept, ...).  The parameters travel
+// in a TileParams so that the plan cache stores them like any other choice:
+// tinBytes = bytes along dimension 0, toutBytes = bytes along dimension p, stages, nthreads,
+// loopOrder = which of the two varies fastest in the tile index.
+bool build_tma(const Problem& P, const TileParams& tp, const DeviceInfo& dev, Candidate& out);
 
 // Row-copy candidate for problems whose fastest dimension is kept; false if not applicable.
 bool build_rowcopy(const Problem& P, const DeviceInfo& dev, Candidate& out);

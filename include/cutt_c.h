@@ -60,7 +60,12 @@ int cutt_c_plan_candidate(unsigned int* handle, int rank, const int* dim, const 
 
 /* Plan with an explicit tile parameter choice (tests; see TileParams in planner.h).
  * method: 2 = tiled kernel, 3 = one-thread-per-element kernel, 4 = strided row copy (fastest
- * dimension kept), 0 = copy kernel (identity only), 1 = cudaMemcpyAsync (identity only). */
+ * dimension kept), 0 = copy kernel (identity only), 1 = cudaMemcpyAsync (identity only),
+ * 6 = tensor-map (TMA) transpose: tinBytes = tile bytes along the input's fastest dimension (128,
+ * 256 or 512), toutBytes = tile bytes along the output's fastest dimension (a multiple of 128, at
+ * most 256 elements), stages 2-8, nthreads 128 or 256, loopOrder = which of the two runs fastest
+ * in the tile order; CUTT_INVALID_PARAMETER when a stride of the problem is not a multiple of 16
+ * bytes, its fused rank exceeds 5 or the fastest dimension does not move. */
 int cutt_c_plan_params(unsigned int* handle, int rank, const int* dim, const int* permutation,
                        size_t sizeofType, void* stream, int method, unsigned tinBytes,
                        unsigned toutBytes, unsigned vtargetBytes, int extend, int loopOrder,

@@ -237,3 +237,75 @@ def test_wide_row_offsets(hc, oracle_mod):
         assert wide > 20
     finally:
         hc.cutt_hostcheck_force_wide(0)
+
+
+def _tma(hc):
+    hc.cutt_hostcheck_run_tma.argtypes = [ctypes.c_int, ctypes.POINTER(ctypes.c_int), ctypes.POINTER(ctypes.c_int),
+                                          ctypes.c_int, ctypes.c_uint, ctypes.c_uint, ctypes.c_int, ctypes.c_int,
+                                          ctypes.c_int, ctypes.c_void_p, ctypes.c_void_p, ctypes.c_char_p, ctypes.c_int]
+    return hc.cutt_hostcheck_run_tma
+
+
+@pytest.mark.parametrize("dims,perm", [
+    ([64, 64], [1, 0]), ([132, 200], [1, 0]), ([36, 8, 44], [2, 1, 0]), ([40, 6, 52], [1, 2, 0]),
+    ([72, 3, 5, 56], [3, 0, 2, 1]), ([24, 4, 3, 2, 40], [4, 2, 0, 3, 1]), ([256, 96, 3], [1, 0, 2]),
+    ([16, 10, 36], [2, 0, 1]),
+])
+def test_tensor_map_transpose(hc, oracle_mod, dims, perm):
+    """The tensor-map method on the host: box loads emulated (128-byte swizzle, zero fill outside
+    the tensor), store phase = the device code, every access range- and alignment-checked.  All
+    tile shapes, both tile orders, both element sizes; edge tiles in both dimensions."""
+    run = _tma(hc)
+    ran = 0
+    for elt in (4, 8):
+        a = raw_bits(volume(dims), elt, 41)
+        want = oracle_mod.transpose_blocked(dims, perm, a)
+        for ta in (128, 256, 512):
+            for tb in (128, 256, 512):
+                for order in (0, 1):
+                    out = np.full_like(a, 0xAB)
+                    lab = ctypes.create_string_buffer(2048)
+                    rc = run(len(dims), _iarr(dims), _iarr(perm), elt, ta, tb, 3, 128, order, a.ctypes.data,
+                             out.ctypes.data, lab, 2048)
+                    if rc == 2:
+                        continue          # this tile shape does not apply to this problem
+                    assert rc == 0, (rc, dims, perm, elt, ta, tb)
+                    assert np.array_equal(out, want), (dims, perm, elt, ta, tb, order, lab.value.decode())
+                    ran += 1
+    assert ran >= 8, ran
+
+
+def test_tensor_map_transpose_rejects_what_it_cannot_do(hc):
+    run = _tma(hc)
+    a = np.zeros(1 << 16, dtype=np.uint64)
+    out = np.zeros_like(a)
+
+    def rc(dims, perm, elt, ta=128, tb=128):
+        return run(len(dims), _iarr(dims), _iarr(perm), elt, ta, tb, 3, 128, 0, a.ctypes.data, out.ctypes.data, None, 0)
+
+    assert rc([64, 64], [1, 0], 4) == 0
+    assert rc([66, 64], [1, 0], 4) == 2            # input rows of 264 bytes: not a multiple of 16
+    assert rc([64, 66], [1, 0], 4) == 2            # output rows of 264 bytes
+    assert rc([66, 64], [1, 0], 8) == 0            # the same extents are legal for 8-byte elements
+    assert rc([64, 8, 64], [0, 2, 1], 4) == 2      # fastest dimension kept: not a transpose
+    assert rc([64, 64], [0, 1], 4) == 2            # identity
+    assert rc([16, 2, 2, 2, 2, 2, 16], [6, 5, 4, 3, 2, 1, 0], 4) == 2   # fused rank 7 > 5
+    assert rc([64, 64], [1, 0], 4, ta=192) == 2    # tile bytes along dimension 0 must be 128, 256 or 512
+    assert rc([64, 64], [1, 0], 4, tb=96) == 2     # 24 rows: not a multiple of 32
+
+
+def test_tensor_map_candidates_are_enumerated_for_legal_strides_only(hc):
+    def labels(dims, perm, elt):
+        n = hc.cutt_hostcheck_num_candidates(len(dims), _iarr(dims), _iarr(perm), elt)
+        a = np.zeros(volume(dims), dtype=np.uint32 if elt == 4 else np.uint64)
+        out = np.zeros_like(a)
+        res = []
+        for i in range(n):
+            lab = ctypes.create_string_buffer(2048)
+            assert hc.cutt_hostcheck_run(len(dims), _iarr(dims), _iarr(perm), elt, i, a.ctypes.data, out.ctypes.data,
+                                         lab, 2048) == 0
+            res.append(json.loads(lab.value.decode())["label"])
+        return res
+    assert any(l.startswith("tma ") for l in labels([128, 96], [1, 0], 4))
+    assert any(l.startswith("tma ") for l in labels([130, 98], [1, 0], 8))
+    assert not any(l.startswith("tma ") for l in labels([130, 98], [1, 0], 4))
