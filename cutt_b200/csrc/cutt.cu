@@ -270,7 +270,7 @@ bool adopt_candidate(Plan& p, const DeviceInfo& dev, const Candidate& c) {
   p.cand = c;
   if (c.method == kMethodTma) {
     const int nb = tma_blocks_per_sm(p.cand.tma);
-    if (nb <= 0) return false;
+    if (nb <= 0 || !tma_map_encodable(p.cand.tma, p.cand.tmaMap)) return false;
     p.cand.blocksPerSM = nb;
     long long g = (long long)dev.numSM * nb;
     if (g > (long long)c.tma.numTiles) g = c.tma.numTiles;

@@ -165,8 +165,10 @@ static int run_tma(const Candidate& c, const unsigned char* in, unsigned char* o
       for (uint32_t row = 0; row < D.tb; row++)
         for (uint32_t chunk = 0; chunk < 8; chunk++)
           for (uint32_t e = 0; e < V; e++) {
-            const uint64_t x[5] = {(uint64_t)t.c0 + k * (128 / elt) + chunk * V + e, (uint64_t)t.cp + row,
-                                   t.co[0], t.co[1], t.co[2]};
+            int b0, b1, b2, b3, b4;
+            tma_box_coords(D, t, k, b0, b1, b2, b3, b4);
+            uint64_t x[5] = {(uint64_t)b0 + chunk * V + e, (uint64_t)b1, (uint64_t)b2, (uint64_t)b3, (uint64_t)b4};
+            x[D.pSlot] += row;
             unsigned char* dst = stage + k * (D.tb * 128) + row * 128 + ((chunk ^ (row & 7u)) << 4) + e * elt;
             bool inside = true;
             for (int i = 0; i < 5; i++) inside = inside && x[i] < R.dims[i];

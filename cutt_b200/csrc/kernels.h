@@ -44,6 +44,7 @@ unsigned int* bulk_copy_status_word();
 // Tensor-map (TMA) transpose (tma_transpose.cu, tma_transpose.h).
 bool tma_supported();                       // the driver exports cuTensorMapEncodeTiled
 int tma_blocks_per_sm(const TmaDesc& D);    // resident blocks per SM (<= 0 on error)
+bool tma_map_encodable(const TmaDesc& D, const TmaMapRecipe& R);
 cudaError_t launch_tma(const TmaDesc& D, const TmaMapRecipe& R, int gridBlocks, const void* in, void* out,
                        cudaStream_t stream);
 cudaError_t launch_rowcopy(const RowCopyDesc& d, int numSM, const void* in, void* out, cudaStream_t stream);

@@ -788,12 +788,16 @@ bool build_tma(const Problem& P, const TileParams& tp, const DeviceInfo& dev, Ca
   TmaMapRecipe& R = out.tmaMap;
   memset(&R, 0, sizeof R);
   for (int i = 0; i < 5; i++) { R.dims[i] = 1; R.box[i] = 1; }
-  for (int i = 0; i < 4; i++) R.strideBytes[i] = 16;   // (extent-1 dimensions: any legal stride)
-  R.dims[0] = (uint64_t)P.d[0];
+  // the tensor map lists the dimensions in input order (ascending strides); dimension p sits at
+  // slot p, the loop dimensions fill the other slots in order
+  for (int j = 0; j < r; j++) {
+    R.dims[j] = (uint64_t)P.d[j];
+    if (j >= 1) R.strideBytes[j - 1] = (uint64_t)P.is[j] * elt;
+  }
+  for (int j = r; j < 5; j++) R.strideBytes[j - 1] = R.strideBytes[j - 2] * R.dims[j - 1];
   R.box[0] = 128 / elt;
-  R.dims[1] = (uint64_t)P.d[p];
-  R.strideBytes[0] = (uint64_t)P.is[p] * elt;
-  R.box[1] = tb;
+  R.box[p] = tb;
+  D.pSlot = (uint32_t)p;
   int64_t ntiles = (int64_t)D.nA * D.nB;
   D.nOuter = 0;
   for (int j = 1; j < r; j++) {
@@ -802,8 +806,6 @@ bool build_tma(const Problem& P, const TileParams& tp, const DeviceInfo& dev, Ca
     D.nO[k] = (uint32_t)P.d[j];
     D.divO[k] = make_fastdiv(D.nO[k]);
     D.osO[k] = P.os[j];
-    R.dims[2 + k] = (uint64_t)P.d[j];
-    R.strideBytes[1 + k] = (uint64_t)P.is[j] * elt;
     ntiles *= P.d[j];
     if (ntiles >= (1ll << 31)) return false;
   }

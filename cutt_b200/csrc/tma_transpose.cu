@@ -88,9 +88,11 @@ tma_transpose_kernel(const __grid_constant__ CUtensorMap tm, const __grid_consta
     const uint32_t s = i % S;
     const uint32_t bar = bar0 + 8u * s;
     tma_mbar_expect_tx(bar, stageBytes);
-    for (uint32_t k = 0; k < D.nboxes; k++)
-      tma_load_box(sbase + s * stageBytes + k * (D.tb * kTmaBoxBytes), &tm, bar,
-                   (int)(t.c0 + k * (kTmaBoxBytes / ELT)), (int)t.cp, (int)t.co[0], (int)t.co[1], (int)t.co[2]);
+    for (uint32_t k = 0; k < D.nboxes; k++) {
+      int c0, c1, c2, c3, c4;
+      tma_box_coords(D, t, k, c0, c1, c2, c3, c4);
+      tma_load_box(sbase + s * stageBytes + k * (D.tb * kTmaBoxBytes), &tm, bar, c0, c1, c2, c3, c4);
+    }
   };
 
   uint32_t issued = 0;
@@ -184,12 +186,18 @@ int tma_blocks_per_sm(const TmaDesc& D) {
   return nb;
 }
 
-cudaError_t launch_tma(const TmaDesc& D, const TmaMapRecipe& R, int gridBlocks, const void* in, void* out,
-                       cudaStream_t stream) {
-  EncodeTiledFn enc = encode_fn();
-  if (!enc) return cudaErrorNotSupported;
-  if ((uintptr_t)in % 16 || (uintptr_t)out % 16) return cudaErrorInvalidValue;
+static bool tma_encode(const TmaDesc& D, const TmaMapRecipe& R, const void* in, CUtensorMap& tm);
+
+// The driver accepts this problem's tensor map (checked once, when a plan adopts the candidate; the
+// encoder looks at the numbers only, so any 16-byte aligned address will do).
+bool tma_map_encodable(const TmaDesc& D, const TmaMapRecipe& R) {
   CUtensorMap tm;
+  return tma_encode(D, R, reinterpret_cast<const void*>((uintptr_t)1 << 20), tm);
+}
+
+static bool tma_encode(const TmaDesc& D, const TmaMapRecipe& R, const void* in, CUtensorMap& tm) {
+  EncodeTiledFn enc = encode_fn();
+  if (!enc) return false;
   cuuint64_t dims[5], strides[4];
   cuuint32_t box[5], estr[5];
   for (int i = 0; i < 5; i++) { dims[i] = R.dims[i]; box[i] = R.box[i]; estr[i] = 1; }
@@ -198,7 +206,15 @@ cudaError_t launch_tma(const TmaDesc& D, const TmaMapRecipe& R, int gridBlocks, 
                          const_cast<void*>(in), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
                          CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
                          CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
-  if (r != CUDA_SUCCESS) return cudaErrorInvalidValue;
+  return r == CUDA_SUCCESS;
+}
+
+cudaError_t launch_tma(const TmaDesc& D, const TmaMapRecipe& R, int gridBlocks, const void* in, void* out,
+                       cudaStream_t stream) {
+  if (!tma_supported()) return cudaErrorNotSupported;
+  if ((uintptr_t)in % 16 || (uintptr_t)out % 16) return cudaErrorInvalidValue;
+  CUtensorMap tm;
+  if (!tma_encode(D, R, in, tm)) return cudaErrorInvalidValue;
   const void* k = tma_kernel(D);
   cudaError_t e = tma_ensure_smem(k);
   if (e != cudaSuccess) return e;

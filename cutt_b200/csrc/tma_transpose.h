@@ -44,14 +44,16 @@ struct TmaDesc {
   uint32_t nA, nB;     // tiles along dimension 0 / dimension p
   uint32_t nOuter;     // loop dimensions beside the two tile dimensions (0..3)
   uint32_t nO[3];
-  uint32_t pad_;
+  uint32_t pSlot;      // position (1..4) of dimension p among the tensor map's dimensions
   FastDiv divA, divB, divO[3];
   int64_t os0;         // output stride of dimension 0 (elements)
   int64_t osO[3];      // output strides of the loop dimensions
 };
 
-// What cuTensorMapEncodeTiled needs for the input tensor (host side only): dimension 0, then
-// dimension p, then the loop dimensions; unused trailing dimensions have extent 1.
+// What cuTensorMapEncodeTiled needs for the input tensor (host side only): the problem's
+// dimensions in input order (ascending strides, as for any dense tensor); the box is 128 bytes
+// along dimension 0, tb along dimension p (slot pSlot) and 1 elsewhere; unused trailing dimensions
+// have extent 1.
 struct TmaMapRecipe {
   uint64_t dims[5];
   uint64_t strideBytes[4];   // strides of dimensions 1..4
@@ -87,6 +89,17 @@ CUTT_HD void tma_decode(const TmaDesc& D, uint32_t tile, TmaTile& t) {
     t.co[k] = c;
     t.outOff += (int64_t)c * D.osO[k];
   }
+}
+
+// Coordinates of box k of tile t in the order of the tensor map's dimensions: dimension 0, then
+// the loop dimensions with dimension p inserted at slot pSlot.
+CUTT_HD void tma_box_coords(const TmaDesc& D, const TmaTile& t, uint32_t k, int& c0, int& c1, int& c2, int& c3, int& c4) {
+  const uint32_t p = D.pSlot;
+  c0 = (int)(t.c0 + k * (kTmaBoxBytes / D.elt));
+  c1 = (int)(p == 1 ? t.cp : t.co[0]);
+  c2 = (int)(p == 1 ? t.co[0] : (p == 2 ? t.cp : t.co[1]));
+  c3 = (int)(p <= 2 ? t.co[1] : (p == 3 ? t.cp : t.co[2]));
+  c4 = (int)(p == 4 ? t.cp : t.co[2]);
 }
 
 CUTT_HD uint32_t tma_items_per_tile(const TmaDesc& D) {
