@@ -24,10 +24,10 @@ GENCODE = ["-gencode", "arch=compute_100a,code=sm_100a"]
 NVCC_FLAGS = ["-O3", "-std=c++17", "-lineinfo", "-Xcompiler", "-fPIC", "-Xptxas", "-v"] + GENCODE
 CXX_FLAGS = ["-O2", "-std=c++17", "-fPIC", "-Wall", "-Wno-unknown-pragmas"]
 
-CU_SOURCES = ["kernels.cu", "bulk_copy.cu", "small_elt.cu", "tma_transpose.cu", "cutt.cu"]
+CU_SOURCES = ["kernels.cu", "bulk_copy.cu", "small_elt.cu", "tma_transpose.cu", "tile2d.cu", "cutt.cu"]
 CXX_SOURCES = ["planner.cpp"]
 HEADERS = ["permute_desc.h", "permute_tile_impl.h", "planner.h", "kernels.h", "cost_model_data.h", "rowcopy_impl.h", "small_elt_impl.h",
-           "tma_transpose.h",
+           "tma_transpose.h", "tile2d.h",
            os.path.join("..", "..", "include", "cutt.h"), os.path.join("..", "..", "include", "cutt_c.h"),
            os.path.join("..", "..", "include", "cutt_mg.h")]
 

@@ -224,6 +224,17 @@ cudaError_t run_plan(const Plan& p, const void* in, void* out, cudaStream_t stre
     case kMethodRowCopy:
       if ((uintptr_t)in % p.elt || (uintptr_t)out % p.elt) return cudaErrorInvalidValue;
       return launch_rowcopy(p.cand.rc, p.numSM, in, out, stream);
+    case kMethodT2d: {
+      if (t2d_pointers_aligned(p.cand.t2d, in, out)) return launch_t2d(p.cand.t2d, in, out, stream);
+      if (p.haveFallback) {   // the same tile with element-sized accesses
+        if (p.fallback.method == kMethodT2d) return launch_t2d(p.fallback.t2d, in, out, stream);
+        PeerPtrs pp;
+        for (int i = 0; i < kMaxPeers; i++) pp.p[i] = (unsigned char*)out;
+        return launch_tiles(p.fallback, p.fallbackGrid, in, pp, stream);
+      }
+      if (p.mgMode >= 1) return cudaErrorInvalidValue;
+      return launch_naive(p.naive, p.numSM, in, out, stream);
+    }
     case kMethodTma: {
       // tensor maps and 16-byte stores need 16-byte aligned buffers; others take the tiled kernel
       // with element-sized accesses
@@ -268,12 +279,32 @@ std::string plain_label(const Plan& p) {
 bool adopt_candidate(Plan& p, const DeviceInfo& dev, const Candidate& c) {
   p.method = c.method;
   p.cand = c;
+  if (c.method == kMethodT2d) {
+    const int nb = t2d_blocks_per_sm(p.cand.t2d);
+    if (nb <= 0) return false;
+    p.cand.blocksPerSM = nb;
+    p.grid = (int)c.t2d.numTiles;
+    p.cand.gridBlocks = p.grid;
+    p.haveFallback = false;
+    if (c.t2d.wiB > (uint32_t)p.elt || c.t2d.woB > (uint32_t)p.elt) {
+      TileParams tp = c.params;
+      tp.maxVecBytes = p.elt;
+      Candidate f;
+      if (build_t2d(p.prob, tp, dev, f) && t2d_blocks_per_sm(f.t2d) > 0) {
+        p.fallback = f;
+        p.fallbackGrid = (int)f.t2d.numTiles;
+        p.haveFallback = true;
+      }
+    }
+    return true;
+  }
   if (c.method == kMethodTma) {
     const int nb = tma_blocks_per_sm(p.cand.tma);
     if (nb <= 0 || !tma_map_encodable(p.cand.tma, p.cand.tmaMap)) return false;
     p.cand.blocksPerSM = nb;
     long long g = (long long)dev.numSM * nb;
-    if (g > (long long)c.tma.numTiles) g = c.tma.numTiles;
+    // a single stage means one tile per block: the hardware block scheduler replaces the ring
+    if (g > (long long)c.tma.numTiles || c.tma.stages == 1) g = c.tma.numTiles;
     p.grid = (int)g;
     p.cand.gridBlocks = p.grid;
     // buffers that are not 16-byte aligned: a default tile with element-sized accesses
@@ -342,7 +373,7 @@ bool valid_tile_params(const TileParams& t, Method method = kMethodTiles) {
     for (int x : ok) if (v == x) return true;
     return false;
   };
-  if (method == kMethodTma ? (t.stages < 2 || t.stages > kTmaMaxStages) : (t.stages != 1 && t.stages != 2)) return false;
+  if (method == kMethodTma ? (t.stages < 1 || t.stages > kTmaMaxStages) : (t.stages != 1 && t.stages != 2)) return false;
   return one_of(t.nthreads, {64, 128, 256, 512}) &&
          one_of(t.maxVecBytes, {4, 8, 16}) && one_of(t.maxVBytes, {4, 8, 16}) &&
          one_of(t.extend, {0, 1}) && one_of(t.loopOrder, {0, 1}) && one_of(t.groupIn, {1, 2, 4}) &&
@@ -455,6 +486,11 @@ cuttResult make_plan(cuttHandle* handle, int rank, const int* dim, const int* pe
       if (!build_rowcopy(p->prob, dev, c)) return CUTT_INVALID_PARAMETER;
       ok = adopt_candidate(*p, dev, c);
     }
+    else if (req.method == kMethodT2d) {
+      Candidate c;
+      if (!build_t2d(p->prob, req.params, dev, c)) return CUTT_INVALID_PARAMETER;
+      ok = adopt_candidate(*p, dev, c);
+    }
     else if (req.method == kMethodTma) {
       Candidate c;
       if (!dev.tmaLoads || !build_tma(p->prob, req.params, dev, c)) return CUTT_INVALID_PARAMETER;
@@ -493,6 +529,10 @@ cuttResult make_plan(cuttHandle* handle, int rank, const int* dim, const int* pe
         } else if (cc.method == kMethodRowCopy) {
           Candidate c;
           ok = build_rowcopy(p->prob, dev, c) && adopt_candidate(*p, dev, c);
+        } else if (cc.method == kMethodT2d) {
+          Candidate c;
+          ok = valid_tile_params(cc.params, kMethodT2d) && build_t2d(p->prob, cc.params, dev, c) &&
+               adopt_candidate(*p, dev, c);
         } else if (cc.method == kMethodTma) {
           Candidate c;
           ok = dev.tmaLoads && valid_tile_params(cc.params, kMethodTma) && build_tma(p->prob, cc.params, dev, c) &&
@@ -629,7 +669,7 @@ cuttResult make_plan(cuttHandle* handle, int rank, const int* dim, const int* pe
   if (verbose) {
     Candidate shown = p->cand;
     shown.method = p->method;
-    if (p->method != kMethodTiles && p->method != kMethodRowCopy && p->method != kMethodTma)
+    if (p->method != kMethodTiles && p->method != kMethodRowCopy && p->method != kMethodTma && p->method != kMethodT2d)
       shown.label = plain_label(*p);
     fprintf(stderr, "[cutt] plan %u (%s): %s\n", *handle, p->note.c_str(),
             canon ? describe(p->prob, shown).c_str() : "naive (rank too high after fusion)");
@@ -770,7 +810,8 @@ int cutt_c_plan_describe(unsigned int handle, char* buf, size_t len) {
   const Plan& p = *it->second;
   Candidate shown = p.cand;
   shown.method = p.method;
-  if (p.method != kMethodTiles && p.method != kMethodRowCopy && p.method != kMethodTma) shown.label = plain_label(p);
+  if (p.method != kMethodTiles && p.method != kMethodRowCopy && p.method != kMethodTma && p.method != kMethodT2d)
+    shown.label = plain_label(p);
   snprintf(buf, len, "%s", describe(p.prob, shown).c_str());
   return CUTT_SUCCESS;
 }
@@ -809,7 +850,7 @@ int cutt_c_plan_params(unsigned int* handle, int rank, const int* dim, const int
   req.params.maxVecBytes = maxVecBytes;
   req.params.maxVBytes = maxVBytes;
   if (nthreads != 64 && nthreads != 128 && nthreads != 256 && nthreads != 512) return CUTT_INVALID_PARAMETER;
-  if (method == kMethodTma ? (stages < 2 || stages > kTmaMaxStages) : (stages != 1 && stages != 2))
+  if (method == kMethodTma ? (stages < 1 || stages > kTmaMaxStages) : (stages != 1 && stages != 2))
     return CUTT_INVALID_PARAMETER;
   req.params.nthreads = nthreads;
   req.params.stages = stages;
@@ -1162,9 +1203,10 @@ int cutt_c_plan_cache_load(const char* path) {
       continue;
     // winners are tiled plans, row copies or (identity permutations) the two copy methods
     if (method != kMethodTiles && method != kMethodRowCopy && method != kMethodCopy && method != kMethodMemcpy &&
-        method != kMethodTma)
+        method != kMethodTma && method != kMethodT2d)
       continue;
-    if ((method == kMethodTiles || method == kMethodTma) && !valid_tile_params(t, (Method)method)) continue;
+    if ((method == kMethodTiles || method == kMethodTma || method == kMethodT2d) && !valid_tile_params(t, (Method)method))
+      continue;
     c.method = (Method)method;
     plan_cache().put(key, c);
     n++;

@@ -187,6 +187,37 @@ static int run_tma(const Candidate& c, const unsigned char* in, unsigned char* o
   return b.violations ? 9 : 0;
 }
 
+// Two-dimensional tile method: load units and store items are the device code; every global and
+// shared access is range- and alignment-checked.
+template <int ELT, int WIB, int WOB>
+static void run_t2d_typed(const T2dDesc& D, const unsigned char* in, unsigned char* out, unsigned char* stage) {
+  for (uint32_t tile = 0; tile < D.numTiles; tile++) {
+    T2dTile t;
+    t2d_decode(D, tile, t);
+    memset(stage, 0xEE, (size_t)D.ta * D.tb * ELT);
+    const uint32_t nUnits = t2d_load_units(D), nItems = t2d_store_items(D);
+    for (uint32_t u = 0; u < nUnits; u++) t2d_load_unit<ELT, WIB>(D, t, stage, in, u);
+    for (uint32_t it = 0; it < nItems; it++) t2d_store_item<ELT, WOB>(D, t, stage, out, it);
+  }
+}
+
+static int run_t2d(const Candidate& c, const unsigned char* in, size_t inBytes, unsigned char* out,
+                   unsigned char* outLo, unsigned char* outHi) {
+  const T2dDesc& D = c.t2d;
+  if ((uintptr_t)in % D.wiB || (uintptr_t)out % D.woB) return 7;
+  HostBounds& b = host_bounds();
+  b.gin0 = in; b.gin1 = in + inBytes; b.gout0 = outLo; b.gout1 = outHi; b.violations = 0;
+  std::vector<unsigned char> raw((size_t)D.ta * D.tb * D.elt + 256);
+  unsigned char* stage = raw.data() + (128 - ((uintptr_t)raw.data() & 127)) % 128;
+  b.s0 = stage; b.s1 = stage + (size_t)D.ta * D.tb * D.elt;
+#define T2D_CASE(E, A, B) if (D.elt == E && D.wiB == A && D.woB == B) { run_t2d_typed<E, A, B>(D, in, out, stage); return b.violations ? 9 : 0; }
+  T2D_CASE(4, 4, 4) T2D_CASE(4, 4, 8) T2D_CASE(4, 4, 16) T2D_CASE(4, 8, 4) T2D_CASE(4, 8, 8) T2D_CASE(4, 8, 16)
+  T2D_CASE(4, 16, 4) T2D_CASE(4, 16, 8) T2D_CASE(4, 16, 16)
+  T2D_CASE(8, 8, 8) T2D_CASE(8, 8, 16) T2D_CASE(8, 16, 8) T2D_CASE(8, 16, 16)
+#undef T2D_CASE
+  return 4;
+}
+
 static DeviceInfo g_dev;
 
 // Candidate list of the last problem asked for (tests run candidate 0, 1, 2, ... of one problem
@@ -234,7 +265,28 @@ int cutt_hostcheck_run(int rank, const int* dim, const int* perm, int elt, int i
   }
   if (c.method == kMethodRowCopy) return run_rowcopy(c.rc, (const unsigned char*)in, (unsigned char*)out, (size_t)P.volume * elt);
   if (c.method == kMethodTma) return run_tma(c, (const unsigned char*)in, (unsigned char*)out, (size_t)P.volume * elt);
+  if (c.method == kMethodT2d)
+    return run_t2d(c, (const unsigned char*)in, (size_t)P.volume * elt, (unsigned char*)out, (unsigned char*)out,
+                   (unsigned char*)out + (size_t)P.volume * elt);
   return dispatch_checked(c.desc, (const unsigned char*)in, (unsigned char*)out, (size_t)P.volume * elt);
+}
+
+// Two-dimensional tile method with explicit parameters (tile bytes along dimension 0, tile extent
+// along dimension p, threads, tile order, widest access in bytes).  Returns 2 when the problem is
+// outside the method's class.
+int cutt_hostcheck_run_t2d(int rank, const int* dim, const int* perm, int elt, unsigned taBytes, unsigned tbElems,
+                           int nthreads, int order, int maxVecBytes, const void* in, void* out, char* label,
+                           int labelLen) {
+  Problem P;
+  if (!problem_from_cutt(rank, dim, perm, elt, P)) return 2;
+  TileParams tp;
+  tp.tinBytes = taBytes; tp.toutBytes = tbElems * elt; tp.stages = 1; tp.nthreads = nthreads; tp.loopOrder = order;
+  tp.maxVecBytes = maxVecBytes;
+  Candidate c;
+  if (!build_t2d(P, tp, g_dev, c)) return 2;
+  if (label && labelLen > 0) snprintf(label, labelLen, "%s", describe(P, c).c_str());
+  return run_t2d(c, (const unsigned char*)in, (size_t)P.volume * elt, (unsigned char*)out, (unsigned char*)out,
+                 (unsigned char*)out + (size_t)P.volume * elt);
 }
 
 // Tensor-map transpose with explicit parameters (tile bytes along the two dimensions, stages,
@@ -284,6 +336,8 @@ int cutt_hostcheck_run_ext(int rank, const int* dim, const int* perm, int eltByt
   if (c.method == kMethodCopy || c.method == kMethodMemcpy) { memcpy(out, in, bytes); return 0; }
   if (c.method == kMethodRowCopy) return run_rowcopy(c.rc, (const unsigned char*)in, (unsigned char*)out, bytes);
   if (c.method == kMethodTma) return run_tma(c, (const unsigned char*)in, (unsigned char*)out, bytes);
+  if (c.method == kMethodT2d)
+    return run_t2d(c, (const unsigned char*)in, bytes, (unsigned char*)out, (unsigned char*)out, (unsigned char*)out + bytes);
   return dispatch_checked(c.desc, (const unsigned char*)in, (unsigned char*)out, bytes);
 }
 
@@ -384,6 +438,15 @@ int cutt_hostcheck_run_chunked(int rank, const int* dim, const int* perm, int el
     }
     if (c.method == kMethodCopy || c.method == kMethodMemcpy) {
       memcpy(pout, pin, (size_t)P.volume * elt);
+    } else if (c.method == kMethodT2d) {
+      if ((uintptr_t)pin % c.t2d.wiB || (uintptr_t)pout % c.t2d.woB) {   // as the library: element-sized accesses
+        TileParams tp = c.params;
+        tp.maxVecBytes = elt;
+        Candidate f;
+        if (!build_t2d(P, tp, g_dev, f)) return 6;
+        c = f;
+      }
+      if (run_t2d(c, pin, (size_t)P.volume * elt, pout, (unsigned char*)out, (unsigned char*)out + total)) return 9;
     } else if (c.method == kMethodTma) {
       if ((uintptr_t)pin % 16 || (uintptr_t)pout % 16) return 7;   // (the library would take its fallback tile)
       if (run_tma(c, pin, pout, (size_t)P.volume * elt, (unsigned char*)out, (unsigned char*)out + total)) return 9;

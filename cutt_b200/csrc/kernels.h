@@ -49,6 +49,11 @@ cudaError_t launch_tma(const TmaDesc& D, const TmaMapRecipe& R, int gridBlocks, 
                        cudaStream_t stream);
 cudaError_t launch_rowcopy(const RowCopyDesc& d, int numSM, const void* in, void* out, cudaStream_t stream);
 
+// Two-dimensional tile transpose with swizzled shared memory (tile2d.cu, tile2d.h).
+int t2d_blocks_per_sm(const T2dDesc& D);
+bool t2d_pointers_aligned(const T2dDesc& D, const void* in, const void* out);
+cudaError_t launch_t2d(const T2dDesc& D, const void* in, void* out, cudaStream_t stream);
+
 // Permutation of 1- or 2-byte elements, one tile per block (small_elt.cu).
 struct SmallDesc;
 cudaError_t launch_small(const SmallDesc& d, const void* in, void* out, cudaStream_t stream);

@@ -759,7 +759,7 @@ bool build_tma(const Problem& P, const TileParams& tp, const DeviceInfo& dev, Ca
   const uint32_t ta = tp.tinBytes / elt, tb = tp.toutBytes / elt;
   if (ta == 0 || (ta * elt) % 128 != 0 || ta * elt > 512) return false;
   if (tb == 0 || tb % (8 * VE) != 0 || tb > 256) return false;
-  if (tp.stages < 2 || tp.stages > kTmaMaxStages) return false;
+  if (tp.stages < 1 || tp.stages > kTmaMaxStages) return false;
   if (tp.nthreads != 128 && tp.nthreads != 256) return false;
   // tiles far larger than the tensor along either dimension would be mostly padding
   if (P.d[0] * elt < 64 || P.d[p] < (int64_t)tb / 4) return false;
@@ -812,11 +812,11 @@ bool build_tma(const Problem& P, const TileParams& tp, const DeviceInfo& dev, Ca
   for (uint32_t k = D.nOuter; k < 3; k++) { D.nO[k] = 1; D.divO[k] = make_fastdiv(1); D.osO[k] = 0; }
   D.numTiles = (uint32_t)ntiles;
   out.smemBytes = (int)(D.stages * ta * tb * elt + 1024);
-  if (out.smemBytes > dev.maxSmemPerBlock) return false;
+  if (out.smemBytes > dev.maxSmemPerBlock - 1024) return false;   // (room for the kernel's static shared memory)
   int bps = std::min(dev.smemPerSM / (out.smemBytes + 1024), dev.maxThreadsPerSM / tp.nthreads);
   bps = std::max(1, std::min(bps, 16));
   out.blocksPerSM = bps;
-  out.gridBlocks = (int)std::min<int64_t>(ntiles, (int64_t)dev.numSM * bps);
+  out.gridBlocks = tp.stages == 1 ? (int)ntiles : (int)std::min<int64_t>(ntiles, (int64_t)dev.numSM * bps);
   // Estimate: the copy rate, reduced by the share of each tile that lies outside the tensor and,
   // for tensors too small to give every SM a few tiles, by the idle SMs.  Measured on B200: within
   // its class this kernel runs at or above the rate of the best cp.async tile plan.
@@ -826,6 +826,86 @@ bool build_tma(const Problem& P, const TileParams& tp, const DeviceInfo& dev, Ca
   out.cost = 2.0 * (double)P.volume * elt / (dev.hbmGBs * 1e9 * eff) + 5e-6;
   char buf[160];
   snprintf(buf, sizeof buf, "tma t=%ux%u boxes=%u st=%u lo=%u nt=%u smem=%d tiles=%u", ta, tb, D.nboxes, D.stages,
+           D.order, D.nthreads, out.smemBytes, D.numTiles);
+  out.label = buf;
+  return true;
+}
+
+bool build_t2d(const Problem& P, const TileParams& tp, const DeviceInfo& dev, Candidate& out) {
+  const int r = P.rank;
+  const int elt = P.elt;
+  if (elt != 4 && elt != 8) return false;
+  if (r < 2 || r > kT2dMaxOuter + 2 || P.peerDim >= 0 || P.identity) return false;
+  if (P.is[0] != 1) return false;
+  int p = 0;
+  for (int j = 1; j < r; j++) if (P.os[j] < P.os[p]) p = j;
+  if (p == 0 || P.os[p] != 1) return false;
+  for (int j = 0; j < r; j++) if (P.d[j] >= (1ll << 31)) return false;
+  // widest accesses the strides allow (the pointers are checked when the plan is executed)
+  auto width = [&](bool input) -> uint32_t {
+    for (int64_t w = std::min(16, tp.maxVecBytes) / elt; w > 1; w /= 2) {
+      bool ok = (input ? P.inBase : P.outBase) % w == 0 && P.d[input ? 0 : p] % w == 0;
+      for (int j = 0; j < r && ok; j++) {
+        if (input ? j == 0 : j == p) continue;
+        if ((input ? P.is[j] : P.os[j]) % w != 0) ok = false;
+      }
+      if (ok) return (uint32_t)(w * elt);
+    }
+    return (uint32_t)elt;
+  };
+  const uint32_t ta = tp.tinBytes / elt, tb = tp.toutBytes / elt;
+  if ((ta * elt != 128 && ta * elt != 256) || (tb != 32 && tb != 64)) return false;
+  if (tp.nthreads != 128 && tp.nthreads != 256) return false;
+  if (P.d[0] * elt < 64 || P.d[p] < 16) return false;   // tiles would be mostly padding
+  out = Candidate();
+  out.method = kMethodT2d;
+  out.params = tp;
+  T2dDesc& D = out.t2d;
+  memset(&D, 0, sizeof D);
+  D.elt = elt;
+  D.ta = ta;
+  D.tb = tb;
+  D.tbShift = ilog2_exact(tb);
+  D.nboxes = ta * elt / 128;
+  D.nthreads = tp.nthreads;
+  D.wiB = width(true);
+  D.woB = width(false);
+  D.order = tp.loopOrder ? 1 : 0;
+  D.d0 = (uint32_t)P.d[0];
+  D.dp = (uint32_t)P.d[p];
+  D.nA = (uint32_t)ceil_div(P.d[0], ta);
+  D.nB = (uint32_t)ceil_div(P.d[p], tb);
+  D.divA = make_fastdiv(D.nA);
+  D.divB = make_fastdiv(D.nB);
+  D.isP = P.is[p];
+  D.os0 = P.os[0];
+  D.inBase = P.inBase;
+  D.outBase = P.outBase;
+  int64_t ntiles = (int64_t)D.nA * D.nB;
+  for (int j = 1; j < r; j++) {
+    if (j == p) continue;
+    const uint32_t k = D.nOuter++;
+    D.nO[k] = (uint32_t)P.d[j];
+    D.divO[k] = make_fastdiv(D.nO[k]);
+    D.isO[k] = P.is[j];
+    D.osO[k] = P.os[j];
+    ntiles *= P.d[j];
+    if (ntiles >= (1ll << 31)) return false;
+  }
+  D.numTiles = (uint32_t)ntiles;
+  out.smemBytes = (int)(ta * tb * elt);
+  int bps = std::min(dev.smemPerSM / (out.smemBytes + 1024), dev.maxThreadsPerSM / tp.nthreads);
+  out.blocksPerSM = std::max(1, std::min(bps, 32));
+  out.gridBlocks = (int)ntiles;
+  // Estimate: the copy rate, reduced by the share of each tile that lies outside the tensor, by
+  // narrow accesses, and for tensors too small to give every SM a few tiles by the idle SMs.
+  const double util = ((double)P.d[0] / ((double)D.nA * ta)) * ((double)P.d[p] / ((double)D.nB * tb));
+  const double fill = std::min(1.0, (double)ntiles / ((double)dev.numSM * 4.0));
+  const double narrow = (D.wiB == 16 ? 1.0 : (D.wiB == 8 ? 0.985 : 0.96)) * (D.woB == 16 ? 1.0 : (D.woB == 8 ? 0.985 : 0.95));
+  const double eff = 0.955 * util * narrow * (0.25 + 0.75 * fill);
+  out.cost = 2.0 * (double)P.volume * elt / (dev.hbmGBs * 1e9 * eff) + 5e-6;
+  char buf[160];
+  snprintf(buf, sizeof buf, "t2d t=%ux%u in/w%u out/w%u lo=%u nt=%u smem=%d tiles=%u", ta, tb, D.wiB / elt, D.woB / elt,
            D.order, D.nthreads, out.smemBytes, D.numTiles);
   out.label = buf;
   return true;
@@ -922,18 +1002,22 @@ std::vector<Candidate> enumerate_candidates(const Problem& P, const DeviceInfo& 
     Candidate rc;
     if (build_rowcopy(P, dev, rc)) res.push_back(rc);
   }
-  // tensor-map transposes (legal strides only): a few tile shapes, both tile orders
-  if (dev.tmaLoads) {
-    const uint32_t ta[] = {128, 256}, tbB[] = {128, 256};
+  // two-dimensional tiles with swizzled shared memory, loaded by cp.async (any alignment) or by the
+  // copy engine through a tensor map (strides that are multiples of 16 bytes only): one tile per
+  // block, a few tile shapes, both tile orders
+  {
+    const uint32_t ta[] = {128, 256}, tbE[] = {32, 64};
     for (uint32_t a : ta)
-      for (uint32_t b : tbB)
+      for (uint32_t b : tbE)
         for (int lo = 0; lo < 2; lo++)
           for (int nt = 128; nt <= 256; nt *= 2) {
+            if (nt == 256 && a * b <= 128 * 32) continue;   // 4 KB tiles: 128 threads are enough
             TileParams tp;
-            tp.tinBytes = a; tp.toutBytes = b; tp.loopOrder = lo; tp.nthreads = nt;
-            tp.stages = (a * b / (uint32_t)P.elt <= 8192) ? 4 : 3;
+            tp.tinBytes = a; tp.toutBytes = b * (uint32_t)P.elt; tp.loopOrder = lo; tp.nthreads = nt;
+            tp.stages = 1;
             Candidate c;
-            if (build_tma(P, tp, dev, c)) res.push_back(c);
+            if (build_t2d(P, tp, dev, c)) res.push_back(c);
+            if (dev.tmaLoads && build_tma(P, tp, dev, c)) res.push_back(c);
           }
   }
   std::stable_sort(res.begin(), res.end(), [](const Candidate& a, const Candidate& b) { return a.cost < b.cost; });
@@ -952,7 +1036,9 @@ std::string describe(const Problem& P, const Candidate& c) {
            "{\"method\": %d, \"label\": \"%s\", \"fused_dims\": [%s], \"istride\": [%s], \"ostride\": [%s], "
            "\"elt\": %d, \"num_tiles\": %u, \"grid\": %d, \"smem\": %d, \"model_us\": %.2f, \"feat\": [",
            (int)c.method, c.label.c_str(), dims.c_str(), iss.c_str(), oss.c_str(), P.elt,
-           c.method == kMethodTiles ? c.desc.numTiles : (c.method == kMethodTma ? c.tma.numTiles : 0u), c.gridBlocks,
+           c.method == kMethodTiles ? c.desc.numTiles
+                                    : (c.method == kMethodTma ? c.tma.numTiles : (c.method == kMethodT2d ? c.t2d.numTiles : 0u)),
+           c.gridBlocks,
            c.smemBytes, c.cost * 1e6);
   std::string res = buf;
   for (int i = 0; i < kNumFeatures; i++) {

@@ -12,6 +12,7 @@
 #include "permute_desc.h"
 #include "rowcopy_impl.h"
 #include "tma_transpose.h"
+#include "tile2d.h"
 
 namespace cuttb {
 
@@ -81,6 +82,7 @@ enum Method : int {
   kMethodRowCopy = 4,  // strided copy of contiguous rows with register shifting (rowcopy_impl.h)
   kMethodSmall = 5,    // 1- and 2-byte elements moved one by one (small_elt_impl.h)
   kMethodTma = 6,      // tensor-map box loads into swizzled shared memory (tma_transpose.h)
+  kMethodT2d = 7,      // two-dimensional tiles, cp.async loads into swizzled shared memory (tile2d.h)
 };
 
 struct TileParams {
@@ -117,6 +119,7 @@ struct Candidate {
   RowCopyDesc rc;              // kMethodRowCopy only
   TmaDesc tma;                 // kMethodTma only
   TmaMapRecipe tmaMap;         // kMethodTma only
+  T2dDesc t2d;                 // kMethodT2d only
   int smemBytes = 0;
   int blocksPerSM = 1;
   int gridBlocks = 0;
@@ -137,6 +140,12 @@ bool build_tile(const Problem& P, const TileParams& tp, const DeviceInfo& dev, C
 // tinBytes = bytes along dimension 0, toutBytes = bytes along dimension p, stages, nthreads,
 // loopOrder = which of the two varies fastest in the tile index.
 bool build_tma(const Problem& P, const TileParams& tp, const DeviceInfo& dev, Candidate& out);
+
+// Two-dimensional tile candidate (tile2d.h): tinBytes = tile bytes along dimension 0 (128 or 256),
+// toutBytes = tile extent along the output's fastest dimension times the element size (32 or 64
+// elements), nthreads 128 or 256, loopOrder = which of the two runs fastest in the tile order,
+// maxVecBytes caps the access width on both sides.  False outside the class.
+bool build_t2d(const Problem& P, const TileParams& tp, const DeviceInfo& dev, Candidate& out);
 
 // Row-copy candidate for problems whose fastest dimension is kept; false if not applicable.
 bool build_rowcopy(const Problem& P, const DeviceInfo& dev, Candidate& out);

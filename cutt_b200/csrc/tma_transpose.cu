@@ -13,6 +13,8 @@
 // cudaGetDriverEntryPoint so that the library keeps linking against the CUDA runtime alone) and
 // travels as a __grid_constant__ kernel parameter.
 #include <cuda.h>
+#include <cstdio>
+#include <cstdlib>
 #include <mutex>
 #include <map>
 #include "kernels.h"
@@ -169,8 +171,16 @@ static cudaError_t tma_ensure_smem(const void* k) {
   int maxOptin = 0;
   e = cudaDeviceGetAttribute(&maxOptin, cudaDevAttrMaxSharedMemoryPerBlockOptin, dev);
   if (e != cudaSuccess) return e;
-  e = cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, maxOptin);
+  // the kernel also has a little static shared memory (barriers, abort flag): the dynamic part
+  // may take what is left of the per-block limit
+  cudaFuncAttributes fa;
+  e = cudaFuncGetAttributes(&fa, k);
   if (e != cudaSuccess) return e;
+  e = cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, maxOptin - (int)fa.sharedSizeBytes);
+  if (e != cudaSuccess) {
+    if (getenv("CUTT_VERBOSE")) fprintf(stderr, "[cutt] tma shared-memory attribute: %s\n", cudaGetErrorString(e));
+    return e;
+  }
   g_tmaAttr[key] = true;
   return cudaSuccess;
 }
@@ -179,10 +189,13 @@ int tma_blocks_per_sm(const TmaDesc& D) {
   const void* k = tma_kernel(D);
   if (!tma_supported() || tma_ensure_smem(k) != cudaSuccess) return -1;
   int nb = 0;
-  if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&nb, k, (int)D.nthreads, tma_smem_bytes(D)) != cudaSuccess) {
+  const cudaError_t e = cudaOccupancyMaxActiveBlocksPerMultiprocessor(&nb, k, (int)D.nthreads, tma_smem_bytes(D));
+  if (e != cudaSuccess) {
+    if (getenv("CUTT_VERBOSE")) fprintf(stderr, "[cutt] tma occupancy query failed: %s\n", cudaGetErrorString(e));
     cudaGetLastError();
     return -1;
   }
+  if (nb <= 0 && getenv("CUTT_VERBOSE")) fprintf(stderr, "[cutt] tma kernel does not fit: %zu bytes of shared memory\n", tma_smem_bytes(D));
   return nb;
 }
 
@@ -206,6 +219,12 @@ static bool tma_encode(const TmaDesc& D, const TmaMapRecipe& R, const void* in, 
                          const_cast<void*>(in), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
                          CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
                          CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS && getenv("CUTT_VERBOSE"))
+    fprintf(stderr, "[cutt] cuTensorMapEncodeTiled failed with code %d: dims %llu %llu %llu %llu %llu strides %llu %llu %llu %llu "
+            "box %u %u %u %u %u\n", (int)r, (unsigned long long)dims[0], (unsigned long long)dims[1],
+            (unsigned long long)dims[2], (unsigned long long)dims[3], (unsigned long long)dims[4],
+            (unsigned long long)strides[0], (unsigned long long)strides[1], (unsigned long long)strides[2],
+            (unsigned long long)strides[3], box[0], box[1], box[2], box[3], box[4]);
   return r == CUDA_SUCCESS;
 }
 

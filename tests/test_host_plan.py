@@ -309,3 +309,63 @@ def test_tensor_map_candidates_are_enumerated_for_legal_strides_only(hc):
     assert any(l.startswith("tma ") for l in labels([128, 96], [1, 0], 4))
     assert any(l.startswith("tma ") for l in labels([130, 98], [1, 0], 8))
     assert not any(l.startswith("tma ") for l in labels([130, 98], [1, 0], 4))
+
+
+def _t2d(hc):
+    hc.cutt_hostcheck_run_t2d.argtypes = [ctypes.c_int, ctypes.POINTER(ctypes.c_int), ctypes.POINTER(ctypes.c_int),
+                                          ctypes.c_int, ctypes.c_uint, ctypes.c_uint, ctypes.c_int, ctypes.c_int,
+                                          ctypes.c_int, ctypes.c_void_p, ctypes.c_void_p, ctypes.c_char_p, ctypes.c_int]
+    return hc.cutt_hostcheck_run_t2d
+
+
+@pytest.mark.parametrize("dims,perm", [
+    ([64, 64], [1, 0]), ([129, 130], [1, 0]), ([131, 67], [1, 0]), ([66, 202], [1, 0]), ([132, 200], [1, 0]),
+    ([36, 8, 44], [2, 1, 0]), ([41, 6, 53], [1, 2, 0]), ([72, 3, 5, 57], [3, 0, 2, 1]), ([25, 4, 3, 2, 40], [4, 2, 0, 3, 1]),
+    ([30, 2, 3, 2, 2, 3, 2, 34], [7, 6, 5, 4, 3, 2, 1, 0]), ([16, 10, 36], [2, 0, 1]), ([250, 3, 18], [2, 1, 0]),
+])
+def test_two_dimensional_tiles(hc, oracle_mod, dims, perm):
+    """The swizzled two-dimensional tile method on the host: every access width the strides allow and
+    all narrower ones, every tile shape, both tile orders, both element sizes; odd extents give edge
+    tiles in both dimensions and rows that start on 4- and 8-byte boundaries only."""
+    run = _t2d(hc)
+    widths = set()
+    for elt in (4, 8):
+        a = raw_bits(volume(dims), elt, 43)
+        want = oracle_mod.transpose_blocked(dims, perm, a)
+        for ta in (128, 256):
+            for tb in (32, 64):
+                for order, nt in ((0, 128), (1, 256)):
+                    for maxvec in (16, 8, 4):
+                        if maxvec < elt:
+                            continue
+                        out = np.full_like(a, 0xAB)
+                        lab = ctypes.create_string_buffer(2048)
+                        rc = run(len(dims), _iarr(dims), _iarr(perm), elt, ta, tb, nt, order, maxvec, a.ctypes.data,
+                                 out.ctypes.data, lab, 2048)
+                        assert rc == 0, (rc, dims, perm, elt, ta, tb, maxvec)
+                        label = json.loads(lab.value.decode())["label"]
+                        assert np.array_equal(out, want), (dims, perm, elt, label)
+                        widths.add(label.split(" lo=")[0].split(" ", 2)[2])
+    assert widths
+
+
+def test_two_dimensional_tiles_widths_and_rejections(hc):
+    run = _t2d(hc)
+    a = np.zeros(1 << 16, dtype=np.uint64)
+    out = np.zeros_like(a)
+
+    def label(dims, perm, elt, maxvec=16):
+        lab = ctypes.create_string_buffer(2048)
+        rc = run(len(dims), _iarr(dims), _iarr(perm), elt, 128, 32, 128, 0, maxvec, a.ctypes.data, out.ctypes.data, lab, 2048)
+        return rc, (json.loads(lab.value.decode())["label"] if rc == 0 else "")
+
+    assert "in/w4 out/w4" in label([64, 64], [1, 0], 4)[1]
+    assert "in/w2 out/w4" in label([66, 64], [1, 0], 4)[1]       # input rows on 8-byte boundaries
+    assert "in/w4 out/w1" in label([64, 67], [1, 0], 4)[1]       # output rows on 4-byte boundaries
+    assert "in/w1 out/w2" in label([67, 66], [1, 0], 4)[1]
+    assert "in/w2 out/w1" in label([66, 67], [1, 0], 8)[1]
+    assert "in/w1 out/w1" in label([64, 64], [1, 0], 4, maxvec=4)[1]
+    assert label([64, 8, 64], [0, 2, 1], 4)[0] == 2              # fastest dimension kept
+    assert label([64, 64], [0, 1], 4)[0] == 2                    # identity
+    assert label([8, 64], [1, 0], 4)[0] == 2                     # 32-byte rows: mostly padding
+    assert label([64, 8], [1, 0], 4)[0] == 2
