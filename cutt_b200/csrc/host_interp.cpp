@@ -375,10 +375,16 @@ int cutt_hostcheck_run_sharded(int rank, const int* dim, const int* perm, int el
   const Candidate& c = cands[index];
   if (label && labelLen > 0) snprintf(label, labelLen, "%s", describe(P, c).c_str());
   const size_t bytes = (size_t)info.localVolume * elt;
-  if (c.method != kMethodTiles) {
+  if (c.method != kMethodTiles) {   // slab mode only: an ordinary local problem
     if (info.mode != 0) return -4;
-    memcpy(outs[me], in, bytes);
-    return 0;
+    unsigned char* o = (unsigned char*)outs[me];
+    int rc = 0;
+    if (c.method == kMethodCopy || c.method == kMethodMemcpy) memcpy(o, in, bytes);
+    else if (c.method == kMethodRowCopy) rc = run_rowcopy(c.rc, (const unsigned char*)in, o, bytes);
+    else if (c.method == kMethodTma) rc = run_tma(c, (const unsigned char*)in, o, bytes);
+    else if (c.method == kMethodT2d) rc = run_t2d(c, (const unsigned char*)in, bytes, o, o, o + bytes);
+    else rc = 4;
+    return rc ? -5 : 0;
   }
   HostBounds& b = host_bounds();
   b.gin0 = (const unsigned char*)in; b.gin1 = b.gin0 + bytes; b.violations = 0;
