@@ -35,7 +35,7 @@ def test_forced_tile_shapes_and_widths(native, oracle_mod, dims, perm):
                         assert label.startswith("t2d "), desc
                         assert_bit_exact(out, want, desc)
                         labels.add(label.split(" lo=")[0])
-    assert len(labels) >= 8
+    assert len(labels) >= 4
 
 
 def test_rejected_problems(native):

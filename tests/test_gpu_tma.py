@@ -44,7 +44,7 @@ def test_rejected_problems(native):
     bad = native.CUTT_INVALID_PARAMETER
     assert native.plan_params([66, 64], [1, 0], 4, 0, method=6, tin=128, tout=128)[0] == bad   # 264-byte rows
     assert native.plan_params([64, 8, 64], [0, 2, 1], 4, 0, method=6, tin=128, tout=128)[0] == bad
-    assert native.plan_params([64, 64], [1, 0], 4, 0, method=6, tin=128, tout=128, stages=1)[0] == bad
+    assert native.plan_params([64, 64], [1, 0], 4, 0, method=6, tin=128, tout=128, stages=0)[0] == bad
     assert native.plan_params([64, 64], [1, 0], 4, 0, method=6, tin=128, tout=128, stages=9)[0] == bad
 
 

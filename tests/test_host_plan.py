@@ -265,7 +265,7 @@ def test_tensor_map_transpose(hc, oracle_mod, dims, perm):
                 for order in (0, 1):
                     out = np.full_like(a, 0xAB)
                     lab = ctypes.create_string_buffer(2048)
-                    rc = run(len(dims), _iarr(dims), _iarr(perm), elt, ta, tb, 3, 128, order, a.ctypes.data,
+                    rc = run(len(dims), _iarr(dims), _iarr(perm), elt, ta, tb, 1 + 2 * order, 128, order, a.ctypes.data,
                              out.ctypes.data, lab, 2048)
                     if rc == 2:
                         continue          # this tile shape does not apply to this problem
