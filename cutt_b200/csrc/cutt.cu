@@ -286,9 +286,12 @@ bool adopt_candidate(Plan& p, const DeviceInfo& dev, const Candidate& c) {
     p.grid = (int)c.t2d.numTiles;
     p.cand.gridBlocks = p.grid;
     p.haveFallback = false;
-    if (c.t2d.wiB > (uint32_t)p.elt || c.t2d.woB > (uint32_t)p.elt) {
+    if (c.t2d.loadMode != 1 || c.t2d.storeMode != 1) {
+      // buffers that are not aligned for this plan's access modes: the same tile in the modes that
+      // take any element-aligned address
       TileParams tp = c.params;
-      tp.maxVecBytes = p.elt;
+      tp.maxVecBytes = 16;
+      tp.extend = 1;
       Candidate f;
       if (build_t2d(p.prob, tp, dev, f) && t2d_blocks_per_sm(f.t2d) > 0) {
         p.fallback = f;

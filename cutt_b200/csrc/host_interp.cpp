@@ -189,31 +189,43 @@ static int run_tma(const Candidate& c, const unsigned char* in, unsigned char* o
 
 // Two-dimensional tile method: load units and store items are the device code; every global and
 // shared access is range- and alignment-checked.
-template <int ELT, int WIB, int WOB>
+template <int ELT, int LOAD, int STORE>
 static void run_t2d_typed(const T2dDesc& D, const unsigned char* in, unsigned char* out, unsigned char* stage) {
   for (uint32_t tile = 0; tile < D.numTiles; tile++) {
     T2dTile t;
     t2d_decode(D, tile, t);
-    memset(stage, 0xEE, (size_t)D.ta * D.tb * ELT);
+    memset(stage, 0xEE, (size_t)D.nboxes * D.rowsAlloc * 128);
     const uint32_t nUnits = t2d_load_units(D), nItems = t2d_store_items(D);
-    for (uint32_t u = 0; u < nUnits; u++) t2d_load_unit<ELT, WIB>(D, t, stage, in, u);
-    for (uint32_t it = 0; it < nItems; it++) t2d_store_item<ELT, WOB>(D, t, stage, out, it);
+    for (uint32_t u = 0; u < nUnits; u++) {
+      if (LOAD == 1) t2d_load_shift<ELT>(D, t, stage, in, u);
+      else t2d_load_unit<ELT, (LOAD == 1 ? 16 : LOAD)>(D, t, stage, in, u);
+    }
+    for (uint32_t it = 0; it < nItems; it++) {
+      if (STORE == 1) t2d_store_shear<ELT>(D, t, stage, out, it);
+      else t2d_store_item<ELT, (STORE == 1 ? 16 : STORE)>(D, t, stage, out, it);
+    }
   }
 }
 
 static int run_t2d(const Candidate& c, const unsigned char* in, size_t inBytes, unsigned char* out,
                    unsigned char* outLo, unsigned char* outHi) {
-  const T2dDesc& D = c.t2d;
-  if ((uintptr_t)in % D.wiB || (uintptr_t)out % D.woB) return 7;
+  T2dDesc D = c.t2d;
+  const uintptr_t ai = D.loadMode == 1 ? D.elt : D.loadMode, ao = D.storeMode == 1 ? D.elt : D.storeMode;
+  if ((uintptr_t)in % ai || (uintptr_t)out % ao) return 7;
+  D.inMis = (uint32_t)(((uintptr_t)in / D.elt) % (16 / D.elt));     // as the launcher does
+  D.outMis = (uint32_t)(((uintptr_t)out / D.elt) % (16 / D.elt));
   HostBounds& b = host_bounds();
   b.gin0 = in; b.gin1 = in + inBytes; b.gout0 = outLo; b.gout1 = outHi; b.violations = 0;
-  std::vector<unsigned char> raw((size_t)D.ta * D.tb * D.elt + 256);
+  const size_t smem = (size_t)D.nboxes * D.rowsAlloc * 128;
+  std::vector<unsigned char> raw(smem + 256);
   unsigned char* stage = raw.data() + (128 - ((uintptr_t)raw.data() & 127)) % 128;
-  b.s0 = stage; b.s1 = stage + (size_t)D.ta * D.tb * D.elt;
-#define T2D_CASE(E, A, B) if (D.elt == E && D.wiB == A && D.woB == B) { run_t2d_typed<E, A, B>(D, in, out, stage); return b.violations ? 9 : 0; }
-  T2D_CASE(4, 4, 4) T2D_CASE(4, 4, 8) T2D_CASE(4, 4, 16) T2D_CASE(4, 8, 4) T2D_CASE(4, 8, 8) T2D_CASE(4, 8, 16)
-  T2D_CASE(4, 16, 4) T2D_CASE(4, 16, 8) T2D_CASE(4, 16, 16)
-  T2D_CASE(8, 8, 8) T2D_CASE(8, 8, 16) T2D_CASE(8, 16, 8) T2D_CASE(8, 16, 16)
+  b.s0 = stage; b.s1 = stage + smem;
+#define T2D_CASE(E, A, B) if (D.elt == E && D.loadMode == A && D.storeMode == B) { run_t2d_typed<E, A, B>(D, in, out, stage); return b.violations ? 9 : 0; }
+#define T2D_ROW(E, A) T2D_CASE(E, A, 16) T2D_CASE(E, A, 1) T2D_CASE(E, A, 8)
+  T2D_ROW(4, 16) T2D_ROW(4, 1) T2D_ROW(4, 8) T2D_ROW(4, 4)
+  T2D_CASE(4, 16, 4) T2D_CASE(4, 1, 4) T2D_CASE(4, 8, 4) T2D_CASE(4, 4, 4)
+  T2D_ROW(8, 16) T2D_ROW(8, 1) T2D_ROW(8, 8)
+#undef T2D_ROW
 #undef T2D_CASE
   return 4;
 }
@@ -275,13 +287,14 @@ int cutt_hostcheck_run(int rank, const int* dim, const int* perm, int elt, int i
 // along dimension p, threads, tile order, widest access in bytes).  Returns 2 when the problem is
 // outside the method's class.
 int cutt_hostcheck_run_t2d(int rank, const int* dim, const int* perm, int elt, unsigned taBytes, unsigned tbElems,
-                           int nthreads, int order, int maxVecBytes, const void* in, void* out, char* label,
-                           int labelLen) {
+                           int nthreads, int order, int maxVecBytes, int forceShift, const void* in, void* out,
+                           char* label, int labelLen) {
   Problem P;
   if (!problem_from_cutt(rank, dim, perm, elt, P)) return 2;
   TileParams tp;
   tp.tinBytes = taBytes; tp.toutBytes = tbElems * elt; tp.stages = 1; tp.nthreads = nthreads; tp.loopOrder = order;
   tp.maxVecBytes = maxVecBytes;
+  tp.extend = forceShift;
   Candidate c;
   if (!build_t2d(P, tp, g_dev, c)) return 2;
   if (label && labelLen > 0) snprintf(label, labelLen, "%s", describe(P, c).c_str());
@@ -445,9 +458,11 @@ int cutt_hostcheck_run_chunked(int rank, const int* dim, const int* perm, int el
     if (c.method == kMethodCopy || c.method == kMethodMemcpy) {
       memcpy(pout, pin, (size_t)P.volume * elt);
     } else if (c.method == kMethodT2d) {
-      if ((uintptr_t)pin % c.t2d.wiB || (uintptr_t)pout % c.t2d.woB) {   // as the library: element-sized accesses
+      const uintptr_t ai = c.t2d.loadMode == 1 ? elt : c.t2d.loadMode, ao = c.t2d.storeMode == 1 ? elt : c.t2d.storeMode;
+      if ((uintptr_t)pin % ai || (uintptr_t)pout % ao) {   // as the library: the modes that take any address
         TileParams tp = c.params;
-        tp.maxVecBytes = elt;
+        tp.maxVecBytes = 16;
+        tp.extend = 1;
         Candidate f;
         if (!build_t2d(P, tp, g_dev, f)) return 6;
         c = f;

@@ -865,11 +865,20 @@ bool build_t2d(const Problem& P, const TileParams& tp, const DeviceInfo& dev, Ca
   D.elt = elt;
   D.ta = ta;
   D.tb = tb;
-  D.tbShift = ilog2_exact(tb);
   D.nboxes = ta * elt / 128;
   D.nthreads = tp.nthreads;
-  D.wiB = width(true);
-  D.woB = width(false);
+  // 16-byte accesses always: directly when the rows are aligned, else through the shift / shear
+  // modes.  A cap below 16 bytes (tests, comparisons) selects the plain narrow modes; extend = 1
+  // forces shift / shear even for aligned rows (plans that must accept any buffer address).
+  D.loadMode = width(true);
+  D.storeMode = width(false);
+  if (tp.maxVecBytes >= 16 && (D.loadMode < 16 || tp.extend)) D.loadMode = 1;
+  if (tp.maxVecBytes >= 16 && (D.storeMode < 16 || tp.extend)) D.storeMode = 1;
+  D.padTop = D.storeMode == 1 ? kT2dPadTop : 0;
+  D.rowsLoad = tb + (D.storeMode == 1 ? 16 / elt - 1 : 0);
+  D.rowsAlloc = D.storeMode == 1 ? tb + kT2dPadTop + kT2dPadBottom : tb;
+  D.divRows = make_fastdiv(D.rowsLoad);
+  D.inElems = P.inElems;
   D.order = tp.loopOrder ? 1 : 0;
   D.d0 = (uint32_t)P.d[0];
   D.dp = (uint32_t)P.d[p];
@@ -893,7 +902,7 @@ bool build_t2d(const Problem& P, const TileParams& tp, const DeviceInfo& dev, Ca
     if (ntiles >= (1ll << 31)) return false;
   }
   D.numTiles = (uint32_t)ntiles;
-  out.smemBytes = (int)(ta * tb * elt);
+  out.smemBytes = (int)(D.nboxes * D.rowsAlloc * 128);
   int bps = std::min(dev.smemPerSM / (out.smemBytes + 1024), dev.maxThreadsPerSM / tp.nthreads);
   out.blocksPerSM = std::max(1, std::min(bps, 32));
   out.gridBlocks = (int)ntiles;
@@ -901,12 +910,16 @@ bool build_t2d(const Problem& P, const TileParams& tp, const DeviceInfo& dev, Ca
   // narrow accesses, and for tensors too small to give every SM a few tiles by the idle SMs.
   const double util = ((double)P.d[0] / ((double)D.nA * ta)) * ((double)P.d[p] / ((double)D.nB * tb));
   const double fill = std::min(1.0, (double)ntiles / ((double)dev.numSM * 4.0));
-  const double narrow = (D.wiB == 16 ? 1.0 : (D.wiB == 8 ? 0.985 : 0.96)) * (D.woB == 16 ? 1.0 : (D.woB == 8 ? 0.985 : 0.95));
+  auto side = [](uint32_t mode) { return mode == 16 ? 1.0 : (mode == 1 ? 0.98 : (mode == 8 ? 0.95 : 0.7)); };
+  const double narrow = side(D.loadMode) * side(D.storeMode);
   const double eff = 0.955 * util * narrow * (0.25 + 0.75 * fill);
   out.cost = 2.0 * (double)P.volume * elt / (dev.hbmGBs * 1e9 * eff) + 5e-6;
   char buf[160];
-  snprintf(buf, sizeof buf, "t2d t=%ux%u in/w%u out/w%u lo=%u nt=%u smem=%d tiles=%u", ta, tb, D.wiB / elt, D.woB / elt,
-           D.order, D.nthreads, out.smemBytes, D.numTiles);
+  char li[16], lo[16];
+  if (D.loadMode == 1) snprintf(li, sizeof li, "shift"); else snprintf(li, sizeof li, "w%u", D.loadMode / elt);
+  if (D.storeMode == 1) snprintf(lo, sizeof lo, "shear"); else snprintf(lo, sizeof lo, "w%u", D.storeMode / elt);
+  snprintf(buf, sizeof buf, "t2d t=%ux%u in/%s out/%s lo=%u nt=%u smem=%d tiles=%u", ta, tb, li, lo, D.order, D.nthreads,
+           out.smemBytes, D.numTiles);
   out.label = buf;
   return true;
 }

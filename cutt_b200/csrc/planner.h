@@ -144,7 +144,8 @@ bool build_tma(const Problem& P, const TileParams& tp, const DeviceInfo& dev, Ca
 // Two-dimensional tile candidate (tile2d.h): tinBytes = tile bytes along dimension 0 (128 or 256),
 // toutBytes = tile extent along the output's fastest dimension times the element size (32 or 64
 // elements), nthreads 128 or 256, loopOrder = which of the two runs fastest in the tile order,
-// maxVecBytes caps the access width on both sides.  False outside the class.
+// maxVecBytes < 16 selects the plain narrow access modes, extend = 1 forces the shift / shear modes
+// (any buffer alignment).  False outside the class.
 bool build_t2d(const Problem& P, const TileParams& tp, const DeviceInfo& dev, Candidate& out);
 
 // Row-copy candidate for problems whose fastest dimension is kept; false if not applicable.

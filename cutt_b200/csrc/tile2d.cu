@@ -1,5 +1,6 @@
 // Two-dimensional tile transpose kernel for sm_100a (see tile2d.h): one tile per thread block,
-// cp.async loads into 128-byte-swizzled shared memory, register-transposed stores.
+// 16-byte global accesses on both sides whatever the alignment of the rows, 128-byte-swizzled
+// shared memory, register-transposed stores.
 #include <map>
 #include <mutex>
 #include "kernels.h"
@@ -7,37 +8,46 @@
 
 namespace cuttb {
 
-template <int ELT, int WIB, int WOB>
+template <int ELT, int LOAD, int STORE>
 __global__ void __launch_bounds__(256)
 tile2d_kernel(const __grid_constant__ T2dDesc D, const unsigned char* __restrict__ in, unsigned char* __restrict__ out) {
-  extern __shared__ __align__(1024) unsigned char t2d_smem[];
+  extern __shared__ __align__(128) unsigned char t2d_smem[];
   const uint32_t tid = threadIdx.x;
   if (blockIdx.x >= D.numTiles) return;
   T2dTile t;
   t2d_decode(D, blockIdx.x, t);
   const uint32_t stage = (uint32_t)__cvta_generic_to_shared(t2d_smem);
   const uint32_t nUnits = t2d_load_units(D);
-  for (uint32_t u = tid; u < nUnits; u += blockDim.x) t2d_load_unit<ELT, WIB>(D, t, stage, in, u);
-  asm volatile("cp.async.commit_group;\n" ::: "memory");
-  asm volatile("cp.async.wait_group 0;\n" ::: "memory");
+  if (LOAD == 1) {
+    for (uint32_t u = tid; u < nUnits; u += blockDim.x) t2d_load_shift<ELT>(D, t, stage, in, u);
+  } else {
+    for (uint32_t u = tid; u < nUnits; u += blockDim.x) t2d_load_unit<ELT, (LOAD == 1 ? 16 : LOAD)>(D, t, stage, in, u);
+    asm volatile("cp.async.commit_group;\n" ::: "memory");
+    asm volatile("cp.async.wait_group 0;\n" ::: "memory");
+  }
   __syncthreads();
   const uint32_t nItems = t2d_store_items(D);
-  for (uint32_t it = tid; it < nItems; it += blockDim.x) t2d_store_item<ELT, WOB>(D, t, stage, out, it);
+  if (STORE == 1) {
+    for (uint32_t it = tid; it < nItems; it += blockDim.x) t2d_store_shear<ELT>(D, t, stage, out, it);
+  } else {
+    for (uint32_t it = tid; it < nItems; it += blockDim.x) t2d_store_item<ELT, (STORE == 1 ? 16 : STORE)>(D, t, stage, out, it);
+  }
 }
 
 typedef void (*T2dKernel)(const T2dDesc, const unsigned char*, unsigned char*);
 
 static T2dKernel pick_t2d(const T2dDesc& D) {
-#define T2D_CASE(E, A, B) if (D.elt == E && D.wiB == A && D.woB == B) return tile2d_kernel<E, A, B>;
-  T2D_CASE(4, 4, 4) T2D_CASE(4, 4, 8) T2D_CASE(4, 4, 16)
-  T2D_CASE(4, 8, 4) T2D_CASE(4, 8, 8) T2D_CASE(4, 8, 16)
-  T2D_CASE(4, 16, 4) T2D_CASE(4, 16, 8) T2D_CASE(4, 16, 16)
-  T2D_CASE(8, 8, 8) T2D_CASE(8, 8, 16) T2D_CASE(8, 16, 8) T2D_CASE(8, 16, 16)
+#define T2D_CASE(E, A, B) if (D.elt == E && D.loadMode == A && D.storeMode == B) return tile2d_kernel<E, A, B>;
+#define T2D_ROW(E, A) T2D_CASE(E, A, 16) T2D_CASE(E, A, 1) T2D_CASE(E, A, 8)
+  T2D_ROW(4, 16) T2D_ROW(4, 1) T2D_ROW(4, 8) T2D_ROW(4, 4)
+  T2D_CASE(4, 16, 4) T2D_CASE(4, 1, 4) T2D_CASE(4, 8, 4) T2D_CASE(4, 4, 4)
+  T2D_ROW(8, 16) T2D_ROW(8, 1) T2D_ROW(8, 8)
+#undef T2D_ROW
 #undef T2D_CASE
   return nullptr;
 }
 
-size_t t2d_smem_bytes(const T2dDesc& D) { return (size_t)D.ta * D.tb * D.elt; }
+size_t t2d_smem_bytes(const T2dDesc& D) { return (size_t)D.nboxes * D.rowsAlloc * 128u; }
 
 int t2d_blocks_per_sm(const T2dDesc& D) {
   T2dKernel k = pick_t2d(D);
@@ -50,13 +60,20 @@ int t2d_blocks_per_sm(const T2dDesc& D) {
   return nb;
 }
 
+// The cp.async load modes and the plain store modes need buffers aligned to their access width; the
+// shift and shear modes take any element-aligned buffer (the misalignment travels in the descriptor).
 bool t2d_pointers_aligned(const T2dDesc& D, const void* in, const void* out) {
-  return (uintptr_t)in % D.wiB == 0 && (uintptr_t)out % D.woB == 0;
+  const uintptr_t ai = D.loadMode == 1 ? D.elt : D.loadMode, ao = D.storeMode == 1 ? D.elt : D.storeMode;
+  return (uintptr_t)in % ai == 0 && (uintptr_t)out % ao == 0;
 }
 
-cudaError_t launch_t2d(const T2dDesc& D, const void* in, void* out, cudaStream_t stream) {
-  T2dKernel k = pick_t2d(D);
+cudaError_t launch_t2d(const T2dDesc& desc, const void* in, void* out, cudaStream_t stream) {
+  T2dKernel k = pick_t2d(desc);
   if (!k) return cudaErrorInvalidValue;
+  T2dDesc D = desc;
+  const uintptr_t ve = 16 / D.elt;
+  D.inMis = (uint32_t)(((uintptr_t)in / D.elt) % ve);
+  D.outMis = (uint32_t)(((uintptr_t)out / D.elt) % ve);
   k<<<D.numTiles, D.nthreads, t2d_smem_bytes(D), stream>>>(D, (const unsigned char*)in, (unsigned char*)out);
   count_launch();
   return cudaGetLastError();

@@ -6,20 +6,35 @@
 // is ta elements along dimension 0 by tb elements along dimension p, one tile per thread block.
 // This is the case the reference serves with transposeTiled (src/cuttkernel.cu:123-222) and the
 // general tiled kernel of this library with a descriptor-driven code path; here the tile shape is
-// fixed enough for the index arithmetic to collapse to shifts and masks, which is what the
-// instruction-bound 4-byte cases need.
+// fixed enough for the index arithmetic to collapse to shifts and masks.
 //
 // Shared memory holds the tile as rows of 128 bytes along dimension 0 (nboxes row blocks side by
-// side), row r of a block at r * 128, its 16-byte chunk c at chunk position c ^ (r & 7) - the
-// layout the tensor-map kernel gets from the copy engine (tma_transpose.h).
+// side); 16-byte chunk c of shared-memory row s sits at chunk position c ^ (s & 7) - the layout the
+// tensor-map kernel gets from the copy engine (tma_transpose.h).  Tile row q (a position along
+// dimension p, relative to the tile origin) is shared-memory row q + padTop.
 //
-// Load: cp.async of WIB bytes (16, 8 or 4: what the alignment of the input rows allows), consecutive
-// lanes along a row.  Store: an item is one 16-byte chunk (V = 16/elt elements along dimension 0) of
-// wo = WOB/elt consecutive rows: wo shared-memory vector loads, a register transpose, V global
-// stores of WOB bytes (16, 8 or 4: what the alignment of the output rows allows).  The lanes of a
-// warp are spread over WOB/4 chunks and 128/WOB row groups, so every store instruction writes 128
-// contiguous bytes of each output row it touches, and the row groups met by a quarter warp differ
-// in the row bits the swizzle uses: shared-memory reads are conflict free.
+// Every global access is 16 bytes wide and 16-byte aligned, whatever the alignment of the rows:
+//
+// Load modes.  16: the input rows start on 16-byte boundaries: cp.async of 16 bytes.  1 ("shift"):
+// they do not: for each 16-byte chunk of the tile the two aligned vectors that cover it are loaded
+// (ld.global.v4), the chunk is cut out of them in registers and stored to shared memory; only the
+// first and last vector of the whole buffer are read element by element.  8 and 4: cp.async of 8 or
+// 4 bytes (kept as the plain alternative for rows on 8- or 4-byte boundaries).
+//
+// Store modes.  An item is one 16-byte chunk of shared memory (V = 16/elt elements along dimension
+// 0, i.e. V output rows) over a few consecutive rows.  16: the output rows start on 16-byte
+// boundaries: V shared vector loads (V = W rows), a V x W register transpose, V global stores of 16
+// bytes.  1 ("shear"): they do not: output row c is misaligned by mo(c) elements, and the tile is
+// sheared accordingly - for row c it covers positions [cp - mo(c), cp + tb - mo(c)) instead of
+// [cp, cp + tb), so that every vector it writes is aligned; neighbouring tiles along p shear the
+// same way and leave no gap.  An item then reads 2V-1 rows (the V windows of its V output rows lie
+// within them), and the loads bring V-1 extra rows above the tile.  Only the first and last vector
+// of an output row are written element by element.  8 and 4: narrower stores on V x (8/elt) or
+// V x (4/elt) blocks.
+//
+// The lanes of a warp are spread over 4 chunks and 8 row groups (modes 16 and 1), so every store
+// instruction writes 128 contiguous bytes of each output row it touches, and the row groups met by
+// a quarter warp differ in the row bits the swizzle uses: shared-memory reads are conflict free.
 #pragma once
 #include "permute_desc.h"
 #include "permute_tile_impl.h"
@@ -27,15 +42,22 @@
 namespace cuttb {
 
 constexpr int kT2dMaxOuter = 6;
+constexpr uint32_t kT2dPadTop = 4;      // shared-memory rows in front of tile row 0 (sheared stores)
+constexpr uint32_t kT2dPadBottom = 4;   // and behind the last one (never loaded, keeps reads in range)
 
 struct T2dDesc {
   uint32_t elt;        // 4 or 8
   uint32_t ta;         // tile extent along dimension 0 (elements); ta * elt is a multiple of 128
   uint32_t tb;         // tile extent along dimension p (elements): 32 or 64
-  uint32_t tbShift;    // log2(tb)
   uint32_t nboxes;     // ta * elt / 128
   uint32_t nthreads;
-  uint32_t wiB, woB;   // bytes per access on the input / output side
+  uint32_t loadMode;   // 16, 8, 4 or 1 (see above)
+  uint32_t storeMode;  // 16, 8, 4 or 1
+  uint32_t padTop;     // kT2dPadTop for sheared stores, else 0
+  uint32_t rowsLoad;   // rows loaded per tile: tb, plus 16/elt - 1 rows above it for sheared stores
+  uint32_t rowsAlloc;  // shared-memory rows per row block
+  uint32_t inMis;      // (input buffer address / elt) mod (16/elt); set when the kernel is launched
+  uint32_t outMis;     // same for the output buffer
   uint32_t numTiles;
   uint32_t order;      // tile index runs fastest along 0: dimension 0, 1: dimension p
   uint32_t d0, dp;
@@ -43,11 +65,12 @@ struct T2dDesc {
   uint32_t nOuter;
   uint32_t nO[kT2dMaxOuter];
   uint32_t pad_;
-  FastDiv divA, divB, divO[kT2dMaxOuter];
+  FastDiv divA, divB, divRows, divO[kT2dMaxOuter];
   int64_t isP;         // input stride of dimension p (elements)
   int64_t os0;         // output stride of dimension 0 (elements)
   int64_t isO[kT2dMaxOuter], osO[kT2dMaxOuter];
   int64_t inBase, outBase;
+  int64_t inElems;     // elements of the input buffer (the over-fetching loads stay inside it)
 };
 
 struct T2dTile {
@@ -77,26 +100,121 @@ CUTT_HD void t2d_decode(const T2dDesc& D, uint32_t tile, T2dTile& t) {
   }
 }
 
-CUTT_HD uint32_t t2d_load_units(const T2dDesc& D) { return D.ta * D.tb * D.elt / D.wiB; }
-CUTT_HD uint32_t t2d_store_items(const T2dDesc& D) { return (D.ta * D.elt / 16u) * (D.tb * D.elt / D.woB); }
-
-// Load unit u: WIB bytes of one tile row.
-template <int ELT, int WIB>
-CUTT_HD void t2d_load_unit(const T2dDesc& D, const T2dTile& t, sptr_t stage, const unsigned char* gin, uint32_t u) {
-  constexpr uint32_t UPR = 128u / WIB;            // units per 128-byte row
-  const uint32_t q = u & (UPR - 1u);
-  const uint32_t rr = u / UPR;
-  const uint32_t r = rr & (D.tb - 1u);
-  const uint32_t k = rr >> D.tbShift;             // row block (128 bytes of dimension 0 each)
-  const uint32_t e0 = k * (128u / ELT) + q * (WIB / ELT);
-  if (t.c0 + e0 >= D.d0 || t.cp + r >= D.dp) return;   // (extents are multiples of the access width)
-  const unsigned char* g = gin + (t.inOff + (int64_t)e0 + (int64_t)r * D.isP) * ELT;
-  const uint32_t byteInRow = q * WIB;
-  const uint32_t s = k * (D.tb * 128u) + r * 128u + (((byteInRow >> 4) ^ (r & 7u)) << 4) + (byteInRow & 15u);
-  copy_g2s<WIB>(stage + s, g);
+// Shared-memory byte offset of chunk c8 (0..7) of shared-memory row `srow` in row block k.
+CUTT_HD uint32_t t2d_smem_offset(const T2dDesc& D, uint32_t k, uint32_t srow, uint32_t c8) {
+  return k * (D.rowsAlloc * 128u) + srow * 128u + ((c8 ^ (srow & 7u)) << 4);
 }
 
-// Store item `it`: wo rows x one 16-byte chunk -> V output rows x WOB bytes.
+CUTT_HD uint32_t t2d_load_units(const T2dDesc& D) {
+  const uint32_t perRow = 128u / (D.loadMode == 1u ? 16u : D.loadMode);
+  return D.nboxes * D.rowsLoad * perRow;
+}
+
+// Row block k, tile row q (may be negative: rows above the tile) and unit-in-row of load unit u.
+CUTT_HD void t2d_unit_decode(const T2dDesc& D, uint32_t u, uint32_t upr, uint32_t& k, int32_t& q, uint32_t& x) {
+  x = u & (upr - 1u);
+  const uint32_t rr = u / upr;
+  k = fdiv(rr, D.divRows);
+  q = (int32_t)(rr - k * D.rowsLoad) - (int32_t)(D.rowsLoad - D.tb);
+}
+
+// cp.async load unit: WIB bytes (16, 8 or 4) of one tile row; rows and buffer aligned to WIB.
+template <int ELT, int WIB>
+CUTT_HD void t2d_load_unit(const T2dDesc& D, const T2dTile& t, sptr_t stage, const unsigned char* gin, uint32_t u) {
+  constexpr uint32_t UPR = 128u / WIB;
+  uint32_t k, x;
+  int32_t q;
+  t2d_unit_decode(D, u, UPR, k, q, x);
+  const uint32_t e0 = k * (128u / ELT) + x * (WIB / ELT);
+  const int64_t pos = (int64_t)t.cp + q;
+  if (t.c0 + e0 >= D.d0 || pos < 0 || pos >= (int64_t)D.dp) return;   // (extents are multiples of the access width)
+  const unsigned char* g = gin + (t.inOff + (int64_t)e0 + (int64_t)q * D.isP) * ELT;
+  const uint32_t byteInRow = x * WIB;
+  copy_g2s<WIB>(stage + t2d_smem_offset(D, k, (uint32_t)(q + (int32_t)D.padTop), byteInRow >> 4) + (byteInRow & 15u), g);
+}
+
+// global -> registers / registers -> shared, 16 bytes (plain loads and stores; range-checked on the host)
+CUTT_HD void t2d_ldg16(uint32_t* dst, const unsigned char* g) {
+#if defined(__CUDA_ARCH__)
+  const uint4 v = *reinterpret_cast<const uint4*>(g);
+  dst[0] = v.x; dst[1] = v.y; dst[2] = v.z; dst[3] = v.w;
+#else
+  CUTT_CHECK_RANGE(g, 16, host_bounds().gin0, host_bounds().gin1);
+  memcpy(dst, g, 16);
+#endif
+}
+template <int ELT>
+CUTT_HD void t2d_ldg_elem(uint32_t* dst, const unsigned char* g) {
+#if defined(__CUDA_ARCH__)
+  if (ELT == 4) dst[0] = *reinterpret_cast<const uint32_t*>(g);
+  else { const uint2 v = *reinterpret_cast<const uint2*>(g); dst[0] = v.x; dst[1] = v.y; }
+#else
+  CUTT_CHECK_RANGE(g, ELT, host_bounds().gin0, host_bounds().gin1);
+  memcpy(dst, g, ELT);
+#endif
+}
+CUTT_HD void t2d_sts16(sptr_t s, const uint32_t* w) {
+#if defined(__CUDA_ARCH__)
+  asm volatile("st.shared.v4.u32 [%0], {%1, %2, %3, %4};\n" ::"r"(s), "r"(w[0]), "r"(w[1]), "r"(w[2]), "r"(w[3]) : "memory");
+#else
+  CUTT_CHECK_RANGE(s, 16, host_bounds().s0, host_bounds().s1);
+  memcpy(s, w, 16);
+#endif
+}
+
+// "Shift" load unit: one 16-byte chunk of the tile, cut out of the two aligned vectors that cover it.
+template <int ELT>
+CUTT_HD void t2d_load_shift(const T2dDesc& D, const T2dTile& t, sptr_t stage, const unsigned char* gin, uint32_t u) {
+  constexpr int VE = 16 / ELT;
+  constexpr int EW = ELT / 4;
+  uint32_t k, c8;
+  int32_t q;
+  t2d_unit_decode(D, u, 8u, k, q, c8);
+  const uint32_t e0 = k * (128u / ELT) + c8 * (uint32_t)VE;
+  const int64_t pos = (int64_t)t.cp + q;
+  if (t.c0 + e0 >= D.d0 || pos < 0 || pos >= (int64_t)D.dp) return;
+  const int64_t ge = t.inOff + (int64_t)e0 + (int64_t)q * D.isP;   // first element of the chunk in the buffer
+  const uint32_t m = (uint32_t)((ge + (int64_t)D.inMis) & (int64_t)(VE - 1));
+  const int64_t gl = ge - (int64_t)m;                              // first element of the aligned vector below it
+  uint32_t w[8];
+#pragma unroll
+  for (int i = 0; i < 8; i++) w[i] = 0u;
+  if (gl >= 0 && gl + 2 * VE <= D.inElems) {
+    t2d_ldg16(w, gin + gl * ELT);
+    if (m) t2d_ldg16(w + 4, gin + (gl + VE) * ELT);
+  } else {
+    // first or last vector of the buffer: the chunk's own elements, one by one, placed where the
+    // aligned loads would have put them
+#pragma unroll
+    for (int e = 0; e < 2 * VE; e++) {
+      const int64_t idx = gl + e;
+      if (e >= (int)m && e < (int)m + VE && idx >= 0 && idx < D.inElems) t2d_ldg_elem<ELT>(w + e * EW, gin + idx * ELT);
+    }
+  }
+  uint32_t o[4];
+  if (ELT == 4) {
+    uint32_t s[6];
+#pragma unroll
+    for (int i = 0; i < 6; i++) s[i] = (m & 2u) ? w[i + 2] : w[i];
+#pragma unroll
+    for (int i = 0; i < 4; i++) o[i] = (m & 1u) ? s[i + 1] : s[i];
+  } else {
+#pragma unroll
+    for (int i = 0; i < 4; i++) o[i] = m ? w[i + 2] : w[i];
+  }
+  t2d_sts16(stage + t2d_smem_offset(D, k, (uint32_t)(q + (int32_t)D.padTop), c8), o);
+}
+
+CUTT_HD uint32_t t2d_store_items(const T2dDesc& D) {
+  const uint32_t chunks = D.ta * D.elt / 16u;
+  if (D.storeMode == 1u) {
+    const uint32_t nv = D.tb / (16u / D.elt) + 1u;        // vectors per output row, one more in the last tile
+    return chunks * ((nv + 7u) & ~7u);
+  }
+  return chunks * (D.tb * D.elt / D.storeMode);
+}
+
+// Store item for output rows on WOB-byte boundaries: wo rows x one 16-byte chunk -> V output rows x WOB bytes.
 template <int ELT, int WOB>
 CUTT_HD void t2d_store_item(const T2dDesc& D, const T2dTile& t, sptr_t stage, unsigned char* gout, uint32_t it) {
   constexpr int WO = WOB / ELT;          // rows per item = elements per global store
@@ -117,13 +235,10 @@ CUTT_HD void t2d_store_item(const T2dDesc& D, const T2dTile& t, sptr_t stage, un
   const uint32_t row0 = (gb * NG + g) * (uint32_t)WO;
   const uint32_t r0 = t.c0 + chunk * (uint32_t)V;
   if (r0 >= D.d0 || t.cp + row0 >= D.dp) return;
-  const uint32_t box = chunk >> 3, cib = chunk & 7u;
   uint32_t x[WO][4];
 #pragma unroll
-  for (int i = 0; i < WO; i++) {
-    const uint32_t row = row0 + (uint32_t)i;
-    lds<16>(x[i], stage + box * (D.tb * 128u) + row * 128u + ((cib ^ (row & 7u)) << 4));
-  }
+  for (int i = 0; i < WO; i++)
+    lds<16>(x[i], stage + t2d_smem_offset(D, chunk >> 3, row0 + (uint32_t)i + D.padTop, chunk & 7u));
   unsigned char* g0 = gout + (t.outOff + (int64_t)(chunk * (uint32_t)V) * D.os0 + (int64_t)row0) * ELT;
   const int64_t os0B = D.os0 * ELT;
 #pragma unroll
@@ -138,6 +253,69 @@ CUTT_HD void t2d_store_item(const T2dDesc& D, const T2dTile& t, sptr_t stage, un
       stg<WOB>(g0, y);
     }
     g0 += os0B;
+  }
+}
+
+// One output row of a sheared item whose misalignment is MO elements: the aligned vector holds the
+// elements of shared rows (V-1) - MO + i, i < V.  pos0: position along p of its first element.
+template <int ELT, int MO>
+CUTT_HD void t2d_shear_row(const uint32_t (*x)[4], int j, unsigned char* g, int64_t pos0, int64_t dp) {
+  constexpr int VE = 16 / ELT;
+  constexpr int EW = ELT / 4;
+  uint32_t y[4];
+#pragma unroll
+  for (int i = 0; i < VE; i++) {
+#pragma unroll
+    for (int w = 0; w < EW; w++) y[i * EW + w] = x[(VE - 1) - MO + i][j * EW + w];
+  }
+  if (pos0 >= 0 && pos0 + VE <= dp) {
+    stg<16>(g, y);
+  } else {   // first or last vector of an output row: only the elements inside it
+#pragma unroll
+    for (int i = 0; i < VE; i++)
+      if (pos0 + i >= 0 && pos0 + i < dp) stg<ELT>(g + i * ELT, y + i * EW);
+  }
+}
+
+// "Shear" store item: one chunk (V output rows) x one aligned vector per output row.
+template <int ELT>
+CUTT_HD void t2d_store_shear(const T2dDesc& D, const T2dTile& t, sptr_t stage, unsigned char* gout, uint32_t it) {
+  constexpr int VE = 16 / ELT;
+  constexpr int NR = 2 * VE - 1;         // shared-memory rows an item reads
+  const uint32_t cl = it & 3u;
+  uint32_t g = (it >> 2) & 7u;
+  const uint32_t rest = it >> 5;
+  const uint32_t cblocks = (D.ta * ELT / 16u) / 4u;
+  const uint32_t cb = rest & (cblocks - 1u);
+  const uint32_t gb = rest / cblocks;
+  if (ELT == 8) g = ((g << 1) & 6u) | ((g >> 2) & 1u);   // (see t2d_store_item)
+  const uint32_t chunk = cb * 4u + cl;
+  const uint32_t kv = gb * 8u + g;                       // vector index along p within the sheared tile
+  const uint32_t nvFull = D.tb / (uint32_t)VE;
+  const bool lastTile = t.cp + D.tb >= D.dp;
+  if (kv > nvFull || (kv == nvFull && !lastTile)) return;
+  const uint32_t r0 = t.c0 + chunk * (uint32_t)VE;
+  if (r0 >= D.d0) return;
+  const int32_t qb = (int32_t)(kv * (uint32_t)VE) - (VE - 1);   // tile row held by x[0]
+  if ((int64_t)t.cp + qb >= (int64_t)D.dp) return;
+  uint32_t x[NR][4];
+#pragma unroll
+  for (int r = 0; r < NR; r++)
+    lds<16>(x[r], stage + t2d_smem_offset(D, chunk >> 3, (uint32_t)(qb + r + (int32_t)D.padTop), chunk & 7u));
+#pragma unroll
+  for (int j = 0; j < VE; j++) {
+    if (r0 + (uint32_t)j >= D.d0) continue;
+    const int64_t rowOff = t.outOff + (int64_t)(chunk * (uint32_t)VE + (uint32_t)j) * D.os0;   // element (c, cp)
+    const uint32_t mo = (uint32_t)((rowOff + (int64_t)D.outMis) & (int64_t)(VE - 1));
+    const int64_t pos0 = (int64_t)t.cp + (int64_t)(kv * (uint32_t)VE) - (int64_t)mo;
+    if (pos0 >= (int64_t)D.dp) continue;
+    if (kv == nvFull && mo == 0u) continue;
+    unsigned char* gp = gout + (rowOff + (int64_t)(kv * (uint32_t)VE) - (int64_t)mo) * ELT;
+    // (mo is the same for every lane of the warp: no divergence)
+    if (mo == 0u) t2d_shear_row<ELT, 0>(x, j, gp, pos0, (int64_t)D.dp);
+    else if (mo == 1u) t2d_shear_row<ELT, 1>(x, j, gp, pos0, (int64_t)D.dp);
+    else if (ELT == 4 && mo == 2u) t2d_shear_row<ELT, (ELT == 4 ? 2 : 0)>(x, j, gp, pos0, (int64_t)D.dp);
+    else if (ELT == 4) t2d_shear_row<ELT, (ELT == 4 ? 3 : 0)>(x, j, gp, pos0, (int64_t)D.dp);
   }
 }
 

@@ -26,16 +26,17 @@ def test_forced_tile_shapes_and_widths(native, oracle_mod, dims, perm):
         for ta in (128, 256):
             for tb in (32, 64):
                 for kw in (dict(nthreads=128, loop_order=0), dict(nthreads=256, loop_order=1)):
-                    for maxvec in (16, 8, 4):
+                    for maxvec, force in ((16, 0), (16, 1), (8, 0), (4, 0)):
                         if maxvec < elt:
                             continue
                         out, desc = gpu_transpose(native, dims, perm, elt, a, planner="params", method=7, tin=ta,
-                                                  tout=tb * elt, stages=1, max_vec=maxvec, **kw)
+                                                  tout=tb * elt, stages=1, max_vec=maxvec, extend=force, **kw)
                         label = json.loads(desc)["label"]
                         assert label.startswith("t2d "), desc
                         assert_bit_exact(out, want, desc)
                         labels.add(label.split(" lo=")[0])
     assert len(labels) >= 4
+    assert any("in/shift out/shear" in l for l in labels)
 
 
 def test_rejected_problems(native):
@@ -46,24 +47,28 @@ def test_rejected_problems(native):
     assert native.plan_params([8, 64], [1, 0], 4, 0, method=7, tin=128, tout=128, stages=1)[0] == bad
 
 
-def test_element_aligned_buffers(native, oracle_mod):
-    """A plan with 16-byte accesses executed on buffers that are only element-aligned must take the
-    element-wise form of the same tile."""
+@pytest.mark.parametrize("off_in,off_out", [(1, 0), (0, 1), (1, 1), (3, 2), (2, 3)])
+def test_element_aligned_buffers(native, oracle_mod, off_in, off_out):
+    """A plan whose strides allow aligned 16-byte accesses, executed on buffers that start 1-3
+    elements past a 16-byte boundary, takes the shift / shear form of the same tile; a plan already
+    in that form takes them directly.  The words around the output stay untouched."""
     import torch
-    dims, perm = [256, 260], [1, 0]
-    for elt in (4, 8):
-        vol = volume(dims)
-        a = raw_bits(vol, elt, 3)
-        dt = torch.int32 if elt == 4 else torch.int64
-        big_in = torch.zeros(vol + 1, dtype=dt, device="cuda")
-        big_out = torch.full((vol + 1,), -1, dtype=dt, device="cuda")
-        big_in[1:] = torch.from_numpy(a.view(np.int32 if elt == 4 else np.int64)).cuda()
-        rc, h = native.plan_params(dims, perm, elt, 0, method=7, tin=256, tout=64 * elt, stages=1, nthreads=128)
-        assert rc == 0
-        assert "in/w%d out/w%d" % (16 // elt, 16 // elt) in native.plan_describe(h)
-        assert native.cuttExecute(h, big_in.data_ptr() + elt, big_out.data_ptr() + elt) == 0
-        torch.cuda.synchronize()
-        native.cuttDestroy(h)
-        out = big_out[1:].cpu().numpy().view(np.uint32 if elt == 4 else np.uint64)
-        assert_bit_exact(out, oracle_mod.transpose_blocked(dims, perm, a))
-        assert int(big_out[0].item()) == -1
+    for dims, perm in (([256, 260], [1, 0]), ([131, 67, 5], [1, 0, 2]), ([130, 3, 34], [2, 1, 0])):
+        for elt in (4, 8):
+            ve = 16 // elt
+            vol = volume(dims)
+            a = raw_bits(vol, elt, 3)
+            dt = torch.int32 if elt == 4 else torch.int64
+            oi, oo = off_in % ve, off_out % ve
+            big_in = torch.zeros(vol + 8, dtype=dt, device="cuda")
+            big_out = torch.full((vol + 8,), -1, dtype=dt, device="cuda")
+            big_in[oi:oi + vol] = torch.from_numpy(a.view(np.int32 if elt == 4 else np.int64)).cuda()
+            rc, h = native.plan_params(dims, perm, elt, 0, method=7, tin=256, tout=64 * elt, stages=1, nthreads=128)
+            assert rc == 0
+            assert native.cuttExecute(h, big_in.data_ptr() + oi * elt, big_out.data_ptr() + oo * elt) == 0
+            torch.cuda.synchronize()
+            native.cuttDestroy(h)
+            got = big_out.cpu().numpy().view(np.uint32 if elt == 4 else np.uint64)
+            assert_bit_exact(got[oo:oo + vol], oracle_mod.transpose_blocked(dims, perm, a), (dims, perm, elt))
+            ones = np.iinfo(got.dtype).max
+            assert (got[:oo] == ones).all() and (got[oo + vol:] == ones).all()

@@ -314,56 +314,93 @@ def test_tensor_map_candidates_are_enumerated_for_legal_strides_only(hc):
 def _t2d(hc):
     hc.cutt_hostcheck_run_t2d.argtypes = [ctypes.c_int, ctypes.POINTER(ctypes.c_int), ctypes.POINTER(ctypes.c_int),
                                           ctypes.c_int, ctypes.c_uint, ctypes.c_uint, ctypes.c_int, ctypes.c_int,
-                                          ctypes.c_int, ctypes.c_void_p, ctypes.c_void_p, ctypes.c_char_p, ctypes.c_int]
+                                          ctypes.c_int, ctypes.c_int, ctypes.c_void_p, ctypes.c_void_p, ctypes.c_char_p,
+                                          ctypes.c_int]
     return hc.cutt_hostcheck_run_t2d
 
 
-@pytest.mark.parametrize("dims,perm", [
+T2D_SHAPES = [
     ([64, 64], [1, 0]), ([129, 130], [1, 0]), ([131, 67], [1, 0]), ([66, 202], [1, 0]), ([132, 200], [1, 0]),
     ([36, 8, 44], [2, 1, 0]), ([41, 6, 53], [1, 2, 0]), ([72, 3, 5, 57], [3, 0, 2, 1]), ([25, 4, 3, 2, 40], [4, 2, 0, 3, 1]),
     ([30, 2, 3, 2, 2, 3, 2, 34], [7, 6, 5, 4, 3, 2, 1, 0]), ([16, 10, 36], [2, 0, 1]), ([250, 3, 18], [2, 1, 0]),
-])
+    ([63, 65], [1, 0]), ([97, 16], [1, 0]),
+]
+
+
+@pytest.mark.parametrize("dims,perm", T2D_SHAPES)
 def test_two_dimensional_tiles(hc, oracle_mod, dims, perm):
-    """The swizzled two-dimensional tile method on the host: every access width the strides allow and
-    all narrower ones, every tile shape, both tile orders, both element sizes; odd extents give edge
-    tiles in both dimensions and rows that start on 4- and 8-byte boundaries only."""
+    """The swizzled two-dimensional tile method on the host, every access range- and
+    alignment-checked: the wide modes the strides select (aligned cp.async / 16-byte stores, or the
+    shift loads and sheared stores for rows that are not 16-byte aligned), the same forced to
+    shift + shear, and the plain narrow modes; every tile shape, both tile orders, both element
+    sizes; odd extents give edge tiles in both dimensions."""
     run = _t2d(hc)
-    widths = set()
+    modes = set()
     for elt in (4, 8):
         a = raw_bits(volume(dims), elt, 43)
         want = oracle_mod.transpose_blocked(dims, perm, a)
         for ta in (128, 256):
             for tb in (32, 64):
                 for order, nt in ((0, 128), (1, 256)):
-                    for maxvec in (16, 8, 4):
+                    for maxvec, force in ((16, 0), (16, 1), (8, 0), (4, 0)):
                         if maxvec < elt:
                             continue
                         out = np.full_like(a, 0xAB)
                         lab = ctypes.create_string_buffer(2048)
-                        rc = run(len(dims), _iarr(dims), _iarr(perm), elt, ta, tb, nt, order, maxvec, a.ctypes.data,
-                                 out.ctypes.data, lab, 2048)
-                        assert rc == 0, (rc, dims, perm, elt, ta, tb, maxvec)
+                        rc = run(len(dims), _iarr(dims), _iarr(perm), elt, ta, tb, nt, order, maxvec, force,
+                                 a.ctypes.data, out.ctypes.data, lab, 2048)
+                        assert rc == 0, (rc, dims, perm, elt, ta, tb, maxvec, force)
                         label = json.loads(lab.value.decode())["label"]
                         assert np.array_equal(out, want), (dims, perm, elt, label)
-                        widths.add(label.split(" lo=")[0].split(" ", 2)[2])
-    assert widths
+                        modes.add(label.split(" lo=")[0].split(" ", 2)[2])
+    assert "in/shift out/shear" in modes
 
 
-def test_two_dimensional_tiles_widths_and_rejections(hc):
+@pytest.mark.parametrize("off_in,off_out", [(0, 0), (1, 0), (0, 1), (1, 1), (3, 2), (2, 3)])
+def test_two_dimensional_tiles_on_unaligned_buffers(hc, oracle_mod, off_in, off_out):
+    """Shift loads and sheared stores take any element-aligned buffer address: the buffers start
+    1-3 elements past a 16-byte boundary; the words around the output must stay untouched."""
+    run = _t2d(hc)
+    for dims, perm in (([131, 67], [1, 0]), ([64, 64], [1, 0]), ([41, 6, 53], [1, 2, 0]), ([130, 3, 34], [2, 1, 0])):
+        for elt in (4, 8):
+            vol = volume(dims)
+            a = raw_bits(vol, elt, 47)
+            want = oracle_mod.transpose_blocked(dims, perm, a)
+            dt = a.dtype
+            backing_in = np.zeros(vol + 8, dtype=dt)
+            backing_out = np.full(vol + 8, 0x5A, dtype=dt)
+            base_in = (-backing_in.ctypes.data // elt) % (16 // elt)      # elements up to the next 16-byte boundary
+            base_out = (-backing_out.ctypes.data // elt) % (16 // elt)
+            oi, oo = base_in + off_in % (16 // elt), base_out + off_out % (16 // elt)
+            backing_in[oi:oi + vol] = a
+            for ta, tb in ((128, 32), (256, 64)):
+                backing_out[:] = 0x5A
+                rc = run(len(dims), _iarr(dims), _iarr(perm), elt, ta, tb, 128, 0, 16, 1,
+                         backing_in.ctypes.data + oi * elt, backing_out.ctypes.data + oo * elt, None, 0)
+                assert rc == 0, (rc, dims, perm, elt, off_in, off_out)
+                assert np.array_equal(backing_out[oo:oo + vol], want), (dims, perm, elt, off_in, off_out)
+                assert (backing_out[:oo] == 0x5A).all() and (backing_out[oo + vol:] == 0x5A).all()
+
+
+def test_two_dimensional_tiles_modes_and_rejections(hc):
     run = _t2d(hc)
     a = np.zeros(1 << 16, dtype=np.uint64)
     out = np.zeros_like(a)
 
-    def label(dims, perm, elt, maxvec=16):
+    def label(dims, perm, elt, maxvec=16, force=0):
         lab = ctypes.create_string_buffer(2048)
-        rc = run(len(dims), _iarr(dims), _iarr(perm), elt, 128, 32, 128, 0, maxvec, a.ctypes.data, out.ctypes.data, lab, 2048)
+        rc = run(len(dims), _iarr(dims), _iarr(perm), elt, 128, 32, 128, 0, maxvec, force, a.ctypes.data, out.ctypes.data,
+                 lab, 2048)
         return rc, (json.loads(lab.value.decode())["label"] if rc == 0 else "")
 
     assert "in/w4 out/w4" in label([64, 64], [1, 0], 4)[1]
-    assert "in/w2 out/w4" in label([66, 64], [1, 0], 4)[1]       # input rows on 8-byte boundaries
-    assert "in/w4 out/w1" in label([64, 67], [1, 0], 4)[1]       # output rows on 4-byte boundaries
-    assert "in/w1 out/w2" in label([67, 66], [1, 0], 4)[1]
-    assert "in/w2 out/w1" in label([66, 67], [1, 0], 8)[1]
+    assert "in/shift out/w4" in label([66, 64], [1, 0], 4)[1]    # input rows on 8-byte boundaries
+    assert "in/w4 out/shear" in label([64, 67], [1, 0], 4)[1]    # output rows on 4-byte boundaries
+    assert "in/shift out/shear" in label([67, 66], [1, 0], 4)[1]
+    assert "in/shift out/shear" in label([67, 67], [1, 0], 8)[1]
+    assert "in/w2 out/w2" in label([66, 66], [1, 0], 8)[1]
+    assert "in/shift out/shear" in label([64, 64], [1, 0], 4, force=1)[1]
+    assert "in/w2 out/w1" in label([66, 67], [1, 0], 4, maxvec=8)[1]
     assert "in/w1 out/w1" in label([64, 64], [1, 0], 4, maxvec=4)[1]
     assert label([64, 8, 64], [0, 2, 1], 4)[0] == 2              # fastest dimension kept
     assert label([64, 64], [0, 1], 4)[0] == 2                    # identity
