@@ -25,7 +25,8 @@ reproduced; other bench numbers (a plain memory-copy benchmark there) are not of
 
 ``-method M`` forces an implementation for every tensor (this library's method numbers: 0 copy
 kernel and 1 driver copy for identity permutations, 2 tiled kernel with default tile parameters,
-3 one thread per element, 4 strided row copy) and ``-offset B`` shifts both device buffers by B
+3 one thread per element, 4 strided row copy, 6 tensor-map transpose, 7 two-dimensional tiles with
+swizzled shared memory) and ``-offset B`` shifts both device buffers by B
 bytes (a multiple of the element size): profiling aids without a counterpart in the original.
 
 ``-volume`` scales every generated tensor (default 200 M elements, as the original); ``-samples``
@@ -242,7 +243,7 @@ def main(argv=None, checker="permute"):
     ap.add_argument("-volume", type=int, default=200_000_000, help="elements per generated tensor")
     ap.add_argument("-samples", type=int, default=None, help="random draws per rank (benches 3, 5RR, 7)")
     ap.add_argument("-nocheck", action="store_true")
-    ap.add_argument("-method", type=int, default=None, choices=[0, 1, 2, 3, 4])
+    ap.add_argument("-method", type=int, default=None, choices=[0, 1, 2, 3, 4, 6, 7])
     ap.add_argument("-offset", type=int, default=0, help="byte offset of both device buffers")
     args = ap.parse_args(argv)
     import torch

@@ -577,9 +577,15 @@ cuttResult make_plan(cuttHandle* handle, int rank, const int* dim, const int* pe
         int bestIdx = -1;
         std::vector<std::pair<double, int>> scored;   // (score, candidate) of fully timed candidates
         Plan trial = *p;
+        size_t nT2d = 0, nTma = 0;
+        const size_t familyQuota = env_size("CUTT_MEASURE_FAMILY", 6);
         for (size_t i = 0; i < cands.size(); i++) {
-          // beyond the model's best `topk`, only methods of another kind still get their turn
+          // beyond the model's best `topk`, only methods of another kind still get their turn; the
+          // two swizzled-tile families are timed up to a quota each (their estimates are coarse, so
+          // they do not compete for the tiled kernel's slots)
           if (i >= topk && cands[i].method == kMethodTiles) continue;
+          if (cands[i].method == kMethodT2d && nT2d++ >= familyQuota) continue;
+          if (cands[i].method == kMethodTma && nTma++ >= familyQuota) continue;
           if (!adopt_candidate(trial, dev, cands[i])) continue;
           bool fail = false;
           double tmin = 1e30;

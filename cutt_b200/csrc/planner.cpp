@@ -818,11 +818,13 @@ bool build_tma(const Problem& P, const TileParams& tp, const DeviceInfo& dev, Ca
   out.blocksPerSM = bps;
   out.gridBlocks = tp.stages == 1 ? (int)ntiles : (int)std::min<int64_t>(ntiles, (int64_t)dev.numSM * bps);
   // Estimate: the copy rate, reduced by the share of each tile that lies outside the tensor and,
-  // for tensors too small to give every SM a few tiles, by the idle SMs.  Measured on B200: within
-  // its class this kernel runs at or above the rate of the best cp.async tile plan.
+  // for tensors too small to give every SM a few tiles, by the idle SMs.  Measured on B200: in its
+  // one-tile-per-block form this kernel runs within 1-2 % of the best cp.async tile plan (a ring of
+  // stages in a persistent block: 15 % behind), so the estimate sits just below the fitted model's
+  // typical value for those and cuttPlanMeasure decides.
   const double util = ((double)P.d[0] / ((double)D.nA * ta)) * ((double)P.d[p] / ((double)D.nB * tb));
   const double fill = std::min(1.0, (double)ntiles / ((double)dev.numSM * 2.0));
-  const double eff = 0.96 * util * (0.25 + 0.75 * fill);
+  const double eff = 0.93 * util * (0.25 + 0.75 * fill);
   out.cost = 2.0 * (double)P.volume * elt / (dev.hbmGBs * 1e9 * eff) + 5e-6;
   char buf[160];
   snprintf(buf, sizeof buf, "tma t=%ux%u boxes=%u st=%u lo=%u nt=%u smem=%d tiles=%u", ta, tb, D.nboxes, D.stages,
@@ -867,13 +869,14 @@ bool build_t2d(const Problem& P, const TileParams& tp, const DeviceInfo& dev, Ca
   D.tb = tb;
   D.nboxes = ta * elt / 128;
   D.nthreads = tp.nthreads;
-  // 16-byte accesses always: directly when the rows are aligned, else through the shift / shear
-  // modes.  A cap below 16 bytes (tests, comparisons) selects the plain narrow modes; extend = 1
-  // forces shift / shear even for aligned rows (plans that must accept any buffer address).
+  // The widest plain accesses the strides allow (16, 8 or 4 bytes per side).  extend = 1 selects
+  // the shift / shear modes instead: 16-byte aligned accesses whatever the alignment of rows and
+  // buffers.  Measured on B200 they cost 1.5 warp instructions per element and run at 4.0-5.3 TB/s,
+  // below the 8-byte modes (6.0 TB/s), so they serve as the form a plan falls back to when its
+  // buffers turn out not to be aligned for its access width, not as a first choice.
   D.loadMode = width(true);
   D.storeMode = width(false);
-  if (tp.maxVecBytes >= 16 && (D.loadMode < 16 || tp.extend)) D.loadMode = 1;
-  if (tp.maxVecBytes >= 16 && (D.storeMode < 16 || tp.extend)) D.storeMode = 1;
+  if (tp.extend) D.loadMode = D.storeMode = 1;
   D.padTop = D.storeMode == 1 ? kT2dPadTop : 0;
   D.rowsLoad = tb + (D.storeMode == 1 ? 16 / elt - 1 : 0);
   D.rowsAlloc = D.storeMode == 1 ? tb + kT2dPadTop + kT2dPadBottom : tb;
@@ -910,9 +913,9 @@ bool build_t2d(const Problem& P, const TileParams& tp, const DeviceInfo& dev, Ca
   // narrow accesses, and for tensors too small to give every SM a few tiles by the idle SMs.
   const double util = ((double)P.d[0] / ((double)D.nA * ta)) * ((double)P.d[p] / ((double)D.nB * tb));
   const double fill = std::min(1.0, (double)ntiles / ((double)dev.numSM * 4.0));
-  auto side = [](uint32_t mode) { return mode == 16 ? 1.0 : (mode == 1 ? 0.98 : (mode == 8 ? 0.95 : 0.7)); };
+  auto side = [](uint32_t mode) { return mode == 16 ? 1.0 : (mode == 8 ? 0.97 : (mode == 1 ? 0.8 : 0.75)); };
   const double narrow = side(D.loadMode) * side(D.storeMode);
-  const double eff = 0.955 * util * narrow * (0.25 + 0.75 * fill);
+  const double eff = 0.93 * util * narrow * (0.25 + 0.75 * fill);
   out.cost = 2.0 * (double)P.volume * elt / (dev.hbmGBs * 1e9 * eff) + 5e-6;
   char buf[160];
   char li[16], lo[16];
@@ -1029,7 +1032,9 @@ std::vector<Candidate> enumerate_candidates(const Problem& P, const DeviceInfo& 
             tp.tinBytes = a; tp.toutBytes = b * (uint32_t)P.elt; tp.loopOrder = lo; tp.nthreads = nt;
             tp.stages = 1;
             Candidate c;
-            if (build_t2d(P, tp, dev, c)) res.push_back(c);
+            // (rows on 4-byte boundaries: measured 3.6-4.1 TB/s against 4.4-5.7 TB/s for the general
+            // kernel's over-fetching loads - not worth a measurement slot)
+            if (build_t2d(P, tp, dev, c) && c.t2d.loadMode >= 8 && c.t2d.storeMode >= 8) res.push_back(c);
             if (dev.tmaLoads && build_tma(P, tp, dev, c)) res.push_back(c);
           }
   }

@@ -19,7 +19,20 @@ tile2d_kernel(const __grid_constant__ T2dDesc D, const unsigned char* __restrict
   const uint32_t stage = (uint32_t)__cvta_generic_to_shared(t2d_smem);
   const uint32_t nUnits = t2d_load_units(D);
   if (LOAD == 1) {
-    for (uint32_t u = tid; u < nUnits; u += blockDim.x) t2d_load_shift<ELT>(D, t, stage, in, u);
+    // four units per thread at a time: eight global loads in flight before the first is consumed
+    constexpr int B = 4;
+    for (uint32_t u0 = tid; u0 < nUnits; u0 += B * blockDim.x) {
+      uint32_t w[B][8], m[B], soff[B];
+      bool ok[B];
+#pragma unroll
+      for (int b = 0; b < B; b++) {
+        const uint32_t u = u0 + (uint32_t)b * blockDim.x;
+        ok[b] = u < nUnits && t2d_shift_fetch<ELT>(D, t, in, u, w[b], m[b], soff[b]);
+      }
+#pragma unroll
+      for (int b = 0; b < B; b++)
+        if (ok[b]) t2d_shift_commit<ELT>(stage + soff[b], w[b], m[b]);
+    }
   } else {
     for (uint32_t u = tid; u < nUnits; u += blockDim.x) t2d_load_unit<ELT, (LOAD == 1 ? 16 : LOAD)>(D, t, stage, in, u);
     asm volatile("cp.async.commit_group;\n" ::: "memory");

@@ -163,8 +163,12 @@ CUTT_HD void t2d_sts16(sptr_t s, const uint32_t* w) {
 }
 
 // "Shift" load unit: one 16-byte chunk of the tile, cut out of the two aligned vectors that cover it.
+// In two steps, so that a thread can have the global loads of several units in flight before it
+// needs the data of the first: fetch (global -> registers; returns false if the unit lies outside
+// the tensor) and commit (cut the chunk out, registers -> shared).
 template <int ELT>
-CUTT_HD void t2d_load_shift(const T2dDesc& D, const T2dTile& t, sptr_t stage, const unsigned char* gin, uint32_t u) {
+CUTT_HD bool t2d_shift_fetch(const T2dDesc& D, const T2dTile& t, const unsigned char* gin, uint32_t u, uint32_t* w,
+                             uint32_t& m, uint32_t& soff) {
   constexpr int VE = 16 / ELT;
   constexpr int EW = ELT / 4;
   uint32_t k, c8;
@@ -172,11 +176,11 @@ CUTT_HD void t2d_load_shift(const T2dDesc& D, const T2dTile& t, sptr_t stage, co
   t2d_unit_decode(D, u, 8u, k, q, c8);
   const uint32_t e0 = k * (128u / ELT) + c8 * (uint32_t)VE;
   const int64_t pos = (int64_t)t.cp + q;
-  if (t.c0 + e0 >= D.d0 || pos < 0 || pos >= (int64_t)D.dp) return;
+  if (t.c0 + e0 >= D.d0 || pos < 0 || pos >= (int64_t)D.dp) return false;
   const int64_t ge = t.inOff + (int64_t)e0 + (int64_t)q * D.isP;   // first element of the chunk in the buffer
-  const uint32_t m = (uint32_t)((ge + (int64_t)D.inMis) & (int64_t)(VE - 1));
+  m = (uint32_t)((ge + (int64_t)D.inMis) & (int64_t)(VE - 1));
+  soff = t2d_smem_offset(D, k, (uint32_t)(q + (int32_t)D.padTop), c8);
   const int64_t gl = ge - (int64_t)m;                              // first element of the aligned vector below it
-  uint32_t w[8];
 #pragma unroll
   for (int i = 0; i < 8; i++) w[i] = 0u;
   if (gl >= 0 && gl + 2 * VE <= D.inElems) {
@@ -191,6 +195,11 @@ CUTT_HD void t2d_load_shift(const T2dDesc& D, const T2dTile& t, sptr_t stage, co
       if (e >= (int)m && e < (int)m + VE && idx >= 0 && idx < D.inElems) t2d_ldg_elem<ELT>(w + e * EW, gin + idx * ELT);
     }
   }
+  return true;
+}
+
+template <int ELT>
+CUTT_HD void t2d_shift_commit(sptr_t sdst, const uint32_t* w, uint32_t m) {
   uint32_t o[4];
   if (ELT == 4) {
     uint32_t s[6];
@@ -202,7 +211,13 @@ CUTT_HD void t2d_load_shift(const T2dDesc& D, const T2dTile& t, sptr_t stage, co
 #pragma unroll
     for (int i = 0; i < 4; i++) o[i] = m ? w[i + 2] : w[i];
   }
-  t2d_sts16(stage + t2d_smem_offset(D, k, (uint32_t)(q + (int32_t)D.padTop), c8), o);
+  t2d_sts16(sdst, o);
+}
+
+template <int ELT>
+CUTT_HD void t2d_load_shift(const T2dDesc& D, const T2dTile& t, sptr_t stage, const unsigned char* gin, uint32_t u) {
+  uint32_t w[8], m, soff;
+  if (t2d_shift_fetch<ELT>(D, t, gin, u, w, m, soff)) t2d_shift_commit<ELT>(stage + soff, w, m);
 }
 
 CUTT_HD uint32_t t2d_store_items(const T2dDesc& D) {

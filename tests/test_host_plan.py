@@ -394,11 +394,12 @@ def test_two_dimensional_tiles_modes_and_rejections(hc):
         return rc, (json.loads(lab.value.decode())["label"] if rc == 0 else "")
 
     assert "in/w4 out/w4" in label([64, 64], [1, 0], 4)[1]
-    assert "in/shift out/w4" in label([66, 64], [1, 0], 4)[1]    # input rows on 8-byte boundaries
-    assert "in/w4 out/shear" in label([64, 67], [1, 0], 4)[1]    # output rows on 4-byte boundaries
-    assert "in/shift out/shear" in label([67, 66], [1, 0], 4)[1]
-    assert "in/shift out/shear" in label([67, 67], [1, 0], 8)[1]
+    assert "in/w2 out/w4" in label([66, 64], [1, 0], 4)[1]       # input rows on 8-byte boundaries
+    assert "in/w4 out/w1" in label([64, 67], [1, 0], 4)[1]       # output rows on 4-byte boundaries
+    assert "in/w1 out/w2" in label([67, 66], [1, 0], 4)[1]
+    assert "in/w1 out/w1" in label([67, 67], [1, 0], 8)[1]
     assert "in/w2 out/w2" in label([66, 66], [1, 0], 8)[1]
+    assert "in/shift out/shear" in label([67, 66], [1, 0], 4, force=1)[1]
     assert "in/shift out/shear" in label([64, 64], [1, 0], 4, force=1)[1]
     assert "in/w2 out/w1" in label([66, 67], [1, 0], 4, maxvec=8)[1]
     assert "in/w1 out/w1" in label([64, 64], [1, 0], 4, maxvec=4)[1]
