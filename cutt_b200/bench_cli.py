@@ -64,7 +64,7 @@ def permute_checker(torch):
 
 
 def run_case(C, torch, dims, perm, elt, measure, buf_in, buf_out, checker=None, plantimer=False,
-             method=None, offset=0):
+             method=None, offset=0, stages=None, threads=None):
     vol = _vol(dims)
     words = 1
     if elt == 16:   # checked as two 64-bit words per element under an unpermuted innermost dimension
@@ -76,7 +76,14 @@ def run_case(C, torch, dims, perm, elt, measure, buf_in, buf_out, checker=None, 
     stream = torch.cuda.current_stream().cuda_stream
     t0 = time.perf_counter()
     if method is not None:
-        rc, h = C.plan_params(dims, perm, elt, stream, method=method)
+        kw = {}
+        if method in (6, 7):    # swizzled-tile kernels: 256-byte x 64-row (4-byte) / 32-row (8-byte) tiles, one per block
+            kw = dict(tin=256, tout=256, stages=1, nthreads=128)
+        if stages is not None:
+            kw["stages"] = stages
+        if threads is not None:
+            kw["nthreads"] = threads
+        rc, h = C.plan_params(dims, perm, elt, stream, method=method, **kw)
     elif elt not in (4, 8):   # sizes the original rejects: extension entry points
         if measure:
             rc, h = C.plan_measure_ext(dims, perm, elt, stream, tin.data_ptr(), tout.data_ptr())
@@ -245,6 +252,8 @@ def main(argv=None, checker="permute"):
     ap.add_argument("-nocheck", action="store_true")
     ap.add_argument("-method", type=int, default=None, choices=[0, 1, 2, 3, 4, 6, 7])
     ap.add_argument("-offset", type=int, default=0, help="byte offset of both device buffers")
+    ap.add_argument("-stages", type=int, default=None, help="with -method: shared-memory stages")
+    ap.add_argument("-threads", type=int, default=None, help="with -method: threads per block")
     args = ap.parse_args(argv)
     import torch
     import cutt_b200 as C
@@ -279,7 +288,8 @@ def main(argv=None, checker="permute"):
     failed = 0
     for dims, perm in cases:
         gbs, ok, plan = run_case(C, torch, list(dims), list(perm), args.elemsize, args.measure, buf_in, buf_out,
-                                 checker=checker, plantimer=args.plantimer, method=args.method, offset=args.offset)
+                                 checker=checker, plantimer=args.plantimer, method=args.method, offset=args.offset,
+                                 stages=args.stages, threads=args.threads)
         failed += 0 if ok else 1
         print("dims %s perm %s : %s GB/s %s  [%s]" % (list(dims), list(perm), " ".join("%.1f" % g for g in gbs),
                                                       "OK" if ok else "FAIL", plan))
