@@ -196,13 +196,16 @@ static void run_t2d_typed(const T2dDesc& D, const unsigned char* in, unsigned ch
     t2d_decode(D, tile, t);
     memset(stage, 0xEE, (size_t)D.nboxes * D.rowsAlloc * 128);
     const uint32_t nUnits = t2d_load_units(D), nItems = t2d_store_items(D);
-    for (uint32_t u = 0; u < nUnits; u++) {
-      if (LOAD == 1) t2d_load_shift<ELT>(D, t, stage, in, u);
-      else t2d_load_unit<ELT, (LOAD == 1 ? 16 : LOAD)>(D, t, stage, in, u);
+    // as the kernel: per-thread phases for the plain modes, unit / item loops for shift and shear
+    if (LOAD == 1) {
+      for (uint32_t u = 0; u < nUnits; u++) t2d_load_shift<ELT>(D, t, stage, in, u);
+    } else {
+      for (uint32_t tid = 0; tid < D.nthreads; tid++) t2d_load_rows<ELT, (LOAD == 1 ? 16 : LOAD)>(D, t, stage, in, tid);
     }
-    for (uint32_t it = 0; it < nItems; it++) {
-      if (STORE == 1) t2d_store_shear<ELT>(D, t, stage, out, it);
-      else t2d_store_item<ELT, (STORE == 1 ? 16 : STORE)>(D, t, stage, out, it);
+    if (STORE == 1) {
+      for (uint32_t it = 0; it < nItems; it++) t2d_store_shear<ELT>(D, t, stage, out, it);
+    } else {
+      for (uint32_t tid = 0; tid < D.nthreads; tid++) t2d_store_rows<ELT, (STORE == 1 ? 16 : STORE)>(D, t, stage, out, tid);
     }
   }
 }

@@ -881,6 +881,7 @@ bool build_t2d(const Problem& P, const TileParams& tp, const DeviceInfo& dev, Ca
   D.rowsLoad = tb + (D.storeMode == 1 ? 16 / elt - 1 : 0);
   D.rowsAlloc = D.storeMode == 1 ? tb + kT2dPadTop + kT2dPadBottom : tb;
   D.divRows = make_fastdiv(D.rowsLoad);
+  D.uprShift = ilog2_exact(D.nboxes * 8u * (16u / (D.loadMode == 1 ? 16u : D.loadMode)));
   D.inElems = P.inElems;
   D.order = tp.loopOrder ? 1 : 0;
   D.d0 = (uint32_t)P.d[0];

@@ -34,7 +34,7 @@ tile2d_kernel(const __grid_constant__ T2dDesc D, const unsigned char* __restrict
         if (ok[b]) t2d_shift_commit<ELT>(stage + soff[b], w[b], m[b]);
     }
   } else {
-    for (uint32_t u = tid; u < nUnits; u += blockDim.x) t2d_load_unit<ELT, (LOAD == 1 ? 16 : LOAD)>(D, t, stage, in, u);
+    t2d_load_rows<ELT, (LOAD == 1 ? 16 : LOAD)>(D, t, stage, in, tid);
     asm volatile("cp.async.commit_group;\n" ::: "memory");
     asm volatile("cp.async.wait_group 0;\n" ::: "memory");
   }
@@ -43,7 +43,7 @@ tile2d_kernel(const __grid_constant__ T2dDesc D, const unsigned char* __restrict
   if (STORE == 1) {
     for (uint32_t it = tid; it < nItems; it += blockDim.x) t2d_store_shear<ELT>(D, t, stage, out, it);
   } else {
-    for (uint32_t it = tid; it < nItems; it += blockDim.x) t2d_store_item<ELT, (STORE == 1 ? 16 : STORE)>(D, t, stage, out, it);
+    t2d_store_rows<ELT, (STORE == 1 ? 16 : STORE)>(D, t, stage, out, tid);
   }
 }
 

@@ -56,6 +56,7 @@ struct T2dDesc {
   uint32_t padTop;     // kT2dPadTop for sheared stores, else 0
   uint32_t rowsLoad;   // rows loaded per tile: tb, plus 16/elt - 1 rows above it for sheared stores
   uint32_t rowsAlloc;  // shared-memory rows per row block
+  uint32_t uprShift;   // log2(load units per tile row)
   uint32_t inMis;      // (input buffer address / elt) mod (16/elt); set when the kernel is launched
   uint32_t outMis;     // same for the output buffer
   uint32_t numTiles;
@@ -131,6 +132,36 @@ CUTT_HD void t2d_load_unit(const T2dDesc& D, const T2dTile& t, sptr_t stage, con
   const unsigned char* g = gin + (t.inOff + (int64_t)e0 + (int64_t)q * D.isP) * ELT;
   const uint32_t byteInRow = x * WIB;
   copy_g2s<WIB>(stage + t2d_smem_offset(D, k, (uint32_t)(q + (int32_t)D.padTop), byteInRow >> 4) + (byteInRow & 15u), g);
+}
+
+// The cp.async load phase of one thread: a thread keeps its place along dimension 0 and walks down
+// the rows of the tile, so everything but one pointer addition and the swizzled shared-memory offset
+// is computed once.
+template <int ELT, int WIB>
+CUTT_HD void t2d_load_rows(const T2dDesc& D, const T2dTile& t, sptr_t stage, const unsigned char* gin, uint32_t tid) {
+  constexpr uint32_t UPC = 16u / WIB;                   // units per 16-byte chunk
+  const uint32_t ux = tid & ((1u << D.uprShift) - 1u);  // unit along the tile row
+  const uint32_t ry = tid >> D.uprShift;                // first row of this thread
+  const uint32_t rstep = D.nthreads >> D.uprShift;      // rows per pass (a power of two)
+  const uint32_t e0 = ux * (WIB / ELT);
+  if (t.c0 + e0 >= D.d0) return;                        // (extents are multiples of the access width)
+  const uint32_t chunk = ux / UPC;
+  const uint32_t c8 = chunk & 7u;
+  const uint32_t sbase = (chunk >> 3) * (D.rowsAlloc * 128u) + (ux & (UPC - 1u)) * WIB;
+  const uint32_t pad = D.rowsLoad - D.tb;               // rows loaded above the tile
+  // rows whose position cp + rl - pad lies inside [0, dp)
+  const uint32_t rlo = t.cp >= pad ? 0u : pad - t.cp;
+  uint32_t rhi = D.dp - t.cp + pad;
+  if (rhi > D.rowsLoad) rhi = D.rowsLoad;
+  uint32_t rl = ry;
+  while (rl < rlo) rl += rstep;
+  const unsigned char* g = gin + (t.inOff + (int64_t)e0 + ((int64_t)rl - (int64_t)pad) * D.isP) * ELT;
+  const int64_t gstep = (int64_t)rstep * D.isP * ELT;
+  const uint32_t sdelta = D.padTop - pad;
+  for (; rl < rhi; rl += rstep, g += gstep) {
+    const uint32_t srow = rl + sdelta;
+    copy_g2s<WIB>(stage + sbase + srow * 128u + ((c8 ^ (srow & 7u)) << 4), g);
+  }
 }
 
 // global -> registers / registers -> shared, 16 bytes (plain loads and stores; range-checked on the host)
@@ -269,6 +300,17 @@ CUTT_HD void t2d_store_item(const T2dDesc& D, const T2dTile& t, sptr_t stage, un
     }
     g0 += os0B;
   }
+}
+
+// The plain store phase of one thread: the lane's chunk and row group are fixed, the warp walks
+// over the blocks of 32 items.
+template <int ELT, int WOB>
+CUTT_HD void t2d_store_rows(const T2dDesc& D, const T2dTile& t, sptr_t stage, unsigned char* gout, uint32_t tid) {
+  constexpr uint32_t NC = WOB / 4, NG = 128u / WOB;
+  const uint32_t lane = tid & 31u;
+  const uint32_t nblocks = ((D.ta * ELT / 16u) / NC) * (D.tb * ELT / 128u);
+  for (uint32_t ib = tid >> 5; ib < nblocks; ib += D.nthreads >> 5) t2d_store_item<ELT, WOB>(D, t, stage, gout, ib * 32u + lane);
+  (void)NG;
 }
 
 // One output row of a sheared item whose misalignment is MO elements: the aligned vector holds the
