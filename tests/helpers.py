@@ -27,7 +27,7 @@ TEST3_CASES = [
 # Streaming test of the reference (src/cutt_test.cpp:371-404).
 TEST4_CASE = ([24, 32, 16, 36, 43, 9], [5, 1, 4, 2, 3, 0])
 
-# README example (README.md:94-97) = BASELINE config 1.
+# README example of the original library (README.md:94-97).
 README_CASE = ([31, 549, 2, 3], [3, 0, 2, 1])
 
 
