@@ -56,6 +56,7 @@ struct Plan {
   // plans of the extension entry points (element sizes 1, 2, 16)
   int extBytes = 0;        // the caller's element size; 0 for ordinary plans
   SmallDesc small{};       // kMethodSmall
+  bool extSmallFallback = false;   // 2-byte tile2d plans: `small` is filled and serves unaligned buffers
 };
 
 struct CachedChoice {
@@ -226,6 +227,8 @@ cudaError_t run_plan(const Plan& p, const void* in, void* out, cudaStream_t stre
       return launch_rowcopy(p.cand.rc, p.numSM, in, out, stream);
     case kMethodT2d: {
       if (t2d_pointers_aligned(p.cand.t2d, in, out)) return launch_t2d(p.cand.t2d, in, out, stream);
+      if (p.extBytes && p.elt < 4) return p.extSmallFallback ? launch_small(p.small, in, out, stream)
+                                                             : launch_naive(p.naive, p.numSM, in, out, stream);
       if (p.haveFallback) {   // the same tile with element-sized accesses
         if (p.fallback.method == kMethodT2d) return launch_t2d(p.fallback.t2d, in, out, stream);
         PeerPtrs pp;
@@ -478,7 +481,16 @@ cuttResult make_plan(cuttHandle* handle, int rank, const int* dim, const int* pe
     p->method = kMethodMemcpy;
     ok = true;
   } else if (extSize && p->prob.elt < 4) {
-    p->method = build_small(p->prob, p->small) ? kMethodSmall : kMethodNaive;
+    // 2-byte elements whose output rows start on 16-byte boundaries: swizzled two-dimensional tiles
+    // with an 8 x 8 register transpose; everything else: the element-wise tiled kernel, which is
+    // also what such a plan falls back to on buffers that are not aligned for it
+    const bool haveSmall = build_small(p->prob, p->small);
+    Candidate c;
+    if (build_t2d_small(p->prob, dev, c) && adopt_candidate(*p, dev, c)) {
+      p->extSmallFallback = haveSmall;
+    } else {
+      p->method = haveSmall ? kMethodSmall : kMethodNaive;
+    }
     ok = true;
   } else if (p->mgMode == 1 && req.mode != kByModel && req.mode != kByMeasure && req.mode != kByIndex) {
     return CUTT_INVALID_PARAMETER;

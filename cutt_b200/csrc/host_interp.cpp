@@ -197,12 +197,14 @@ static void run_t2d_typed(const T2dDesc& D, const unsigned char* in, unsigned ch
     memset(stage, 0xEE, (size_t)D.nboxes * D.rowsAlloc * 128);
     const uint32_t nUnits = t2d_load_units(D), nItems = t2d_store_items(D);
     // as the kernel: per-thread phases for the plain modes, unit / item loops for shift and shear
-    if (LOAD == 1) {
+    if constexpr (LOAD == 1) {
       for (uint32_t u = 0; u < nUnits; u++) t2d_load_shift<ELT>(D, t, stage, in, u);
     } else {
       for (uint32_t tid = 0; tid < D.nthreads; tid++) t2d_load_rows<ELT, (LOAD == 1 ? 16 : LOAD)>(D, t, stage, in, tid);
     }
-    if (STORE == 1) {
+    if constexpr (ELT == 2) {
+      for (uint32_t tid = 0; tid < D.nthreads; tid++) t2d_store_rows_e2(D, t, stage, out, tid);
+    } else if constexpr (STORE == 1) {
       for (uint32_t it = 0; it < nItems; it++) t2d_store_shear<ELT>(D, t, stage, out, it);
     } else {
       for (uint32_t tid = 0; tid < D.nthreads; tid++) t2d_store_rows<ELT, (STORE == 1 ? 16 : STORE)>(D, t, stage, out, tid);
@@ -228,6 +230,7 @@ static int run_t2d(const Candidate& c, const unsigned char* in, size_t inBytes, 
   T2D_ROW(4, 16) T2D_ROW(4, 1) T2D_ROW(4, 8) T2D_ROW(4, 4)
   T2D_CASE(4, 16, 4) T2D_CASE(4, 1, 4) T2D_CASE(4, 8, 4) T2D_CASE(4, 4, 4)
   T2D_ROW(8, 16) T2D_ROW(8, 1) T2D_ROW(8, 8)
+  T2D_CASE(2, 16, 16) T2D_CASE(2, 8, 16) T2D_CASE(2, 4, 16)
 #undef T2D_ROW
 #undef T2D_CASE
   return 4;
@@ -338,6 +341,13 @@ int cutt_hostcheck_run_ext(int rank, const int* dim, const int* perm, int eltByt
   }
   if (P.elt < 4) {
     if (index > 0) return 3;
+    {   // as the library: 2-byte elements on aligned rows take the swizzled two-dimensional tiles
+      Candidate c;
+      if (build_t2d_small(P, g_dev, c) && (uintptr_t)in % c.t2d.loadMode == 0 && (uintptr_t)out % 16 == 0) {
+        if (label && labelLen > 0) snprintf(label, labelLen, "%s", c.label.c_str());
+        return run_t2d(c, (const unsigned char*)in, bytes, (unsigned char*)out, (unsigned char*)out, (unsigned char*)out + bytes);
+      }
+    }
     SmallDesc S;
     if (!build_small(P, S)) return 5;
     if (label && labelLen > 0)

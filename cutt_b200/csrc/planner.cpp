@@ -836,7 +836,7 @@ bool build_tma(const Problem& P, const TileParams& tp, const DeviceInfo& dev, Ca
 bool build_t2d(const Problem& P, const TileParams& tp, const DeviceInfo& dev, Candidate& out) {
   const int r = P.rank;
   const int elt = P.elt;
-  if (elt != 4 && elt != 8) return false;
+  if (elt != 4 && elt != 8 && elt != 2) return false;
   if (r < 2 || r > kT2dMaxOuter + 2 || P.peerDim >= 0 || P.identity) return false;
   if (P.is[0] != 1) return false;
   int p = 0;
@@ -877,6 +877,9 @@ bool build_t2d(const Problem& P, const TileParams& tp, const DeviceInfo& dev, Ca
   D.loadMode = width(true);
   D.storeMode = width(false);
   if (tp.extend) D.loadMode = D.storeMode = 1;
+  // 2-byte elements: cp.async moves at least 4 bytes, and the 8 x 8 register transpose writes
+  // 16-byte vectors only
+  if (elt == 2 && (tp.extend || D.loadMode < 4 || D.storeMode != 16)) return false;
   D.padTop = D.storeMode == 1 ? kT2dPadTop : 0;
   D.rowsLoad = tb + (D.storeMode == 1 ? 16 / elt - 1 : 0);
   D.rowsAlloc = D.storeMode == 1 ? tb + kT2dPadTop + kT2dPadBottom : tb;
@@ -926,6 +929,19 @@ bool build_t2d(const Problem& P, const TileParams& tp, const DeviceInfo& dev, Ca
            out.smemBytes, D.numTiles);
   out.label = buf;
   return true;
+}
+
+bool build_t2d_small(const Problem& P, const DeviceInfo& dev, Candidate& out) {
+  if (P.elt != 2) return false;
+  TileParams tp;
+  tp.tinBytes = 256;          // 128 elements along dimension 0 (two row blocks) ...
+  tp.toutBytes = 64 * 2;      // ... by 64 along the output's fastest dimension: 16 KB
+  tp.stages = 1;
+  tp.nthreads = 256;
+  tp.loopOrder = 1;
+  if (build_t2d(P, tp, dev, out)) return true;
+  tp.tinBytes = 128;
+  return build_t2d(P, tp, dev, out);
 }
 
 std::vector<Candidate> enumerate_candidates(const Problem& P, const DeviceInfo& dev) {

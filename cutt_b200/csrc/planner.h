@@ -148,6 +148,10 @@ bool build_tma(const Problem& P, const TileParams& tp, const DeviceInfo& dev, Ca
 // (any buffer alignment).  False outside the class.
 bool build_t2d(const Problem& P, const TileParams& tp, const DeviceInfo& dev, Candidate& out);
 
+// The tile2d candidate the extension entry points use for 2-byte elements (rows of the output on
+// 16-byte boundaries, rows of the input on at least 4-byte boundaries); false if not applicable.
+bool build_t2d_small(const Problem& P, const DeviceInfo& dev, Candidate& out);
+
 // Row-copy candidate for problems whose fastest dimension is kept; false if not applicable.
 bool build_rowcopy(const Problem& P, const DeviceInfo& dev, Candidate& out);
 

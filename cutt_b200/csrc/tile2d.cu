@@ -18,7 +18,7 @@ tile2d_kernel(const __grid_constant__ T2dDesc D, const unsigned char* __restrict
   t2d_decode(D, blockIdx.x, t);
   const uint32_t stage = (uint32_t)__cvta_generic_to_shared(t2d_smem);
   const uint32_t nUnits = t2d_load_units(D);
-  if (LOAD == 1) {
+  if constexpr (LOAD == 1) {
     // four units per thread at a time: eight global loads in flight before the first is consumed
     constexpr int B = 4;
     for (uint32_t u0 = tid; u0 < nUnits; u0 += B * blockDim.x) {
@@ -40,8 +40,10 @@ tile2d_kernel(const __grid_constant__ T2dDesc D, const unsigned char* __restrict
   }
   __syncthreads();
   const uint32_t nItems = t2d_store_items(D);
-  if (STORE == 1) {
+  if constexpr (STORE == 1) {
     for (uint32_t it = tid; it < nItems; it += blockDim.x) t2d_store_shear<ELT>(D, t, stage, out, it);
+  } else if constexpr (ELT == 2) {
+    t2d_store_rows_e2(D, t, stage, out, tid);
   } else {
     t2d_store_rows<ELT, (STORE == 1 ? 16 : STORE)>(D, t, stage, out, tid);
   }
@@ -55,6 +57,7 @@ static T2dKernel pick_t2d(const T2dDesc& D) {
   T2D_ROW(4, 16) T2D_ROW(4, 1) T2D_ROW(4, 8) T2D_ROW(4, 4)
   T2D_CASE(4, 16, 4) T2D_CASE(4, 1, 4) T2D_CASE(4, 8, 4) T2D_CASE(4, 4, 4)
   T2D_ROW(8, 16) T2D_ROW(8, 1) T2D_ROW(8, 8)
+  T2D_CASE(2, 16, 16) T2D_CASE(2, 8, 16) T2D_CASE(2, 4, 16)   // 2-byte elements: extension entry points
 #undef T2D_ROW
 #undef T2D_CASE
   return nullptr;

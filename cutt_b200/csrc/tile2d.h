@@ -313,6 +313,50 @@ CUTT_HD void t2d_store_rows(const T2dDesc& D, const T2dTile& t, sptr_t stage, un
   (void)NG;
 }
 
+// 2-byte elements (the extension entry points): a 16-byte chunk holds 8 elements, i.e. 8 output rows,
+// so an item is 8 rows x one chunk: 8 shared vector loads, an 8 x 8 transpose of 16-bit values with
+// one byte-permute per output word, 8 global stores of 16 bytes.  The 8 lanes of a quarter warp take
+// the 8 chunks of one shared-memory row (conflict free), the 4 quarters take 4 row groups: every
+// store instruction writes 8 output rows x 64 contiguous bytes.  Output rows must start on 16-byte
+// boundaries (store mode 16).
+CUTT_HD uint32_t t2d_pack16(uint32_t a, uint32_t b, bool high) {
+#if defined(__CUDA_ARCH__)
+  return high ? __byte_perm(a, b, 0x7632) : __byte_perm(a, b, 0x5410);
+#else
+  return high ? ((a >> 16) | (b & 0xffff0000u)) : ((a & 0xffffu) | (b << 16));
+#endif
+}
+
+CUTT_HD void t2d_store_rows_e2(const T2dDesc& D, const T2dTile& t, sptr_t stage, unsigned char* gout, uint32_t tid) {
+  const uint32_t lane = tid & 31u;
+  const uint32_t cl = lane & 7u, g = lane >> 3;
+  const uint32_t gblocks = D.tb >> 5;                    // blocks of 4 groups x 8 rows
+  const uint32_t nblocks = D.nboxes * gblocks;
+  const int64_t os0B = D.os0 * 2;
+  for (uint32_t ib = tid >> 5; ib < nblocks; ib += D.nthreads >> 5) {
+    const uint32_t cb = ib & (D.nboxes - 1u);            // (nboxes is 1 or 2)
+    const uint32_t gb = ib / D.nboxes;
+    const uint32_t chunk = cb * 8u + cl;
+    const uint32_t row0 = (gb * 4u + g) * 8u;
+    const uint32_t r0 = t.c0 + chunk * 8u;
+    if (r0 >= D.d0 || t.cp + row0 >= D.dp) continue;     // (dp is a multiple of 8: whole vectors)
+    uint32_t x[8][4];
+#pragma unroll
+    for (int i = 0; i < 8; i++) lds<16>(x[i], stage + t2d_smem_offset(D, cb, row0 + (uint32_t)i + D.padTop, cl));
+    unsigned char* g0 = gout + (t.outOff + (int64_t)(chunk * 8u) * D.os0 + (int64_t)row0) * 2;
+#pragma unroll
+    for (int j = 0; j < 8; j++) {
+      if (r0 + (uint32_t)j < D.d0) {
+        uint32_t y[4];
+#pragma unroll
+        for (int w = 0; w < 4; w++) y[w] = t2d_pack16(x[2 * w][j >> 1], x[2 * w + 1][j >> 1], (j & 1) != 0);
+        stg<16>(g0, y);
+      }
+      g0 += os0B;
+    }
+  }
+}
+
 // One output row of a sheared item whose misalignment is MO elements: the aligned vector holds the
 // elements of shared rows (V-1) - MO + i, i < V.  pos0: position along p of its first element.
 template <int ELT, int MO>

@@ -140,3 +140,23 @@ def test_rejects_what_it_cannot_do(native):
         assert native.cuttExecute(h, buf.data_ptr(), buf.data_ptr()) == bad   # in place
     finally:
         native.cuttDestroy(h)
+
+
+def test_two_byte_elements_on_swizzled_tiles(native, oracle_mod):
+    """2-byte elements with output rows on 16-byte boundaries run on the two-dimensional tile kernel
+    (8 x 8 register transpose); the same plans on buffers shifted by 2 bytes fall back to the
+    element-wise kernel; shapes outside the class never leave it."""
+    cases = [([64, 72], [1, 0]), ([136, 200], [1, 0]), ([36, 264], [1, 0]), ([34, 8, 40], [2, 1, 0]),
+             ([130, 3, 5, 48], [3, 0, 2, 1]), ([72, 6, 136], [1, 2, 0]), ([2000, 2008], [1, 0]), ([1032, 7, 520], [2, 1, 0]),
+             ([64, 70], [1, 0]), ([33, 72], [1, 0])]
+    kinds = {}
+    for dims, perm in cases:
+        raw = raw_bytes(volume(dims) * 2, 77)
+        want = expected(oracle_mod, dims, perm, 2, raw)
+        for planner in ("plan", "measure"):
+            for offset in (0, 2, 16):
+                got, desc = run_ext(native, dims, perm, 2, raw, planner=planner, offset=offset)
+                assert np.array_equal(got, want), (dims, perm, planner, offset, desc)
+        kinds[tuple(dims)] = desc
+    assert "t2d " in kinds[(64, 72)] and "t2d " in kinds[(2000, 2008)] and "t2d " in kinds[(34, 8, 40)]
+    assert "small" in kinds[(64, 70)] and "small" in kinds[(33, 72)]

@@ -407,3 +407,28 @@ def test_two_dimensional_tiles_modes_and_rejections(hc):
     assert label([64, 64], [0, 1], 4)[0] == 2                    # identity
     assert label([8, 64], [1, 0], 4)[0] == 2                     # 32-byte rows: mostly padding
     assert label([64, 8], [1, 0], 4)[0] == 2
+
+
+def test_two_byte_elements_on_swizzled_tiles(hc, oracle_mod):
+    """2-byte elements whose output rows start on 16-byte boundaries take the two-dimensional tile
+    method with its 8 x 8 register transpose (input rows on 16-, 8- or 4-byte boundaries); other
+    shapes stay on the element-wise kernel."""
+    hc.cutt_hostcheck_run_ext.argtypes = [ctypes.c_int, ctypes.POINTER(ctypes.c_int), ctypes.POINTER(ctypes.c_int),
+                                          ctypes.c_int, ctypes.c_int, ctypes.c_void_p, ctypes.c_void_p,
+                                          ctypes.c_char_p, ctypes.c_int]
+    seen = set()
+    cases = [([64, 72], [1, 0]), ([136, 200], [1, 0]), ([36, 264], [1, 0]), ([34, 8, 40], [2, 1, 0]), ([130, 3, 5, 48], [3, 0, 2, 1]),
+             ([72, 6, 136], [1, 2, 0]), ([200, 3, 24], [2, 0, 1]), ([64, 70], [1, 0]), ([33, 72], [1, 0])]
+    for dims, perm in cases:
+        raw = np.random.default_rng(volume(dims)).integers(0, 65536, volume(dims), dtype=np.uint16)
+        want = oracle_mod.transpose_numpy(dims, perm, raw)
+        out = np.full_like(raw, 0xEEEE)
+        lab = ctypes.create_string_buffer(4096)
+        rc = hc.cutt_hostcheck_run_ext(len(dims), _iarr(dims), _iarr(perm), 2, 0, raw.ctypes.data, out.ctypes.data, lab, 4096)
+        assert rc == 0, (rc, dims, perm)
+        assert np.array_equal(out, want), (dims, perm, lab.value.decode())
+        seen.add((tuple(dims), lab.value.decode().split(" ")[0]))
+    assert ((64, 72), "t2d") in seen and ((136, 200), "t2d") in seen and ((36, 264), "t2d") in seen
+    assert ((34, 8, 40), "t2d") in seen                     # input rows on 4-byte boundaries
+    assert ((64, 70), "small") in seen                      # output rows of 140 bytes: not 16-byte aligned
+    assert ((33, 72), "small") in seen                      # input rows on 2-byte boundaries
