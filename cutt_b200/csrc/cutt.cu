@@ -382,7 +382,7 @@ bool valid_tile_params(const TileParams& t, Method method = kMethodTiles) {
   if (method == kMethodTma ? (t.stages < 1 || t.stages > kTmaMaxStages) : (t.stages != 1 && t.stages != 2)) return false;
   return one_of(t.nthreads, {64, 128, 256, 512}) &&
          one_of(t.maxVecBytes, {4, 8, 16}) && one_of(t.maxVBytes, {4, 8, 16}) &&
-         one_of(t.extend, {0, 1}) && one_of(t.loopOrder, {0, 1}) && one_of(t.groupIn, {1, 2, 4}) &&
+         one_of(t.extend, {0, 1}) && one_of(t.loopOrder, {0, 1, 2, 3}) && one_of(t.groupIn, {1, 2, 4}) &&
          one_of(t.groupOut, {1, 2, 4}) && one_of(t.cutInRun, {0, 1}) && one_of(t.allowAof, {0, 1}) &&
          one_of(t.oneTilePerBlock, {0, 1}) && one_of(t.peerOrder, {0, 1}) && t.tinBytes >= 4 && t.tinBytes <= (1u << 16) &&
          t.toutBytes >= 4 && t.toutBytes <= (1u << 16) && t.vtargetBytes >= 4 && t.vtargetBytes <= (1u << 20);

@@ -193,7 +193,7 @@ template <int ELT, int LOAD, int STORE>
 static void run_t2d_typed(const T2dDesc& D, const unsigned char* in, unsigned char* out, unsigned char* stage) {
   for (uint32_t tile = 0; tile < D.numTiles; tile++) {
     T2dTile t;
-    t2d_decode(D, tile, t);
+    if (!t2d_decode(D, tile, t)) continue;
     memset(stage, 0xEE, (size_t)D.nboxes * D.rowsAlloc * 128);
     const uint32_t nUnits = t2d_load_units(D), nItems = t2d_store_items(D);
     // as the kernel: per-thread phases for the plain modes, unit / item loops for shift and shear

@@ -886,18 +886,22 @@ bool build_t2d(const Problem& P, const TileParams& tp, const DeviceInfo& dev, Ca
   D.divRows = make_fastdiv(D.rowsLoad);
   D.uprShift = ilog2_exact(D.nboxes * 8u * (16u / (D.loadMode == 1 ? 16u : D.loadMode)));
   D.inElems = P.inElems;
-  D.order = tp.loopOrder ? 1 : 0;
+  if (tp.loopOrder < 0 || tp.loopOrder > 3) return false;
+  D.order = (uint32_t)tp.loopOrder;
   D.d0 = (uint32_t)P.d[0];
   D.dp = (uint32_t)P.d[p];
   D.nA = (uint32_t)ceil_div(P.d[0], ta);
   D.nB = (uint32_t)ceil_div(P.d[p], tb);
   D.divA = make_fastdiv(D.nA);
   D.divB = make_fastdiv(D.nB);
+  D.nBand = (uint32_t)ceil_div(D.order == 2 ? D.nA : D.nB, 4);
+  D.divBand = make_fastdiv(D.nBand ? D.nBand : 1);
+  if (D.order >= 2 && (D.order == 2 ? D.nA : D.nB) < 8) return false;   // bands need a few tiles across
   D.isP = P.is[p];
   D.os0 = P.os[0];
   D.inBase = P.inBase;
   D.outBase = P.outBase;
-  int64_t ntiles = (int64_t)D.nA * D.nB;
+  int64_t ntiles = D.order == 2 ? (int64_t)D.nBand * 4 * D.nB : (D.order == 3 ? (int64_t)D.nBand * 4 * D.nA : (int64_t)D.nA * D.nB);
   for (int j = 1; j < r; j++) {
     if (j == p) continue;
     const uint32_t k = D.nOuter++;
@@ -1044,7 +1048,7 @@ std::vector<Candidate> enumerate_candidates(const Problem& P, const DeviceInfo& 
     const uint32_t ta[] = {128, 256}, tbE[] = {32, 64};
     for (uint32_t a : ta)
       for (uint32_t b : tbE)
-        for (int lo = 0; lo < 2; lo++)
+        for (int lo = 0; lo < 4; lo++)
           for (int nt = 128; nt <= 256; nt *= 2) {
             if (nt == 256 && a * b <= 128 * 32) continue;   // 4 KB tiles: 128 threads are enough
             TileParams tp;
@@ -1054,7 +1058,7 @@ std::vector<Candidate> enumerate_candidates(const Problem& P, const DeviceInfo& 
             // (rows on 4-byte boundaries: measured 3.6-4.1 TB/s against 4.4-5.7 TB/s for the general
             // kernel's over-fetching loads - not worth a measurement slot)
             if (build_t2d(P, tp, dev, c) && c.t2d.loadMode >= 8 && c.t2d.storeMode >= 8) res.push_back(c);
-            if (dev.tmaLoads && build_tma(P, tp, dev, c)) res.push_back(c);
+            if (lo < 2 && dev.tmaLoads && build_tma(P, tp, dev, c)) res.push_back(c);
           }
   }
   std::stable_sort(res.begin(), res.end(), [](const Candidate& a, const Candidate& b) { return a.cost < b.cost; });

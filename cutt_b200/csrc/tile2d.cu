@@ -15,7 +15,7 @@ tile2d_kernel(const __grid_constant__ T2dDesc D, const unsigned char* __restrict
   const uint32_t tid = threadIdx.x;
   if (blockIdx.x >= D.numTiles) return;
   T2dTile t;
-  t2d_decode(D, blockIdx.x, t);
+  if (!t2d_decode(D, blockIdx.x, t)) return;
   const uint32_t stage = (uint32_t)__cvta_generic_to_shared(t2d_smem);
   const uint32_t nUnits = t2d_load_units(D);
   if constexpr (LOAD == 1) {

@@ -60,13 +60,16 @@ struct T2dDesc {
   uint32_t inMis;      // (input buffer address / elt) mod (16/elt); set when the kernel is launched
   uint32_t outMis;     // same for the output buffer
   uint32_t numTiles;
-  uint32_t order;      // tile index runs fastest along 0: dimension 0, 1: dimension p
+  uint32_t order;      // tile index runs fastest along 0: dimension 0, 1: dimension p; 2 / 3: as 1 / 0,
+                       // but in bands of four tiles across the other dimension (blocks that run at the
+                       // same time then share lines on BOTH sides); tile indices past the end of a
+                       // band are empty
   uint32_t d0, dp;
   uint32_t nA, nB;
   uint32_t nOuter;
   uint32_t nO[kT2dMaxOuter];
-  uint32_t pad_;
-  FastDiv divA, divB, divRows, divO[kT2dMaxOuter];
+  uint32_t nBand;      // orders 2 / 3: bands of four tiles along dimension 0 / p
+  FastDiv divA, divB, divBand, divRows, divO[kT2dMaxOuter];
   int64_t isP;         // input stride of dimension p (elements)
   int64_t os0;         // output stride of dimension 0 (elements)
   int64_t isO[kT2dMaxOuter], osO[kT2dMaxOuter];
@@ -79,14 +82,25 @@ struct T2dTile {
   int64_t inOff, outOff;   // offsets of the tile origin (elements)
 };
 
-CUTT_HD void t2d_decode(const T2dDesc& D, uint32_t tile, T2dTile& t) {
+// false: the tile index names no tile (bands of the orders 2 and 3 are padded to a multiple of four)
+CUTT_HD bool t2d_decode(const T2dDesc& D, uint32_t tile, T2dTile& t) {
   uint32_t id = tile, a, b;
   if (D.order == 0) {
     uint32_t q = fdiv(id, D.divA); a = id - q * D.nA; id = q;
     q = fdiv(id, D.divB); b = id - q * D.nB; id = q;
-  } else {
+  } else if (D.order == 1) {
     uint32_t q = fdiv(id, D.divB); b = id - q * D.nB; id = q;
     q = fdiv(id, D.divA); a = id - q * D.nA; id = q;
+  } else if (D.order == 2) {   // four tiles along dimension 0, then along p, then the bands of dimension 0
+    const uint32_t lo = id & 3u; id >>= 2;
+    uint32_t q = fdiv(id, D.divB); b = id - q * D.nB; id = q;
+    q = fdiv(id, D.divBand); a = (id - q * D.nBand) * 4u + lo; id = q;
+    if (a >= D.nA) return false;
+  } else {                     // four tiles along p, then along dimension 0, then the bands of p
+    const uint32_t lo = id & 3u; id >>= 2;
+    uint32_t q = fdiv(id, D.divA); a = id - q * D.nA; id = q;
+    q = fdiv(id, D.divBand); b = (id - q * D.nBand) * 4u + lo; id = q;
+    if (b >= D.nB) return false;
   }
   t.c0 = a * D.ta;
   t.cp = b * D.tb;
@@ -99,6 +113,7 @@ CUTT_HD void t2d_decode(const T2dDesc& D, uint32_t tile, T2dTile& t) {
     t.inOff += (int64_t)c * D.isO[k];
     t.outOff += (int64_t)c * D.osO[k];
   }
+  return true;
 }
 
 // Shared-memory byte offset of chunk c8 (0..7) of shared-memory row `srow` in row block k.

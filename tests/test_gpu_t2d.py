@@ -25,7 +25,13 @@ def test_forced_tile_shapes_and_widths(native, oracle_mod, dims, perm):
         want = oracle_mod.transpose_blocked(dims, perm, a)
         for ta in (128, 256):
             for tb in (32, 64):
-                for kw in (dict(nthreads=128, loop_order=0), dict(nthreads=256, loop_order=1)):
+                for kw in (dict(nthreads=128, loop_order=0), dict(nthreads=256, loop_order=1), dict(nthreads=128, loop_order=2),
+                           dict(nthreads=256, loop_order=3)):
+                    rc, h = native.plan_params(dims, perm, elt, 0, method=7, tin=ta, tout=tb * elt, stages=1, **kw)
+                    if rc == native.CUTT_INVALID_PARAMETER and kw["loop_order"] >= 2:
+                        continue      # banded orders need at least 8 tiles across the band dimension
+                    assert rc == 0
+                    native.cuttDestroy(h)
                     for maxvec, force in ((16, 0), (16, 1), (8, 0), (4, 0)):
                         if maxvec < elt:
                             continue

@@ -320,7 +320,7 @@ def _t2d(hc):
 
 
 T2D_SHAPES = [
-    ([64, 64], [1, 0]), ([129, 130], [1, 0]), ([131, 67], [1, 0]), ([66, 202], [1, 0]), ([132, 200], [1, 0]),
+    ([300, 530], [1, 0]), ([1030, 9, 260], [2, 1, 0]), ([64, 64], [1, 0]), ([129, 130], [1, 0]), ([131, 67], [1, 0]), ([66, 202], [1, 0]), ([132, 200], [1, 0]),
     ([36, 8, 44], [2, 1, 0]), ([41, 6, 53], [1, 2, 0]), ([72, 3, 5, 57], [3, 0, 2, 1]), ([25, 4, 3, 2, 40], [4, 2, 0, 3, 1]),
     ([30, 2, 3, 2, 2, 3, 2, 34], [7, 6, 5, 4, 3, 2, 1, 0]), ([16, 10, 36], [2, 0, 1]), ([250, 3, 18], [2, 1, 0]),
     ([63, 65], [1, 0]), ([97, 16], [1, 0]),
@@ -341,7 +341,7 @@ def test_two_dimensional_tiles(hc, oracle_mod, dims, perm):
         want = oracle_mod.transpose_blocked(dims, perm, a)
         for ta in (128, 256):
             for tb in (32, 64):
-                for order, nt in ((0, 128), (1, 256)):
+                for order, nt in ((0, 128), (1, 256), (2, 128), (3, 256)):
                     for maxvec, force in ((16, 0), (16, 1), (8, 0), (4, 0)):
                         if maxvec < elt:
                             continue
@@ -349,6 +349,8 @@ def test_two_dimensional_tiles(hc, oracle_mod, dims, perm):
                         lab = ctypes.create_string_buffer(2048)
                         rc = run(len(dims), _iarr(dims), _iarr(perm), elt, ta, tb, nt, order, maxvec, force,
                                  a.ctypes.data, out.ctypes.data, lab, 2048)
+                        if rc == 2 and order >= 2:
+                            continue          # banded orders need at least 8 tiles across the band dimension
                         assert rc == 0, (rc, dims, perm, elt, ta, tb, maxvec, force)
                         label = json.loads(lab.value.decode())["label"]
                         assert np.array_equal(out, want), (dims, perm, elt, label)
