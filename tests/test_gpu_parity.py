@@ -158,6 +158,24 @@ def test_identity_copy_unaligned(native):
     assert native.copy_timeouts() == 0
 
 
+def test_identity_copy_equally_misaligned(native):
+    """Both buffers miss a 16-byte boundary by the same number of words: a head of one to three
+    words, then the aligned body (large enough for the bulk copy engine) and a tail."""
+    import torch
+    for off in (1, 2, 3):
+        n = 9_000_003
+        src = torch.arange(n + 8, dtype=torch.int32, device="cuda")
+        dst = torch.full((n + 8,), -1, dtype=torch.int32, device="cuda")
+        rc, h = native.plan_params([n // 3, 3], [0, 1], 4, method=0)
+        assert rc == 0
+        assert native.cuttExecute(h, src.data_ptr() + 4 * off, dst.data_ptr() + 4 * off) == 0
+        torch.cuda.synchronize()
+        native.cuttDestroy(h)
+        assert torch.equal(dst[off:off + n], src[off:off + n])
+        assert bool((dst[:off] == -1).all()) and bool((dst[off + n:] == -1).all())
+        assert native.copy_timeouts() == 0
+
+
 def test_streams(native, oracle_mod):
     """Ten plans on ten streams, all writing the same output (src/cutt_test.cpp:371-404)."""
     import torch
