@@ -129,8 +129,8 @@ def _cpu_sample_cases(args):
             dims[2] = max(1, dims[2] // args.c5_scale)
         perm = W.C5A_PERM if w == "c5a" else W.C5B_PERM
         return [(w + "_sample", dims, perm, 4)], \
-            "the same permutation on a slab of 8 positions of the sharded dimension, dims %s (%.2f GB per side)" \
-            % (dims, _vol(dims) * 4 / 1e9)
+            "the same permutation on a slab of %d positions of the sharded dimension, dims %s (%.2f GB per side)" \
+            % (dims[3], dims, _vol(dims) * 4 / 1e9)
     if w == "c3":
         cases = []
         for i, (d, p) in enumerate(W.c3_cases(4)):

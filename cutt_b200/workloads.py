@@ -76,8 +76,8 @@ def c3_holdout_cases(n: int = 100):
 
 
 # Bounded sample of the multi-GPU tensor for legs that run on the host cores or through host
-# buffers: the same permutation on a slab of 8 positions of the sharded dimension (1.07 GB per side).
-C5_SAMPLE_DIMS = [1024, 1024, 32, 8]
+# buffers: the same permutation on a slab of 32 positions of the sharded dimension (4.29 GB per side).
+C5_SAMPLE_DIMS = [1024, 1024, 32, 32]
 
 
 def write_c3_file(n: int = 100):
