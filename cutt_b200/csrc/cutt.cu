@@ -177,6 +177,9 @@ void fill_naive(Plan& p, int rank, const int* dim, const int* perm) {
   for (int i = 0; i < rank; i++) { is[i] = acc; acc *= (unsigned long long)dim[i]; }
   n.volume = acc;
   for (int k = 0; k < rank; k++) { n.odim[k] = dim[perm[k]]; n.istride[k] = is[perm[k]]; }
+  n.narrow = acc < (1ull << 31) ? 1 : 0;
+  if (n.narrow)
+    for (int k = 0; k < rank; k++) n.div[k] = make_fastdiv((uint32_t)n.odim[k]);
 }
 
 // Occupancy-based grid for a tiled candidate; false if the kernel cannot be configured.
@@ -357,6 +360,10 @@ const std::vector<Candidate>& enumerate_cached(const std::string& key, const Pro
 
 enum PlanMode { kByModel, kByMeasure, kByIndex, kByParams };
 
+// Largest tensor (bytes per side) for which the element-per-thread kernel is a candidate of
+// cuttPlan; cuttPlanMeasure, which times it, lets it compete up to eight times that.
+constexpr size_t kNaiveCandidateBytes = (size_t)1 << 20;
+
 struct PlanRequest {
   PlanMode mode = kByModel;
   void* idata = nullptr;
@@ -522,7 +529,23 @@ cuttResult make_plan(cuttHandle* handle, int rank, const int* dim, const int* pe
     }
   } else {
     // (a copy: the cached list may be replaced by another thread while this one measures)
-    const std::vector<Candidate> cands = enumerate_cached(key, p->prob, dev);
+    std::vector<Candidate> cands = enumerate_cached(key, p->prob, dev);
+    if (!cands.empty() && req.world == 0 && req.chunkLast == 0 && !extSize && !p->prob.identity &&
+        (req.mode == kByModel || req.mode == kByMeasure) &&
+        p->bytes <= (req.mode == kByMeasure ? 8 * kNaiveCandidateBytes : kNaiveCandidateBytes) &&
+        !env_flag("CUTT_NO_NAIVE_CANDIDATE")) {
+      // tensors this small stay in the L2 cache and their time is launch plus one round trip to
+      // memory: one thread per element, no shared-memory stage, competes (measured on B200 over
+      // thirty shapes of 0.1-1 MB: 3.5-3.6 us per launch, the rate at which launches issue, against
+      // 4.0-6.2 us for the model's first tiled plan; (31,549,2,3) perm (3,0,2,1): 3.6 against 6.2)
+      Candidate nv;
+      nv.method = kMethodNaive;
+      nv.label = "naive";
+      nv.cost = 4.0e-6 + 2.0 * (double)p->bytes / 1.5e12;
+      size_t at = 0;
+      while (at < cands.size() && cands[at].cost <= nv.cost) at++;
+      cands.insert(cands.begin() + at, nv);
+    }
     if (cands.empty()) {
       if (p->mgMode >= 1) return CUTT_INTERNAL_ERROR;  // no element-wise fallback for these
       p->method = kMethodNaive;
@@ -555,6 +578,10 @@ cuttResult make_plan(cuttHandle* handle, int rank, const int* dim, const int* pe
         } else if (cc.method == kMethodCopy || cc.method == kMethodMemcpy) {
           ok = p->prob.identity;
           if (ok) p->method = cc.method;
+        } else if (cc.method == kMethodNaive) {
+          ok = req.world == 0 && req.chunkLast == 0 && !extSize && !p->prob.identity &&
+               p->bytes <= 8 * kNaiveCandidateBytes;
+          if (ok) p->method = kMethodNaive;
         }
         if (ok) p->note = "cache";
         if (ok && req.mode == kByMeasure) {
@@ -1230,9 +1257,10 @@ int cutt_c_plan_cache_load(const char* path) {
                &t.loopOrder, &t.groupIn, &t.groupOut, &t.cutInRun, &t.allowAof, &t.oneTilePerBlock,
                &t.peerOrder) != 17)
       continue;
-    // winners are tiled plans, row copies or (identity permutations) the two copy methods
+    // winners are tiled plans, row copies, the element-per-thread kernel (small tensors) or, for
+    // identity permutations, the two copy methods
     if (method != kMethodTiles && method != kMethodRowCopy && method != kMethodCopy && method != kMethodMemcpy &&
-        method != kMethodTma && method != kMethodT2d)
+        method != kMethodTma && method != kMethodT2d && method != kMethodNaive)
       continue;
     if ((method == kMethodTiles || method == kMethodTma || method == kMethodT2d) && !valid_tile_params(t, (Method)method))
       continue;

@@ -289,12 +289,37 @@ naive_kernel(const __grid_constant__ NaiveDesc d, const T* __restrict__ in, T* _
   }
 }
 
+// the same with 32-bit indices (volume < 2^31, so neither an offset nor the loop counter wraps)
+template <typename T>
+__global__ void __launch_bounds__(256)
+naive32_kernel(const __grid_constant__ NaiveDesc d, const T* __restrict__ in, T* __restrict__ out) {
+  const uint32_t n = (uint32_t)d.volume;
+  const uint32_t stride = gridDim.x * blockDim.x;
+  for (uint32_t o = blockIdx.x * blockDim.x + threadIdx.x; o < n; o += stride) {
+    uint32_t rem = o, src = 0;
+    for (int k = 0; k < d.rank; k++) {
+      const uint32_t q = fdiv(rem, d.div[k]);
+      src += (rem - q * (uint32_t)d.odim[k]) * (uint32_t)d.istride[k];
+      rem = q;
+    }
+    out[o] = in[src];
+  }
+}
+
 cudaError_t launch_naive(const NaiveDesc& d, int numSM, const void* in, void* out, cudaStream_t stream) {
   const int threads = 256;
   unsigned long long want = (d.volume + threads - 1) / threads;
   const unsigned long long cap = (unsigned long long)(numSM > 0 ? numSM : 1) * 16;
   int grid = (int)(want < cap ? want : cap);
   if (grid < 1) grid = 1;
+  if (d.narrow) {
+    if (d.elt == 4) naive32_kernel<uint32_t><<<grid, threads, 0, stream>>>(d, (const uint32_t*)in, (uint32_t*)out);
+    else if (d.elt == 2) naive32_kernel<uint16_t><<<grid, threads, 0, stream>>>(d, (const uint16_t*)in, (uint16_t*)out);
+    else if (d.elt == 1) naive32_kernel<uint8_t><<<grid, threads, 0, stream>>>(d, (const uint8_t*)in, (uint8_t*)out);
+    else naive32_kernel<unsigned long long><<<grid, threads, 0, stream>>>(d, (const unsigned long long*)in, (unsigned long long*)out);
+    g_launches++;
+    return cudaGetLastError();
+  }
   if (d.elt == 4) naive_kernel<uint32_t><<<grid, threads, 0, stream>>>(d, (const uint32_t*)in, (uint32_t*)out);
   else if (d.elt == 2) naive_kernel<uint16_t><<<grid, threads, 0, stream>>>(d, (const uint16_t*)in, (uint16_t*)out);
   else if (d.elt == 1) naive_kernel<uint8_t><<<grid, threads, 0, stream>>>(d, (const uint8_t*)in, (uint8_t*)out);

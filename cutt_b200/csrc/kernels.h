@@ -10,13 +10,16 @@ struct PeerPtrs {
   unsigned char* p[kMaxPeers];
 };
 
-// One thread per output element; any rank up to 32.  Fallback and cross-check.
+// One thread per output element; any rank up to 32.  Fallback, cross-check, and the quickest way
+// through tensors of a few hundred kilobytes, whose time is launch and one memory round trip.
 struct NaiveDesc {
   int rank;
   int elt;
   unsigned long long volume;
   unsigned long long odim[32];     // extents in output order
   unsigned long long istride[32];  // input stride of the k-th output dimension
+  int narrow;                      // volume < 2^31: 32-bit indices, divisions by multiplication
+  FastDiv div[32];                 // of odim[k]
 };
 
 // Resident blocks per SM of the tiled kernel for this candidate (also raises the kernel's

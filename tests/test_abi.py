@@ -136,20 +136,22 @@ def test_plan_cache_load_rejects_foreign_and_damaged_files(native, tmp_path):
     assert load("# cutt-b200 plan cache v41\n" + good + "\n") == (bad_param, 0)
     assert load("") == (bad_param, 0)
     # damaged entries: thread count 0 or not a power of two, 3 stages, odd vector bytes, the
-    # element-wise methods (3, 5), unknown methods, short lines
+    # small-element method (5), unknown methods, short lines
     body = "\n".join([
         "0/4/64,48,/1,0, 2 128 512 65536 1 0 2 16 16 1 2 4 0 1 0 0",
         "0/4/64,48,/1,0, 2 128 512 65536 1 384 2 16 16 1 2 4 0 1 0 0",
         "0/4/64,48,/1,0, 2 128 512 65536 1 256 3 16 16 1 2 4 0 1 0 0",
         "0/4/64,48,/1,0, 2 128 512 65536 1 256 2 12 16 1 2 4 0 1 0 0",
         "0/4/64,48,/1,0, 2 128 512 65536 1 256 2 16 16 1 3 4 0 1 0 0",
-        "0/4/64,48,/1,0, 3 128 512 65536 1 256 2 16 16 1 2 4 0 1 0 0",
         "0/4/64,48,/1,0, 5 128 512 65536 1 256 2 16 16 1 2 4 0 1 0 0",
         "0/4/64,48,/1,0, 9 128 512 65536 1 256 2 16 16 1 2 4 0 1 0 0",
         "0/4/64,48,/1,0, 2 128 512",
     ])
     assert load("# cutt-b200 plan cache v4\n" + body + "\n") == (bad_param, 0)
     assert load("# cutt-b200 plan cache v4\n" + body + "\n" + good + "\n") == (0, 1)
+    # the element-per-thread kernel (3) can be a measured winner for small tensors
+    assert load("# cutt-b200 plan cache v4\n"
+                "0/4/64,48,/1,0, 3 128 512 65536 1 256 2 16 16 1 2 4 0 1 0 0\n") == (0, 1)
     native.clear_plan_cache()
 
 

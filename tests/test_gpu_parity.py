@@ -176,6 +176,35 @@ def test_identity_copy_equally_misaligned(native):
         assert native.copy_timeouts() == 0
 
 
+def test_small_tensor_element_kernel(native, oracle_mod, monkeypatch):
+    """Tensors of up to 1 MB: cuttPlan picks the element-per-thread kernel; with that candidate
+    switched off the tiled plans still serve the same problem.  Both are bit-exact."""
+    import json
+    import numpy as np
+    import torch
+    for dims, perm, elt in [([31, 549, 2, 3], [3, 0, 2, 1], 8), ([300, 340], [1, 0], 4),
+                            ([7, 11, 13, 17, 3], [4, 3, 2, 1, 0], 4)]:
+        n = int(np.prod(dims))
+        a = np.random.default_rng(3).integers(1, 2**31 - 1, n).astype(np.int64 if elt == 8 else np.int32)
+        want = oracle_mod.transpose_formula(dims, perm, a)
+        src = torch.from_numpy(a).cuda()
+        labels = []
+        for off in (False, True):
+            if off:
+                monkeypatch.setenv("CUTT_NO_NAIVE_CANDIDATE", "1")
+            native.clear_plan_cache()
+            dst = torch.zeros_like(src)
+            rc, h = native.cuttPlan(len(dims), dims, perm, elt)
+            assert rc == 0
+            labels.append(json.loads(native.plan_describe(h))["label"])
+            assert native.cuttExecute(h, src.data_ptr(), dst.data_ptr()) == 0
+            torch.cuda.synchronize()
+            native.cuttDestroy(h)
+            assert np.array_equal(dst.cpu().numpy(), want), (dims, perm, elt, labels)
+        monkeypatch.delenv("CUTT_NO_NAIVE_CANDIDATE")
+        assert labels[0] == "naive" and labels[1] != "naive", labels
+
+
 def test_streams(native, oracle_mod):
     """Ten plans on ten streams, all writing the same output (src/cutt_test.cpp:371-404)."""
     import torch
