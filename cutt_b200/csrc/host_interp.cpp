@@ -204,6 +204,8 @@ static void run_t2d_typed(const T2dDesc& D, const unsigned char* in, unsigned ch
     }
     if constexpr (ELT == 2) {
       for (uint32_t tid = 0; tid < D.nthreads; tid++) t2d_store_rows_e2(D, t, stage, out, tid);
+    } else if constexpr (ELT == 1) {
+      for (uint32_t tid = 0; tid < D.nthreads; tid++) t2d_store_rows_e1(D, t, stage, out, tid);
     } else if constexpr (STORE == 1) {
       for (uint32_t it = 0; it < nItems; it++) t2d_store_shear<ELT>(D, t, stage, out, it);
     } else {
@@ -231,6 +233,7 @@ static int run_t2d(const Candidate& c, const unsigned char* in, size_t inBytes, 
   T2D_CASE(4, 16, 4) T2D_CASE(4, 1, 4) T2D_CASE(4, 8, 4) T2D_CASE(4, 4, 4)
   T2D_ROW(8, 16) T2D_ROW(8, 1) T2D_ROW(8, 8)
   T2D_CASE(2, 16, 16) T2D_CASE(2, 8, 16) T2D_CASE(2, 4, 16)
+  T2D_CASE(1, 16, 16) T2D_CASE(1, 8, 16) T2D_CASE(1, 4, 16)
 #undef T2D_ROW
 #undef T2D_CASE
   return 4;

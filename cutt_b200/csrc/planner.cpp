@@ -836,7 +836,7 @@ bool build_tma(const Problem& P, const TileParams& tp, const DeviceInfo& dev, Ca
 bool build_t2d(const Problem& P, const TileParams& tp, const DeviceInfo& dev, Candidate& out) {
   const int r = P.rank;
   const int elt = P.elt;
-  if (elt != 4 && elt != 8 && elt != 2) return false;
+  if (elt != 4 && elt != 8 && elt != 2 && elt != 1) return false;
   if (r < 2 || r > kT2dMaxOuter + 2 || P.peerDim >= 0 || P.identity) return false;
   if (P.is[0] != 1) return false;
   int p = 0;
@@ -857,6 +857,7 @@ bool build_t2d(const Problem& P, const TileParams& tp, const DeviceInfo& dev, Ca
   };
   const uint32_t ta = tp.tinBytes / elt, tb = tp.toutBytes / elt;
   if ((ta * elt != 128 && ta * elt != 256) || (tb != 32 && tb != 64)) return false;
+  if (elt == 1 && tb != 64) return false;   // an item of the byte transpose is 16 rows, a warp pass 64
   if (tp.nthreads != 128 && tp.nthreads != 256) return false;
   if (P.d[0] * elt < 64 || P.d[p] < 16) return false;   // tiles would be mostly padding
   out = Candidate();
@@ -877,9 +878,9 @@ bool build_t2d(const Problem& P, const TileParams& tp, const DeviceInfo& dev, Ca
   D.loadMode = width(true);
   D.storeMode = width(false);
   if (tp.extend) D.loadMode = D.storeMode = 1;
-  // 2-byte elements: cp.async moves at least 4 bytes, and the 8 x 8 register transpose writes
-  // 16-byte vectors only
-  if (elt == 2 && (tp.extend || D.loadMode < 4 || D.storeMode != 16)) return false;
+  // 1- and 2-byte elements: cp.async moves at least 4 bytes, and the 16 x 16 / 8 x 8 register
+  // transposes write 16-byte vectors only
+  if (elt < 4 && (tp.extend || D.loadMode < 4 || D.storeMode != 16)) return false;
   D.padTop = D.storeMode == 1 ? kT2dPadTop : 0;
   D.rowsLoad = tb + (D.storeMode == 1 ? 16 / elt - 1 : 0);
   D.rowsAlloc = D.storeMode == 1 ? tb + kT2dPadTop + kT2dPadBottom : tb;
@@ -936,10 +937,10 @@ bool build_t2d(const Problem& P, const TileParams& tp, const DeviceInfo& dev, Ca
 }
 
 bool build_t2d_small(const Problem& P, const DeviceInfo& dev, Candidate& out) {
-  if (P.elt != 2) return false;
+  if (P.elt != 2 && P.elt != 1) return false;
   TileParams tp;
-  tp.tinBytes = 256;          // 128 elements along dimension 0 (two row blocks) ...
-  tp.toutBytes = 64 * 2;      // ... by 64 along the output's fastest dimension: 16 KB
+  tp.tinBytes = 256;          // 256 bytes along dimension 0 (two row blocks) ...
+  tp.toutBytes = 64 * P.elt;  // ... by 64 elements along the output's fastest dimension: 16 KB
   tp.stages = 1;
   // measured on B200, (20000,20000) 2-byte: 128 threads 5.2 TB/s, 256 threads 4.5; 128 x 32 tiles
   // 5.0, 64 x 64 tiles 5.0, tile order 0 the same as 1

@@ -44,6 +44,8 @@ tile2d_kernel(const __grid_constant__ T2dDesc D, const unsigned char* __restrict
     for (uint32_t it = tid; it < nItems; it += blockDim.x) t2d_store_shear<ELT>(D, t, stage, out, it);
   } else if constexpr (ELT == 2) {
     t2d_store_rows_e2(D, t, stage, out, tid);
+  } else if constexpr (ELT == 1) {
+    t2d_store_rows_e1(D, t, stage, out, tid);
   } else {
     t2d_store_rows<ELT, (STORE == 1 ? 16 : STORE)>(D, t, stage, out, tid);
   }
@@ -57,7 +59,8 @@ static T2dKernel pick_t2d(const T2dDesc& D) {
   T2D_ROW(4, 16) T2D_ROW(4, 1) T2D_ROW(4, 8) T2D_ROW(4, 4)
   T2D_CASE(4, 16, 4) T2D_CASE(4, 1, 4) T2D_CASE(4, 8, 4) T2D_CASE(4, 4, 4)
   T2D_ROW(8, 16) T2D_ROW(8, 1) T2D_ROW(8, 8)
-  T2D_CASE(2, 16, 16) T2D_CASE(2, 8, 16) T2D_CASE(2, 4, 16)   // 2-byte elements: extension entry points
+  T2D_CASE(2, 16, 16) T2D_CASE(2, 8, 16) T2D_CASE(2, 4, 16)   // 2- and 1-byte elements: extension entry points
+  T2D_CASE(1, 16, 16) T2D_CASE(1, 8, 16) T2D_CASE(1, 4, 16)
 #undef T2D_ROW
 #undef T2D_CASE
   return nullptr;

@@ -46,9 +46,9 @@ constexpr uint32_t kT2dPadTop = 4;      // shared-memory rows in front of tile r
 constexpr uint32_t kT2dPadBottom = 4;   // and behind the last one (never loaded, keeps reads in range)
 
 struct T2dDesc {
-  uint32_t elt;        // 4 or 8
+  uint32_t elt;        // 4 or 8; 1 or 2 for the extension entry points
   uint32_t ta;         // tile extent along dimension 0 (elements); ta * elt is a multiple of 128
-  uint32_t tb;         // tile extent along dimension p (elements): 32 or 64
+  uint32_t tb;         // tile extent along dimension p (elements): 32 or 64 (64 for 1-byte elements)
   uint32_t nboxes;     // ta * elt / 128
   uint32_t nthreads;
   uint32_t loadMode;   // 16, 8, 4 or 1 (see above)
@@ -368,6 +368,59 @@ CUTT_HD void t2d_store_rows_e2(const T2dDesc& D, const T2dTile& t, sptr_t stage,
         stg<16>(g0, y);
       }
       g0 += os0B;
+    }
+  }
+}
+
+// 1-byte elements: a chunk holds 16 elements, i.e. 16 output rows, so an item is 16 rows x one chunk:
+// 16 shared vector loads, a 16 x 16 transpose of bytes (sixteen 4 x 4 blocks, eight byte-permutes
+// each), 16 global stores of 16 bytes.  Lanes as for 2-byte elements: the quarter warp takes the 8
+// chunks of one shared-memory row, the 4 quarters take 4 groups of 16 rows.
+CUTT_HD uint32_t t2d_prmt(uint32_t a, uint32_t b, uint32_t sel) {
+#if defined(__CUDA_ARCH__)
+  return __byte_perm(a, b, sel);
+#else
+  const uint64_t v = ((uint64_t)b << 32) | a;
+  uint32_t r = 0;
+  for (int i = 0; i < 4; i++) r |= (uint32_t)((v >> (8u * ((sel >> (4 * i)) & 7u))) & 0xffu) << (8 * i);
+  return r;
+#endif
+}
+
+CUTT_HD void t2d_store_rows_e1(const T2dDesc& D, const T2dTile& t, sptr_t stage, unsigned char* gout, uint32_t tid) {
+  const uint32_t lane = tid & 31u;
+  const uint32_t cl = lane & 7u, g = lane >> 3;
+  const uint32_t gblocks = D.tb >> 6;                    // blocks of 4 groups x 16 rows
+  const uint32_t nblocks = D.nboxes * gblocks;
+  for (uint32_t ib = tid >> 5; ib < nblocks; ib += D.nthreads >> 5) {
+    const uint32_t cb = ib & (D.nboxes - 1u);            // (nboxes is 1 or 2)
+    const uint32_t gb = ib / D.nboxes;
+    const uint32_t chunk = cb * 8u + cl;
+    const uint32_t row0 = (gb * 4u + g) * 16u;
+    const uint32_t r0 = t.c0 + chunk * 16u;
+    if (r0 >= D.d0 || t.cp + row0 >= D.dp) continue;     // (dp is a multiple of 16: whole vectors)
+    uint32_t x[16][4];
+#pragma unroll
+    for (int i = 0; i < 16; i++) lds<16>(x[i], stage + t2d_smem_offset(D, cb, row0 + (uint32_t)i + D.padTop, cl));
+    unsigned char* g0 = gout + (t.outOff + (int64_t)(chunk * 16u) * D.os0 + (int64_t)row0);
+#pragma unroll
+    for (int jw = 0; jw < 4; jw++) {        // word jw of the chunk: output rows 4 jw .. 4 jw + 3
+      uint32_t o[4][4];
+#pragma unroll
+      for (int w = 0; w < 4; w++) {         // rows 4 w .. 4 w + 3 of the item: one 4 x 4 block of bytes
+        const uint32_t a = x[4 * w][jw], b = x[4 * w + 1][jw], c = x[4 * w + 2][jw], d = x[4 * w + 3][jw];
+        const uint32_t ab01 = t2d_prmt(a, b, 0x5140), cd01 = t2d_prmt(c, d, 0x5140);
+        const uint32_t ab23 = t2d_prmt(a, b, 0x7362), cd23 = t2d_prmt(c, d, 0x7362);
+        o[0][w] = t2d_prmt(ab01, cd01, 0x5410);
+        o[1][w] = t2d_prmt(ab01, cd01, 0x7632);
+        o[2][w] = t2d_prmt(ab23, cd23, 0x5410);
+        o[3][w] = t2d_prmt(ab23, cd23, 0x7632);
+      }
+#pragma unroll
+      for (int jj = 0; jj < 4; jj++) {
+        if (r0 + (uint32_t)(jw * 4 + jj) < D.d0) stg<16>(g0, o[jj]);
+        g0 += D.os0;
+      }
     }
   }
 }

@@ -160,3 +160,23 @@ def test_two_byte_elements_on_swizzled_tiles(native, oracle_mod):
         kinds[tuple(dims)] = desc
     assert "t2d " in kinds[(64, 72)] and "t2d " in kinds[(2000, 2008)] and "t2d " in kinds[(34, 8, 40)]
     assert "small" in kinds[(64, 70)] and "small" in kinds[(33, 72)]
+
+
+def test_one_byte_elements_on_swizzled_tiles(native, oracle_mod):
+    """1-byte elements with output rows on 16-byte boundaries run on the two-dimensional tile kernel
+    (16 x 16 byte transpose in registers); the same plans on buffers shifted by 1 or 2 bytes fall
+    back to the element-wise kernel; shapes outside the class never leave it."""
+    cases = [([128, 64], [1, 0]), ([272, 208], [1, 0]), ([72, 272], [1, 0]), ([68, 8, 80], [2, 1, 0]),
+             ([260, 3, 5, 48], [3, 0, 2, 1]), ([144, 6, 144], [1, 2, 0]), ([4000, 4016], [1, 0]), ([2064, 7, 528], [2, 1, 0]),
+             ([128, 72], [1, 0]), ([66, 80], [1, 0])]
+    kinds = {}
+    for dims, perm in cases:
+        raw = raw_bytes(volume(dims), 78)
+        want = expected(oracle_mod, dims, perm, 1, raw)
+        for planner in ("plan", "measure"):
+            for offset in (0, 1, 2, 16):
+                got, desc = run_ext(native, dims, perm, 1, raw, planner=planner, offset=offset)
+                assert np.array_equal(got, want), (dims, perm, planner, offset, desc)
+        kinds[tuple(dims)] = desc
+    assert "t2d " in kinds[(128, 64)] and "t2d " in kinds[(4000, 4016)] and "t2d " in kinds[(68, 8, 80)]
+    assert "small" in kinds[(128, 72)] and "small" in kinds[(66, 80)]

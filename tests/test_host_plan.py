@@ -434,3 +434,29 @@ def test_two_byte_elements_on_swizzled_tiles(hc, oracle_mod):
     assert ((34, 8, 40), "t2d") in seen                     # input rows on 4-byte boundaries
     assert ((64, 70), "small") in seen                      # output rows of 140 bytes: not 16-byte aligned
     assert ((33, 72), "small") in seen                      # input rows on 2-byte boundaries
+
+
+def test_one_byte_elements_on_swizzled_tiles(hc, oracle_mod):
+    """1-byte elements whose output rows start on 16-byte boundaries take the two-dimensional tile
+    method with its 16 x 16 byte transpose (input rows on 16-, 8- or 4-byte boundaries, ragged
+    edges along both tile dimensions); other shapes stay on the element-wise kernel."""
+    hc.cutt_hostcheck_run_ext.argtypes = [ctypes.c_int, ctypes.POINTER(ctypes.c_int), ctypes.POINTER(ctypes.c_int),
+                                          ctypes.c_int, ctypes.c_int, ctypes.c_void_p, ctypes.c_void_p,
+                                          ctypes.c_char_p, ctypes.c_int]
+    seen = set()
+    cases = [([128, 64], [1, 0]), ([272, 208], [1, 0]), ([72, 272], [1, 0]), ([68, 8, 80], [2, 1, 0]), ([260, 3, 5, 48], [3, 0, 2, 1]),
+             ([144, 6, 144], [1, 2, 0]), ([400, 3, 32], [2, 0, 1]), ([300, 16], [1, 0]), ([128, 72], [1, 0]), ([66, 80], [1, 0])]
+    for dims, perm in cases:
+        raw = np.random.default_rng(volume(dims)).integers(0, 256, volume(dims), dtype=np.uint8)
+        want = oracle_mod.transpose_numpy(dims, perm, raw)
+        out = np.full_like(raw, 0xEE)
+        lab = ctypes.create_string_buffer(4096)
+        rc = hc.cutt_hostcheck_run_ext(len(dims), _iarr(dims), _iarr(perm), 1, 0, raw.ctypes.data, out.ctypes.data, lab, 4096)
+        assert rc == 0, (rc, dims, perm)
+        assert np.array_equal(out, want), (dims, perm, lab.value.decode())
+        seen.add((tuple(dims), lab.value.decode().split(" ")[0]))
+    assert ((128, 64), "t2d") in seen and ((272, 208), "t2d") in seen and ((72, 272), "t2d") in seen
+    assert ((68, 8, 80), "t2d") in seen                     # input rows on 4-byte boundaries
+    assert ((300, 16), "t2d") in seen                       # a single vector along the output rows
+    assert ((128, 72), "small") in seen                     # output rows of 72 bytes: not 16-byte aligned
+    assert ((66, 80), "small") in seen                      # input rows on 2-byte boundaries
