@@ -192,6 +192,8 @@ def test_small_tensor_element_kernel(native, oracle_mod, monkeypatch):
         for off in (False, True):
             if off:
                 monkeypatch.setenv("CUTT_NO_NAIVE_CANDIDATE", "1")
+            else:
+                monkeypatch.delenv("CUTT_NO_NAIVE_CANDIDATE", raising=False)
             native.clear_plan_cache()
             dst = torch.zeros_like(src)
             rc, h = native.cuttPlan(len(dims), dims, perm, elt)
@@ -201,8 +203,30 @@ def test_small_tensor_element_kernel(native, oracle_mod, monkeypatch):
             torch.cuda.synchronize()
             native.cuttDestroy(h)
             assert np.array_equal(dst.cpu().numpy(), want), (dims, perm, elt, labels)
-        monkeypatch.delenv("CUTT_NO_NAIVE_CANDIDATE")
         assert labels[0] == "naive" and labels[1] != "naive", labels
+    native.clear_plan_cache()
+
+
+def test_small_tensor_element_kernel_all_permutations(native, oracle_mod, monkeypatch):
+    """The element-per-thread kernel with 32-bit indices over every permutation of ranks 2-6 (the
+    reference's test1 shapes), chosen by cuttPlan and by cuttPlanMeasure."""
+    import itertools
+    import json
+    monkeypatch.delenv("CUTT_NO_NAIVE_CANDIDATE", raising=False)
+    native.clear_plan_cache()
+    picked = 0
+    for rank in (2, 3, 4, 5, 6):
+        dims = dims_of_test1(rank)
+        for elt in (4, 8):
+            a = raw_bits(volume(dims), elt, 40 + rank)
+            for k, perm in enumerate(itertools.permutations(range(rank))):
+                if list(perm) == sorted(perm) or (rank == 6 and k % 7):
+                    continue
+                out, desc = gpu_transpose(native, dims, list(perm), elt, a, planner="measure" if k % 5 == 0 else "plan")
+                assert_bit_exact(out, oracle_mod.transpose_blocked(dims, list(perm), a), desc)
+                picked += 1 if json.loads(desc)["label"] == "naive" else 0
+    native.clear_plan_cache()
+    assert picked > 150
 
 
 def test_streams(native, oracle_mod):
