@@ -4,6 +4,7 @@
 #include <algorithm>
 #include <cmath>
 #include <cstdio>
+#include <cstdlib>
 #include <cstring>
 #include <set>
 
@@ -856,8 +857,9 @@ bool build_t2d(const Problem& P, const TileParams& tp, const DeviceInfo& dev, Ca
     return (uint32_t)elt;
   };
   const uint32_t ta = tp.tinBytes / elt, tb = tp.toutBytes / elt;
-  if ((ta * elt != 128 && ta * elt != 256) || (tb != 32 && tb != 64)) return false;
-  if (elt == 1 && tb != 64) return false;   // an item of the byte transpose is 16 rows, a warp pass 64
+  if (ta * elt != 128 && ta * elt != 256) return false;
+  if (elt >= 4 ? (tb != 32 && tb != 64) : (tb != 32 && tb != 64 && tb != 128 && tb != 256)) return false;
+  if (elt == 1 && tb < 64) return false;   // an item of the byte transpose is 16 rows, a warp pass 64
   if (tp.nthreads != 128 && tp.nthreads != 256) return false;
   if (P.d[0] * elt < 64 || P.d[p] < 16) return false;   // tiles would be mostly padding
   out = Candidate();
@@ -939,15 +941,30 @@ bool build_t2d(const Problem& P, const TileParams& tp, const DeviceInfo& dev, Ca
 bool build_t2d_small(const Problem& P, const DeviceInfo& dev, Candidate& out) {
   if (P.elt != 2 && P.elt != 1) return false;
   TileParams tp;
-  tp.tinBytes = 256;          // 256 bytes along dimension 0 (two row blocks) ...
-  tp.toutBytes = 64 * P.elt;  // ... by 64 elements along the output's fastest dimension: 16 KB
+  // Tall tiles: with elements this small the runs written per output row are only as long as the
+  // tile is high.  Measured on B200 (GB/s; 1-byte (28000,28000)/(1,0) and (1024,64,16384)/(2,1,0),
+  // 2-byte (20000,20000)/(1,0) and (1024,64,8192)/(2,1,0); tile = bytes along dimension 0 x rows):
+  //   256 x 64: 4770 5029 | 5334 5476     256 x 128: 5054 5364 | 5406 5533
+  //   128 x 128: 4740 4832 | 5407 5405    128 x 256: 5243 5282 | 5495 5533
+  // 128 threads throughout (256 threads: 4-15 % slower); tile order 0 the same as 1.
+  int p = 0;
+  for (int j = 1; j < P.rank; j++) if (P.os[j] < P.os[p]) p = j;
+  const int64_t dp = P.d[p];
+  const uint32_t rows = dp >= 224 ? 256u : (dp >= 112 ? 128u : 64u);
+  tp.tinBytes = rows == 256 ? 128 : 256;
+  tp.toutBytes = rows * P.elt;
   tp.stages = 1;
-  // measured on B200, (20000,20000) 2-byte: 128 threads 5.2 TB/s, 256 threads 4.5; 128 x 32 tiles
-  // 5.0, 64 x 64 tiles 5.0, tile order 0 the same as 1
   tp.nthreads = 128;
   tp.loopOrder = 1;
+  if (const char* v = getenv("CUTT_SMALL_TILE")) {   // tuning aid: "bytes along dimension 0,rows,threads"
+    unsigned a = 0, b = 0, n = 0;
+    if (sscanf(v, "%u,%u,%u", &a, &b, &n) == 3) { tp.tinBytes = a; tp.toutBytes = b * P.elt; tp.nthreads = (int)n; }
+  }
+  if (build_t2d(P, tp, dev, out)) return true;
+  tp.tinBytes = tp.tinBytes == 128 ? 256 : 128;
   if (build_t2d(P, tp, dev, out)) return true;
   tp.tinBytes = 128;
+  tp.toutBytes = 64 * P.elt;
   return build_t2d(P, tp, dev, out);
 }
 

@@ -48,7 +48,7 @@ constexpr uint32_t kT2dPadBottom = 4;   // and behind the last one (never loaded
 struct T2dDesc {
   uint32_t elt;        // 4 or 8; 1 or 2 for the extension entry points
   uint32_t ta;         // tile extent along dimension 0 (elements); ta * elt is a multiple of 128
-  uint32_t tb;         // tile extent along dimension p (elements): 32 or 64 (64 for 1-byte elements)
+  uint32_t tb;         // tile extent along dimension p (elements): 32 or 64; up to 256 for 1- and 2-byte elements
   uint32_t nboxes;     // ta * elt / 128
   uint32_t nthreads;
   uint32_t loadMode;   // 16, 8, 4 or 1 (see above)
