@@ -883,6 +883,12 @@ bool build_t2d(const Problem& P, const TileParams& tp, const DeviceInfo& dev, Ca
   // 1- and 2-byte elements: cp.async moves at least 4 bytes, and the 16 x 16 / 8 x 8 register
   // transposes write 16-byte vectors only
   if (elt < 4 && (tp.extend || D.loadMode < 4 || D.storeMode != 16)) return false;
+  if (elt < 4) {
+    // lane map 1 needs whole warp passes of 64 (2-byte) / 128 (1-byte) rows
+    const uint32_t pass = elt == 2 ? 64u : 128u;
+    const char* lm = getenv("CUTT_SMALL_LANEMAP");   // tuning aid
+    D.laneMap = (tb % pass == 0 && !(lm && lm[0] == '0')) ? 1u : 0u;
+  }
   D.padTop = D.storeMode == 1 ? kT2dPadTop : 0;
   D.rowsLoad = tb + (D.storeMode == 1 ? 16 / elt - 1 : 0);
   D.rowsAlloc = D.storeMode == 1 ? tb + kT2dPadTop + kT2dPadBottom : tb;
@@ -942,16 +948,19 @@ bool build_t2d_small(const Problem& P, const DeviceInfo& dev, Candidate& out) {
   if (P.elt != 2 && P.elt != 1) return false;
   TileParams tp;
   // Tall tiles: with elements this small the runs written per output row are only as long as the
-  // tile is high.  Measured on B200 (GB/s; 1-byte (28000,28000)/(1,0) and (1024,64,16384)/(2,1,0),
-  // 2-byte (20000,20000)/(1,0) and (1024,64,8192)/(2,1,0); tile = bytes along dimension 0 x rows):
-  //   256 x 64: 4770 5029 | 5334 5476     256 x 128: 5054 5364 | 5406 5533
-  //   128 x 128: 4740 4832 | 5407 5405    128 x 256: 5243 5282 | 5495 5533
-  // 128 threads throughout (256 threads: 4-15 % slower); tile order 0 the same as 1.
+  // tile is high.  Measured on B200 with lane map 1 (GB/s; 1-byte (28000,28000)/(1,0) and
+  // (1024,64,16384)/(2,1,0), 2-byte (20000,20000)/(1,0) and (1024,64,8192)/(2,1,0); tile = bytes
+  // along dimension 0 x rows):
+  //   256 x 128: 6027 5935 | 6102 6019     128 x 256: 5893 5887 | 6023 5924
+  //   128 x 128: 5208 5161 | 6066 5987     256 x 64:  4750 5000 (lane map 0) | 6155 6010
+  // (lane map 0, a store instruction writing 64 instead of 128 contiguous bytes per output row:
+  // 256 x 128: 4982 5313 | 5357 5460).  128 threads throughout (256 threads: 4-15 % slower); tile
+  // order 0 the same as 1.
   int p = 0;
   for (int j = 1; j < P.rank; j++) if (P.os[j] < P.os[p]) p = j;
   const int64_t dp = P.d[p];
-  const uint32_t rows = dp >= 224 ? 256u : (dp >= 112 ? 128u : 64u);
-  tp.tinBytes = rows == 256 ? 128 : 256;
+  const uint32_t rows = dp >= 112 ? 128u : 64u;
+  tp.tinBytes = 256;
   tp.toutBytes = rows * P.elt;
   tp.stages = 1;
   tp.nthreads = 128;

@@ -60,6 +60,9 @@ struct T2dDesc {
   uint32_t inMis;      // (input buffer address / elt) mod (16/elt); set when the kernel is launched
   uint32_t outMis;     // same for the output buffer
   uint32_t numTiles;
+  uint32_t laneMap;    // 1- and 2-byte elements: 0 = a quarter warp takes the 8 chunks of one row (a store
+                       // instruction writes 64 contiguous bytes per output row), 1 = 4 chunks x 8 row
+                       // groups per warp with the odd groups walking their rows from the middle (128 bytes)
   uint32_t order;      // tile index runs fastest along 0: dimension 0, 1: dimension p; 2 / 3: as 1 / 0,
                        // but in bands of four tiles across the other dimension (blocks that run at the
                        // same time then share lines on BOTH sides); tile indices past the end of a
@@ -342,7 +345,47 @@ CUTT_HD uint32_t t2d_pack16(uint32_t a, uint32_t b, bool high) {
 #endif
 }
 
+// Lane map 1 for 2-byte elements.  A warp pass covers 4 chunks (half a shared-memory row) x 8 groups
+// of 8 rows, so each store instruction writes 4 output rows x 128 contiguous bytes.  The two groups
+// met by a quarter warp would read the same banks (their rows agree in the bits the swizzle uses);
+// the odd group therefore reads its rows in the order 4,5,6,7,0,1,2,3, which flips swizzle bit 2, and
+// un-rotates the four output words with selects before it stores.
+CUTT_HD void t2d_store_rows_e2_wide(const T2dDesc& D, const T2dTile& t, sptr_t stage, unsigned char* gout, uint32_t tid) {
+  const uint32_t lane = tid & 31u;
+  const uint32_t cl = lane & 3u, g = lane >> 2;
+  const uint32_t rot = (g & 1u) * 4u;
+  const uint32_t nhalf = D.nboxes * 2u;                  // blocks of 4 chunks along dimension 0
+  const uint32_t nblocks = nhalf * (D.tb >> 6);          // x blocks of 8 groups x 8 rows
+  const int64_t os0B = D.os0 * 2;
+  for (uint32_t ib = tid >> 5; ib < nblocks; ib += D.nthreads >> 5) {
+    const uint32_t hb = ib & (nhalf - 1u), rb = ib / nhalf;
+    const uint32_t k = hb >> 1, c8 = (hb & 1u) * 4u + cl;
+    const uint32_t row0 = (rb * 8u + g) * 8u;
+    const uint32_t r0 = t.c0 + (k * 8u + c8) * 8u;
+    if (r0 >= D.d0 || t.cp + row0 >= D.dp) continue;     // (dp is a multiple of 8: whole vectors)
+    uint32_t x[8][4];
+#pragma unroll
+    for (int i = 0; i < 8; i++)
+      lds<16>(x[i], stage + t2d_smem_offset(D, k, row0 + (((uint32_t)i + rot) & 7u) + D.padTop, c8));
+    unsigned char* g0 = gout + (t.outOff + (int64_t)((k * 8u + c8) * 8u) * D.os0 + (int64_t)row0) * 2;
+#pragma unroll
+    for (int j = 0; j < 8; j++) {
+      if (r0 + (uint32_t)j < D.d0) {
+        uint32_t z[4], y[4];
+#pragma unroll
+        for (int w = 0; w < 4; w++) z[w] = t2d_pack16(x[2 * w][j >> 1], x[2 * w + 1][j >> 1], (j & 1) != 0);
+        // register pair w holds rows 2w + rot, 2w + rot + 1 (mod 8): output word w is pair w ^ 2 for the odd groups
+#pragma unroll
+        for (int w = 0; w < 4; w++) y[w] = rot ? z[w ^ 2] : z[w];
+        stg<16>(g0, y);
+      }
+      g0 += os0B;
+    }
+  }
+}
+
 CUTT_HD void t2d_store_rows_e2(const T2dDesc& D, const T2dTile& t, sptr_t stage, unsigned char* gout, uint32_t tid) {
+  if (D.laneMap == 1u) { t2d_store_rows_e2_wide(D, t, stage, gout, tid); return; }
   const uint32_t lane = tid & 31u;
   const uint32_t cl = lane & 7u, g = lane >> 3;
   const uint32_t gblocks = D.tb >> 5;                    // blocks of 4 groups x 8 rows
@@ -387,7 +430,55 @@ CUTT_HD uint32_t t2d_prmt(uint32_t a, uint32_t b, uint32_t sel) {
 #endif
 }
 
+// Lane map 1 for 1-byte elements: 4 chunks x 8 groups of 16 rows per warp pass (128 rows); the odd
+// groups read their rows in the order 4..15,0..3 and un-rotate the four output words.
+CUTT_HD void t2d_store_rows_e1_wide(const T2dDesc& D, const T2dTile& t, sptr_t stage, unsigned char* gout, uint32_t tid) {
+  const uint32_t lane = tid & 31u;
+  const uint32_t cl = lane & 3u, g = lane >> 2;
+  const uint32_t rot = (g & 1u) * 4u;
+  const uint32_t nhalf = D.nboxes * 2u;
+  const uint32_t nblocks = nhalf * (D.tb >> 7);          // x blocks of 8 groups x 16 rows
+  for (uint32_t ib = tid >> 5; ib < nblocks; ib += D.nthreads >> 5) {
+    const uint32_t hb = ib & (nhalf - 1u), rb = ib / nhalf;
+    const uint32_t k = hb >> 1, c8 = (hb & 1u) * 4u + cl;
+    const uint32_t row0 = (rb * 8u + g) * 16u;
+    const uint32_t r0 = t.c0 + (k * 8u + c8) * 16u;
+    if (r0 >= D.d0 || t.cp + row0 >= D.dp) continue;     // (dp is a multiple of 16: whole vectors)
+    uint32_t x[16][4];
+#pragma unroll
+    for (int i = 0; i < 16; i++)
+      lds<16>(x[i], stage + t2d_smem_offset(D, k, row0 + (((uint32_t)i + rot) & 15u) + D.padTop, c8));
+    unsigned char* g0 = gout + (t.outOff + (int64_t)((k * 8u + c8) * 16u) * D.os0 + (int64_t)row0);
+#pragma unroll
+    for (int jw = 0; jw < 4; jw++) {
+      uint32_t o[4][4];
+#pragma unroll
+      for (int w = 0; w < 4; w++) {
+        const uint32_t a = x[4 * w][jw], b = x[4 * w + 1][jw], c = x[4 * w + 2][jw], d = x[4 * w + 3][jw];
+        const uint32_t ab01 = t2d_prmt(a, b, 0x5140), cd01 = t2d_prmt(c, d, 0x5140);
+        const uint32_t ab23 = t2d_prmt(a, b, 0x7362), cd23 = t2d_prmt(c, d, 0x7362);
+        o[0][w] = t2d_prmt(ab01, cd01, 0x5410);
+        o[1][w] = t2d_prmt(ab01, cd01, 0x7632);
+        o[2][w] = t2d_prmt(ab23, cd23, 0x5410);
+        o[3][w] = t2d_prmt(ab23, cd23, 0x7632);
+      }
+#pragma unroll
+      for (int jj = 0; jj < 4; jj++) {
+        if (r0 + (uint32_t)(jw * 4 + jj) < D.d0) {
+          // register quad w holds rows 4w + rot .. (mod 16): output word w is quad w - 1 for the odd groups
+          uint32_t y[4];
+#pragma unroll
+          for (int w = 0; w < 4; w++) y[w] = rot ? o[jj][(w + 3) & 3] : o[jj][w];
+          stg<16>(g0, y);
+        }
+        g0 += D.os0;
+      }
+    }
+  }
+}
+
 CUTT_HD void t2d_store_rows_e1(const T2dDesc& D, const T2dTile& t, sptr_t stage, unsigned char* gout, uint32_t tid) {
+  if (D.laneMap == 1u) { t2d_store_rows_e1_wide(D, t, stage, gout, tid); return; }
   const uint32_t lane = tid & 31u;
   const uint32_t cl = lane & 7u, g = lane >> 3;
   const uint32_t gblocks = D.tb >> 6;                    // blocks of 4 groups x 16 rows
