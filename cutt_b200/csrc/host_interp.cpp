@@ -234,6 +234,7 @@ static int run_t2d(const Candidate& c, const unsigned char* in, size_t inBytes, 
   T2D_ROW(8, 16) T2D_ROW(8, 1) T2D_ROW(8, 8)
   T2D_CASE(2, 16, 16) T2D_CASE(2, 8, 16) T2D_CASE(2, 4, 16)
   T2D_CASE(1, 16, 16) T2D_CASE(1, 8, 16) T2D_CASE(1, 4, 16)
+  T2D_CASE(2, 16, 8) T2D_CASE(2, 8, 8) T2D_CASE(2, 4, 8)
 #undef T2D_ROW
 #undef T2D_CASE
   return 4;
@@ -346,7 +347,7 @@ int cutt_hostcheck_run_ext(int rank, const int* dim, const int* perm, int eltByt
     if (index > 0) return 3;
     {   // as the library: 2-byte elements on aligned rows take the swizzled two-dimensional tiles
       Candidate c;
-      if (build_t2d_small(P, g_dev, c) && (uintptr_t)in % c.t2d.loadMode == 0 && (uintptr_t)out % 16 == 0) {
+      if (build_t2d_small(P, g_dev, c) && (uintptr_t)in % c.t2d.loadMode == 0 && (uintptr_t)out % c.t2d.storeMode == 0) {
         if (label && labelLen > 0) snprintf(label, labelLen, "%s", c.label.c_str());
         return run_t2d(c, (const unsigned char*)in, bytes, (unsigned char*)out, (unsigned char*)out, (unsigned char*)out + bytes);
       }

@@ -384,7 +384,47 @@ CUTT_HD void t2d_store_rows_e2_wide(const T2dDesc& D, const T2dTile& t, sptr_t s
   }
 }
 
+// 2-byte elements whose output rows start on 8-byte boundaries only (store mode 8): an item is one chunk
+// (8 output rows) x 4 rows, written with 8-byte stores.  A warp pass covers 2 chunks x 16 groups of 4
+// rows, so each store instruction still writes 128 contiguous bytes per output row.  The four groups
+// met by a quarter warp lie 4 rows apart; groups 2 and 3 would repeat the swizzle bits of groups 0 and
+// 1, so they read their rows in the order 2,3,0,1 (which flips swizzle bit 1) and swap the two
+// output words back.
+CUTT_HD void t2d_store_rows_e2_w8(const T2dDesc& D, const T2dTile& t, sptr_t stage, unsigned char* gout, uint32_t tid) {
+  const uint32_t lane = tid & 31u;
+  const uint32_t cl = lane & 1u, g = lane >> 1;
+  const uint32_t rot = g & 2u;
+  const uint32_t npair = D.nboxes * 4u;                  // blocks of 2 chunks along dimension 0
+  const uint32_t nblocks = npair * (D.tb >> 6);          // x blocks of 16 groups x 4 rows
+  const int64_t os0B = D.os0 * 2;
+  for (uint32_t ib = tid >> 5; ib < nblocks; ib += D.nthreads >> 5) {
+    const uint32_t pb = ib & (npair - 1u), rb = ib / npair;
+    const uint32_t k = pb >> 2, c8 = (pb & 3u) * 2u + cl;
+    const uint32_t row0 = (rb * 16u + g) * 4u;
+    const uint32_t r0 = t.c0 + (k * 8u + c8) * 8u;
+    if (r0 >= D.d0 || t.cp + row0 >= D.dp) continue;     // (dp is a multiple of 4: whole vectors)
+    uint32_t x[4][4];
+#pragma unroll
+    for (int i = 0; i < 4; i++)
+      lds<16>(x[i], stage + t2d_smem_offset(D, k, row0 + (((uint32_t)i + rot) & 3u) + D.padTop, c8));
+    unsigned char* g0 = gout + (t.outOff + (int64_t)((k * 8u + c8) * 8u) * D.os0 + (int64_t)row0) * 2;
+#pragma unroll
+    for (int j = 0; j < 8; j++) {
+      if (r0 + (uint32_t)j < D.d0) {
+        const uint32_t z0 = t2d_pack16(x[0][j >> 1], x[1][j >> 1], (j & 1) != 0);
+        const uint32_t z1 = t2d_pack16(x[2][j >> 1], x[3][j >> 1], (j & 1) != 0);
+        uint32_t y[2];
+        y[0] = rot ? z1 : z0;
+        y[1] = rot ? z0 : z1;
+        stg<8>(g0, y);
+      }
+      g0 += os0B;
+    }
+  }
+}
+
 CUTT_HD void t2d_store_rows_e2(const T2dDesc& D, const T2dTile& t, sptr_t stage, unsigned char* gout, uint32_t tid) {
+  if (D.storeMode == 8u) { t2d_store_rows_e2_w8(D, t, stage, gout, tid); return; }
   if (D.laneMap == 1u) { t2d_store_rows_e2_wide(D, t, stage, gout, tid); return; }
   const uint32_t lane = tid & 31u;
   const uint32_t cl = lane & 7u, g = lane >> 3;

@@ -148,7 +148,8 @@ def test_two_byte_elements_on_swizzled_tiles(native, oracle_mod):
     element-wise kernel; shapes outside the class never leave it."""
     cases = [([64, 72], [1, 0]), ([136, 200], [1, 0]), ([36, 264], [1, 0]), ([34, 8, 40], [2, 1, 0]),
              ([130, 3, 5, 48], [3, 0, 2, 1]), ([72, 6, 136], [1, 2, 0]), ([2000, 2008], [1, 0]), ([1032, 7, 520], [2, 1, 0]),
-             ([64, 70], [1, 0]), ([33, 72], [1, 0])]
+             ([64, 70], [1, 0]), ([33, 72], [1, 0]),
+             ([72, 68], [1, 0]), ([134, 204], [1, 0]), ([40, 5, 132], [2, 1, 0]), ([2004, 2012], [1, 0])]   # 8-byte output rows
     kinds = {}
     for dims, perm in cases:
         raw = raw_bytes(volume(dims) * 2, 77)
@@ -160,6 +161,7 @@ def test_two_byte_elements_on_swizzled_tiles(native, oracle_mod):
         kinds[tuple(dims)] = desc
     assert "t2d " in kinds[(64, 72)] and "t2d " in kinds[(2000, 2008)] and "t2d " in kinds[(34, 8, 40)]
     assert "small" in kinds[(64, 70)] and "small" in kinds[(33, 72)]
+    assert "t2d " in kinds[(72, 68)] and "out/w4" in kinds[(2004, 2012)]
 
 
 def test_one_byte_elements_on_swizzled_tiles(native, oracle_mod):

@@ -420,7 +420,8 @@ def test_two_byte_elements_on_swizzled_tiles(hc, oracle_mod):
                                           ctypes.c_char_p, ctypes.c_int]
     seen = set()
     cases = [([64, 72], [1, 0]), ([136, 200], [1, 0]), ([36, 264], [1, 0]), ([34, 8, 40], [2, 1, 0]), ([130, 3, 5, 48], [3, 0, 2, 1]),
-             ([72, 6, 136], [1, 2, 0]), ([200, 3, 24], [2, 0, 1]), ([64, 70], [1, 0]), ([33, 72], [1, 0])]
+             ([72, 6, 136], [1, 2, 0]), ([200, 3, 24], [2, 0, 1]), ([64, 70], [1, 0]), ([33, 72], [1, 0]),
+             ([72, 68], [1, 0]), ([134, 204], [1, 0]), ([40, 5, 132], [2, 1, 0]), ([260, 3, 76], [2, 0, 1])]   # 8-byte output rows
     for dims, perm in cases:
         raw = np.random.default_rng(volume(dims)).integers(0, 65536, volume(dims), dtype=np.uint16)
         want = oracle_mod.transpose_numpy(dims, perm, raw)
@@ -432,8 +433,10 @@ def test_two_byte_elements_on_swizzled_tiles(hc, oracle_mod):
         seen.add((tuple(dims), lab.value.decode().split(" ")[0]))
     assert ((64, 72), "t2d") in seen and ((136, 200), "t2d") in seen and ((36, 264), "t2d") in seen
     assert ((34, 8, 40), "t2d") in seen                     # input rows on 4-byte boundaries
-    assert ((64, 70), "small") in seen                      # output rows of 140 bytes: not 16-byte aligned
+    assert ((64, 70), "small") in seen                      # output rows of 140 bytes: on 4-byte boundaries only
     assert ((33, 72), "small") in seen                      # input rows on 2-byte boundaries
+    for d in ((72, 68), (134, 204), (40, 5, 132), (260, 3, 76)):
+        assert (d, "t2d") in seen                           # 8-byte stores
 
 
 def test_one_byte_elements_on_swizzled_tiles(hc, oracle_mod):
