@@ -235,6 +235,7 @@ static int run_t2d(const Candidate& c, const unsigned char* in, size_t inBytes, 
   T2D_CASE(2, 16, 16) T2D_CASE(2, 8, 16) T2D_CASE(2, 4, 16)
   T2D_CASE(1, 16, 16) T2D_CASE(1, 8, 16) T2D_CASE(1, 4, 16)
   T2D_CASE(2, 16, 8) T2D_CASE(2, 8, 8) T2D_CASE(2, 4, 8)
+  T2D_CASE(1, 16, 8) T2D_CASE(1, 8, 8) T2D_CASE(1, 4, 8)
 #undef T2D_ROW
 #undef T2D_CASE
   return 4;

@@ -880,9 +880,9 @@ bool build_t2d(const Problem& P, const TileParams& tp, const DeviceInfo& dev, Ca
   D.loadMode = width(true);
   D.storeMode = width(false);
   if (tp.extend) D.loadMode = D.storeMode = 1;
-  // 1- and 2-byte elements: cp.async moves at least 4 bytes; the 16 x 16 byte transpose writes
-  // 16-byte vectors only, the half-word transpose 16-byte or (tiles of whole 64-row passes) 8-byte ones
-  if (elt < 4 && (tp.extend || D.loadMode < 4 || (D.storeMode != 16 && !(elt == 2 && D.storeMode == 8 && tb % 64 == 0))))
+  // 1- and 2-byte elements: cp.async moves at least 4 bytes; the register transposes write 16-byte
+  // or (tiles of whole 64-row passes) 8-byte vectors
+  if (elt < 4 && (tp.extend || D.loadMode < 4 || (D.storeMode != 16 && !(D.storeMode == 8 && tb % 64 == 0))))
     return false;
   if (elt < 4) {
     // lane map 1 needs whole warp passes of 64 (2-byte) / 128 (1-byte) rows

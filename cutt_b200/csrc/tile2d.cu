@@ -62,6 +62,7 @@ static T2dKernel pick_t2d(const T2dDesc& D) {
   T2D_CASE(2, 16, 16) T2D_CASE(2, 8, 16) T2D_CASE(2, 4, 16)   // 2- and 1-byte elements: extension entry points
   T2D_CASE(1, 16, 16) T2D_CASE(1, 8, 16) T2D_CASE(1, 4, 16)
   T2D_CASE(2, 16, 8) T2D_CASE(2, 8, 8) T2D_CASE(2, 4, 8)
+  T2D_CASE(1, 16, 8) T2D_CASE(1, 8, 8) T2D_CASE(1, 4, 8)
 #undef T2D_ROW
 #undef T2D_CASE
   return nullptr;

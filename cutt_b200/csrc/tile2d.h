@@ -517,7 +517,56 @@ CUTT_HD void t2d_store_rows_e1_wide(const T2dDesc& D, const T2dTile& t, sptr_t s
   }
 }
 
+// 1-byte elements whose output rows start on 8-byte boundaries only (store mode 8): an item is one chunk
+// (16 output rows) x 8 rows, written with 8-byte stores; 4 chunks x 8 groups of 8 rows per warp pass (a
+// store instruction writes 64 contiguous bytes per output row); the odd groups read their rows in the
+// order 4..7,0..3 and swap the two output words back.
+CUTT_HD void t2d_store_rows_e1_w8(const T2dDesc& D, const T2dTile& t, sptr_t stage, unsigned char* gout, uint32_t tid) {
+  const uint32_t lane = tid & 31u;
+  const uint32_t cl = lane & 3u, g = lane >> 2;
+  const uint32_t rot = (g & 1u) * 4u;
+  const uint32_t nhalf = D.nboxes * 2u;
+  const uint32_t nblocks = nhalf * (D.tb >> 6);          // x blocks of 8 groups x 8 rows
+  for (uint32_t ib = tid >> 5; ib < nblocks; ib += D.nthreads >> 5) {
+    const uint32_t hb = ib & (nhalf - 1u), rb = ib / nhalf;
+    const uint32_t k = hb >> 1, c8 = (hb & 1u) * 4u + cl;
+    const uint32_t row0 = (rb * 8u + g) * 8u;
+    const uint32_t r0 = t.c0 + (k * 8u + c8) * 16u;
+    if (r0 >= D.d0 || t.cp + row0 >= D.dp) continue;     // (dp is a multiple of 8: whole vectors)
+    uint32_t x[8][4];
+#pragma unroll
+    for (int i = 0; i < 8; i++)
+      lds<16>(x[i], stage + t2d_smem_offset(D, k, row0 + (((uint32_t)i + rot) & 7u) + D.padTop, c8));
+    unsigned char* g0 = gout + (t.outOff + (int64_t)((k * 8u + c8) * 16u) * D.os0 + (int64_t)row0);
+#pragma unroll
+    for (int jw = 0; jw < 4; jw++) {
+      uint32_t o[4][2];
+#pragma unroll
+      for (int w = 0; w < 2; w++) {
+        const uint32_t a = x[4 * w][jw], b = x[4 * w + 1][jw], c = x[4 * w + 2][jw], d = x[4 * w + 3][jw];
+        const uint32_t ab01 = t2d_prmt(a, b, 0x5140), cd01 = t2d_prmt(c, d, 0x5140);
+        const uint32_t ab23 = t2d_prmt(a, b, 0x7362), cd23 = t2d_prmt(c, d, 0x7362);
+        o[0][w] = t2d_prmt(ab01, cd01, 0x5410);
+        o[1][w] = t2d_prmt(ab01, cd01, 0x7632);
+        o[2][w] = t2d_prmt(ab23, cd23, 0x5410);
+        o[3][w] = t2d_prmt(ab23, cd23, 0x7632);
+      }
+#pragma unroll
+      for (int jj = 0; jj < 4; jj++) {
+        if (r0 + (uint32_t)(jw * 4 + jj) < D.d0) {
+          uint32_t y[2];
+          y[0] = rot ? o[jj][1] : o[jj][0];
+          y[1] = rot ? o[jj][0] : o[jj][1];
+          stg<8>(g0, y);
+        }
+        g0 += D.os0;
+      }
+    }
+  }
+}
+
 CUTT_HD void t2d_store_rows_e1(const T2dDesc& D, const T2dTile& t, sptr_t stage, unsigned char* gout, uint32_t tid) {
+  if (D.storeMode == 8u) { t2d_store_rows_e1_w8(D, t, stage, gout, tid); return; }
   if (D.laneMap == 1u) { t2d_store_rows_e1_wide(D, t, stage, gout, tid); return; }
   const uint32_t lane = tid & 31u;
   const uint32_t cl = lane & 7u, g = lane >> 3;

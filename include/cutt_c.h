@@ -32,9 +32,10 @@ int cutt_c_plan_measure(unsigned int* handle, int rank, const int* dim, const in
  * 16-byte elements move as pairs of 8-byte words through the ordinary plans.  1- and 2-byte
  * elements do so in 4- or 8-byte units when the fastest dimension stays fastest and its byte
  * length is a multiple of 4.  When the elements really move one by one: tensors whose output rows
- * start on 16-byte and whose input rows start on at least 4-byte boundaries take swizzled
- * shared-memory tiles with a register transpose of 16 x 16 bytes or 8 x 8 half-words (16-byte
- * stores); all other cases, and buffers that are not 16-byte aligned, an element-wise tiled kernel. */
+ * start on 16- or 8-byte and whose input rows start on at least 4-byte boundaries take swizzled
+ * shared-memory tiles with a register transpose of 16 x 16 bytes or 8 x 8 half-words (16- or 8-byte
+ * stores); all other cases, and buffers that are not aligned for the plan's access widths, an
+ * element-wise tiled kernel. */
 int cutt_c_plan_ext(unsigned int* handle, int rank, const int* dim, const int* permutation,
                     size_t sizeofType, void* stream);
 int cutt_c_plan_measure_ext(unsigned int* handle, int rank, const int* dim, const int* permutation,

@@ -170,7 +170,8 @@ def test_one_byte_elements_on_swizzled_tiles(native, oracle_mod):
     back to the element-wise kernel; shapes outside the class never leave it."""
     cases = [([128, 64], [1, 0]), ([272, 208], [1, 0]), ([72, 272], [1, 0]), ([68, 8, 80], [2, 1, 0]),
              ([260, 3, 5, 48], [3, 0, 2, 1]), ([144, 6, 144], [1, 2, 0]), ([4000, 4016], [1, 0]), ([2064, 7, 528], [2, 1, 0]),
-             ([128, 72], [1, 0]), ([66, 80], [1, 0])]
+             ([128, 72], [1, 0]), ([66, 80], [1, 0]), ([128, 76], [1, 0]), ([264, 200], [1, 0]), ([72, 5, 136], [2, 1, 0]),
+             ([4000, 4008], [1, 0])]
     kinds = {}
     for dims, perm in cases:
         raw = raw_bytes(volume(dims), 78)
@@ -181,4 +182,5 @@ def test_one_byte_elements_on_swizzled_tiles(native, oracle_mod):
                 assert np.array_equal(got, want), (dims, perm, planner, offset, desc)
         kinds[tuple(dims)] = desc
     assert "t2d " in kinds[(128, 64)] and "t2d " in kinds[(4000, 4016)] and "t2d " in kinds[(68, 8, 80)]
-    assert "small" in kinds[(128, 72)] and "small" in kinds[(66, 80)]
+    assert "t2d " in kinds[(128, 72)] and "out/w8" in kinds[(4000, 4008)]          # 8-byte output rows
+    assert "small" in kinds[(128, 76)] and "small" in kinds[(66, 80)]

@@ -448,7 +448,8 @@ def test_one_byte_elements_on_swizzled_tiles(hc, oracle_mod):
                                           ctypes.c_char_p, ctypes.c_int]
     seen = set()
     cases = [([128, 64], [1, 0]), ([272, 208], [1, 0]), ([72, 272], [1, 0]), ([68, 8, 80], [2, 1, 0]), ([260, 3, 5, 48], [3, 0, 2, 1]),
-             ([144, 6, 144], [1, 2, 0]), ([400, 3, 32], [2, 0, 1]), ([300, 16], [1, 0]), ([128, 72], [1, 0]), ([66, 80], [1, 0])]
+             ([144, 6, 144], [1, 2, 0]), ([400, 3, 32], [2, 0, 1]), ([300, 16], [1, 0]), ([128, 72], [1, 0]), ([66, 80], [1, 0]),
+             ([128, 76], [1, 0]), ([264, 200], [1, 0]), ([72, 5, 136], [2, 1, 0])]
     for dims, perm in cases:
         raw = np.random.default_rng(volume(dims)).integers(0, 256, volume(dims), dtype=np.uint8)
         want = oracle_mod.transpose_numpy(dims, perm, raw)
@@ -461,5 +462,6 @@ def test_one_byte_elements_on_swizzled_tiles(hc, oracle_mod):
     assert ((128, 64), "t2d") in seen and ((272, 208), "t2d") in seen and ((72, 272), "t2d") in seen
     assert ((68, 8, 80), "t2d") in seen                     # input rows on 4-byte boundaries
     assert ((300, 16), "t2d") in seen                       # a single vector along the output rows
-    assert ((128, 72), "small") in seen                     # output rows of 72 bytes: not 16-byte aligned
+    assert ((128, 72), "t2d") in seen and ((264, 200), "t2d") in seen and ((72, 5, 136), "t2d") in seen   # 8-byte stores
+    assert ((128, 76), "small") in seen                     # output rows of 76 bytes: on 4-byte boundaries only
     assert ((66, 80), "small") in seen                      # input rows on 2-byte boundaries
