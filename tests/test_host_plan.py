@@ -439,6 +439,40 @@ def test_two_byte_elements_on_swizzled_tiles(hc, oracle_mod):
         assert (d, "t2d") in seen                           # 8-byte stores
 
 
+@pytest.mark.parametrize("elt", [1, 2])
+def test_small_elements_random_shapes(hc, oracle_mod, elt):
+    """Random rank 2-4 shapes whose extents are multiples of 4, 8 or 16 elements: whatever path the
+    extension picks (swizzled tiles with 16- or 8-byte stores, re-stated units, element-wise kernel),
+    every access stays in range and aligned and the result is the permutation."""
+    import random
+    hc.cutt_hostcheck_run_ext.argtypes = [ctypes.c_int, ctypes.POINTER(ctypes.c_int), ctypes.POINTER(ctypes.c_int),
+                                          ctypes.c_int, ctypes.c_int, ctypes.c_void_p, ctypes.c_void_p,
+                                          ctypes.c_char_p, ctypes.c_int]
+    rng = random.Random(100 + elt)
+    kinds = {}
+    for _ in range(60):
+        rank = rng.choice([2, 2, 3, 3, 4])
+        unit = rng.choice([4, 8, 16])
+        dims = [unit * rng.randint(2, 24 if rank == 2 else 9) if rng.random() < 0.8 else rng.randint(2, 9) for _ in range(rank)]
+        if volume(dims) > 150_000:
+            continue
+        perm = list(range(rank))
+        while perm == sorted(perm):
+            rng.shuffle(perm)
+        raw = np.random.default_rng(volume(dims)).integers(0, 256 ** elt, volume(dims), dtype=np.uint8 if elt == 1 else np.uint16)
+        want = oracle_mod.transpose_numpy(dims, perm, raw)
+        out = np.full_like(raw, 0xEE)
+        lab = ctypes.create_string_buffer(4096)
+        rc = hc.cutt_hostcheck_run_ext(len(dims), _iarr(dims), _iarr(perm), elt, 0, raw.ctypes.data, out.ctypes.data, lab, 4096)
+        assert rc == 0, (rc, dims, perm, lab.value.decode())
+        assert np.array_equal(out, want), (dims, perm, lab.value.decode())
+        text = lab.value.decode()
+        kind = text.split(" ")[0] + (" " + [w for w in text.split(" ") if w.startswith("out/")][0] if text.startswith("t2d") else "")
+        kinds[kind] = kinds.get(kind, 0) + 1
+    assert any(k.startswith("t2d") for k in kinds), kinds
+    assert sum(kinds.values()) >= 40, kinds
+
+
 def test_one_byte_elements_on_swizzled_tiles(hc, oracle_mod):
     """1-byte elements whose output rows start on 16-byte boundaries take the two-dimensional tile
     method with its 16 x 16 byte transpose (input rows on 16-, 8- or 4-byte boundaries, ragged
