@@ -35,6 +35,13 @@
 // The lanes of a warp are spread over 4 chunks and 8 row groups (modes 16 and 1), so every store
 // instruction writes 128 contiguous bytes of each output row it touches, and the row groups met by
 // a quarter warp differ in the row bits the swizzle uses: shared-memory reads are conflict free.
+//
+// 1- and 2-byte elements (extension entry points; cp.async loads of 16, 8 or 4 bytes, stores of 16 or
+// 8 bytes, no shift / shear): a chunk holds 16 / 8 elements, so an item is 16 / 8 rows (store mode 16)
+// or 8 / 4 rows (store mode 8) of one chunk, transposed in registers with byte permutes
+// (t2d_store_rows_e1*, t2d_store_rows_e2*).  Row groups this tall agree in the row bits the swizzle
+// uses; where a quarter warp meets two or four of them, the later groups read their rows in rotated
+// order - which changes exactly those bits - and undo the rotation on the output words.
 #pragma once
 #include "permute_desc.h"
 #include "permute_tile_impl.h"
