@@ -617,7 +617,7 @@ cuttResult make_plan(cuttHandle* handle, int rank, const int* dim, const int* pe
         std::vector<std::pair<double, int>> scored;   // (score, candidate) of fully timed candidates
         Plan trial = *p;
         size_t nT2d = 0, nTma = 0;
-        const size_t familyQuota = env_size("CUTT_MEASURE_FAMILY", 6);
+        const size_t familyQuota = env_size("CUTT_MEASURE_FAMILY", 8);
         for (size_t i = 0; i < cands.size(); i++) {
           // beyond the model's best `topk`, only methods of another kind still get their turn; the
           // two swizzled-tile families are timed up to a quota each (their estimates are coarse, so

@@ -272,6 +272,17 @@ int cutt_hostcheck_num_candidates(int rank, const int* dim, const int* perm, int
   return (int)candidates_of(P).size();
 }
 
+// JSON description (label, model estimate, features) of candidate `index` without executing it.
+int cutt_hostcheck_describe(int rank, const int* dim, const int* perm, int elt, int index, char* label, int labelLen) {
+  Problem P;
+  if (!problem_from_cutt(rank, dim, perm, elt, P)) return 2;
+  const std::vector<Candidate>& cands = candidates_of(P);
+  if (index < 0 || index >= (int)cands.size()) return 3;
+  if (!label || labelLen <= 0) return 4;
+  snprintf(label, labelLen, "%s", describe(P, cands[index]).c_str());
+  return 0;
+}
+
 // Executes candidate `index` on host memory.  Returns 0 on success; `label` receives the
 // JSON description of the candidate.  Copy candidates are executed as a memcpy.
 int cutt_hostcheck_run(int rank, const int* dim, const int* perm, int elt, int index,

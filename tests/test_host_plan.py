@@ -439,6 +439,28 @@ def test_two_byte_elements_on_swizzled_tiles(hc, oracle_mod):
         assert (d, "t2d") in seen                           # 8-byte stores
 
 
+def test_swizzled_tile_candidates_lead_with_the_frequent_winners(hc):
+    """cuttPlanMeasure times only the first few candidates of the two-dimensional tile family; for a
+    large tensor those are the forms that win most often (256-byte x 64-row tiles, banded tile order
+    2, 256 threads), and the whole family sits inside the range the measurement covers."""
+    import json
+    hc.cutt_hostcheck_describe.argtypes = [ctypes.c_int, ctypes.POINTER(ctypes.c_int), ctypes.POINTER(ctypes.c_int),
+                                           ctypes.c_int, ctypes.c_int, ctypes.c_char_p, ctypes.c_int]
+    buf = ctypes.create_string_buffer(8192)
+    for dims, perm, elt, tile in (([14142, 14142], [1, 0], 8, "t=32x64"), ([1024, 1024, 512], [1, 0, 2], 4, "t=64x64")):
+        n = hc.cutt_hostcheck_num_candidates(len(dims), _iarr(dims), _iarr(perm), elt)
+        first = []
+        for i in range(n):
+            assert hc.cutt_hostcheck_describe(len(dims), _iarr(dims), _iarr(perm), elt, i, buf, 8192) == 0
+            d = json.loads(buf.value.decode())
+            if d["label"].startswith("t2d"):
+                first.append((i, d["label"]))
+        assert first and first[0][0] < 48, first[:2]
+        assert tile in first[0][1] and "lo=2" in first[0][1] and "nt=256" in first[0][1], first[0]
+        assert all(tile in lab for _, lab in first[:8]), first[:8]
+    assert hc.cutt_hostcheck_describe(2, _iarr([64, 64]), _iarr([1, 0]), 4, 100000, buf, 8192) == 3
+
+
 @pytest.mark.parametrize("elt", [1, 2])
 def test_small_elements_random_shapes(hc, oracle_mod, elt):
     """Random rank 2-4 shapes whose extents are multiples of 4, 8 or 16 elements: whatever path the
